@@ -1,0 +1,163 @@
+/*
+ * b200gemm: C ABI of the B200-native (sm_100a) GEMM layer.
+ *
+ * This is the boundary a host program binds to in place of the reference
+ * trainer's `Tcgen05Gemm` (gpu/gemm/src/host.rs:469-1098) and of the fp32
+ * `GpuTensor::matmul*` family (gpu/tensor-gpu/src/lib.rs:1754-1851).  Plain
+ * pointers and sizes only: every pointer named "device" is a CUDA device
+ * pointer owned by the caller, `stream` is a `cudaStream_t` passed as `void*`.
+ *
+ * All launches are asynchronous on `stream`.  Every function returns a
+ * `b200gemm_status_t`; nothing aborts the process.  Contract violations that
+ * the reference turns into `assert!` panics (host.rs:81-85, 395-400,
+ * 1105-1109, 1168-1171) are reported as B200GEMM_ERR_SHAPE / _INVALID.
+ *
+ * Differences from the reference boundary, on purpose:
+ *  - raw device pointers + runtime shapes replace caller-built TMA descriptors
+ *    (host.rs:102-465); tensor maps are encoded inside and passed by value;
+ *  - shapes need not be multiples of the tile (256, 256, 64): edges are
+ *    zero-filled on load and clipped on store by the copy engine.  Leading
+ *    dimensions must keep rows 16-byte aligned (multiples of 8 bf16 / 4 fp32);
+ *  - either operand may be MN-major independently, so a `[IN, OUT]` weight can
+ *    be read in place without a transposed shadow copy;
+ *  - split-K for the deep (K = tokens) weight-gradient shapes.
+ */
+#ifndef B200GEMM_H_
+#define B200GEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200GEMM_API __attribute__((visibility("default")))
+#else
+#define B200GEMM_API
+#endif
+
+typedef struct b200gemm_context* b200gemm_handle_t;
+
+typedef enum {
+  B200GEMM_OK = 0,
+  B200GEMM_ERR_INVALID = 1,      /* null pointer, bad enum, bad handle */
+  B200GEMM_ERR_SHAPE = 2,        /* extents / leading dimensions / alignment outside the contract */
+  B200GEMM_ERR_CUDA = 3,         /* a CUDA runtime or driver call failed (see b200gemm_last_error_string) */
+  B200GEMM_ERR_UNSUPPORTED = 4,  /* device is not sm_100, or the combination is not implemented */
+  B200GEMM_ERR_DEVICE = 5        /* a kernel reported a bounded-wait timeout (b200gemm_device_status) */
+} b200gemm_status_t;
+
+/* Operand orientation (gpu/gemm/src/host.rs:112-125 `TmaLayout`). */
+typedef enum {
+  B200GEMM_K_MAJOR = 0,  /* stored [rows, K], K contiguous   */
+  B200GEMM_MN_MAJOR = 1  /* stored [K, rows], rows contiguous */
+} b200gemm_layout_t;
+
+typedef enum { B200GEMM_OUT_F32 = 0, B200GEMM_OUT_BF16 = 1 } b200gemm_out_t;
+typedef enum { B200GEMM_STORE = 0, B200GEMM_ACCUMULATE = 1 } b200gemm_mode_t;
+
+/* flags */
+#define B200GEMM_FLAG_CTA_GROUP_1 0x1u /* force one-CTA 128x256 tiles               */
+#define B200GEMM_FLAG_CTA_GROUP_2 0x2u /* force CTA-pair 256x256 tiles (cta_group::2) */
+
+/*
+ * One launch: for e in [0, batch):  C[e][m, n] (=|+=) A[e] * B[e]^T
+ *   a_layout == K_MAJOR : A[e] is [m, k] with row stride lda;  MN_MAJOR : [k, m] with row stride lda
+ *   b_layout == K_MAJOR : B[e] is [n, k] with row stride ldb;  MN_MAJOR : [k, n] with row stride ldb
+ *   C[e] is [m, n] row-major with row stride ldc; fp32, or bf16 rounded to nearest even.
+ * Inputs are bf16; products are accumulated in fp32.
+ * Leading dimensions and batch strides are in elements; 0 means "dense".
+ *
+ * Covers one-for-one (gpu/gemm/src/host.rs):
+ *   store :616  store_batched :658  accumulate :695  accumulate_transposed :875
+ *   f32_store :729  f32_store_at :766  f32_store_batched :957  f32_store_transposed :1039
+ *   f32_accumulate :802  f32_accumulate_at :837  f32_accumulate_transposed(_at) :1074/:914
+ *   f32_accumulate_transposed_batched :997
+ * (`_at` = pass `c` already offset; `_batched` = batch > 1.)
+ */
+typedef struct {
+  const void* a;   /* device, bf16 */
+  const void* b;   /* device, bf16 */
+  void* c;         /* device, fp32 or bf16 */
+  int64_t m, n, k;
+  int64_t lda, ldb, ldc;
+  int32_t a_layout, b_layout; /* b200gemm_layout_t */
+  int32_t out_type;           /* b200gemm_out_t    */
+  int32_t mode;               /* b200gemm_mode_t   */
+  int32_t batch;              /* >= 1 ("experts", host.rs:658-687) */
+  int32_t split_k;            /* 0 = choose; 1 = none; >1 = that many K slices (fp32 output only) */
+  int64_t batch_stride_a, batch_stride_b, batch_stride_c;
+  uint32_t flags;
+  uint32_t reserved;
+} b200gemm_desc_t;
+
+/* Replaces Tcgen05Gemm::load (host.rs:508-530).  Creates per-device state on
+ * CUDA device `device`: opts kernels into large dynamic shared memory and
+ * allocates the 4-byte device status word.  Fails with ERR_UNSUPPORTED on a
+ * device that is not compute capability 10.x. */
+B200GEMM_API int b200gemm_create(int device, b200gemm_handle_t* out);
+B200GEMM_API int b200gemm_destroy(b200gemm_handle_t h);
+
+/* The tcgen05 GEMM (host.rs:616-1098, kernels gpu/gemm/src/optimized.rs:1138-1268). */
+B200GEMM_API int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
+
+/* The launch geometry b200gemm_gemm would use (tcgen05_launch_config,
+ * host.rs:47-94): grid, cluster size (1 or 2), dynamic shared memory, chosen
+ * split-K.  Any output pointer may be NULL. */
+B200GEMM_API int b200gemm_launch_config(b200gemm_handle_t h, const b200gemm_desc_t* desc,
+                                        int32_t* grid, int32_t* cluster, int32_t* smem_bytes,
+                                        int32_t* split_k);
+
+/*
+ * fp32 CUDA-core GEMM family for fp32 operands and arbitrary shapes
+ * (gpu/gemm/src/fp32.rs:141-191 register_gemm_{store,accumulate,nt_store,
+ * tn_accumulate}; gpu/tensor-gpu/src/lib.rs:1754-1851 GpuTensor::matmul,
+ * matmul_nt, matmul_tn).  All matrices dense row-major fp32.
+ *   op 0 (NN): C[m,n] = A[m,k] B[k,n]
+ *   op 1 (NT): C[m,n] = A[m,k] B[n,k]^T
+ *   op 2 (TN): C[m,n] = A[k,m]^T B[k,n]
+ * accumulate != 0 adds into C.
+ */
+typedef enum { B200GEMM_OP_NN = 0, B200GEMM_OP_NT = 1, B200GEMM_OP_TN = 2 } b200gemm_op_t;
+B200GEMM_API int b200gemm_sgemm(b200gemm_handle_t h, void* stream, int32_t op, int32_t accumulate,
+                                const float* a, const float* b, float* c, int64_t m, int64_t n,
+                                int64_t k);
+
+/* Staging converts and the packed transpose the GEMM callers use
+ * (gpu/tensor-gpu/src/lib.rs:403-413 convert_f32_to_bf16_pairs, :420-450
+ * convert_bf16_pairs_to_f32, :457-507 transpose_bf16_pairs).  `count` in
+ * elements; bf16 is round-to-nearest-even. */
+B200GEMM_API int b200gemm_convert_f32_to_bf16(b200gemm_handle_t h, void* stream, const float* src,
+                                              void* dst_bf16, int64_t count);
+B200GEMM_API int b200gemm_convert_bf16_to_f32(b200gemm_handle_t h, void* stream,
+                                              const void* src_bf16, float* dst, int64_t count);
+/* dst[cols, rows] = src[rows, cols]^T, bf16. */
+B200GEMM_API int b200gemm_transpose_bf16(b200gemm_handle_t h, void* stream, const void* src,
+                                         void* dst, int64_t rows, int64_t cols);
+
+/*
+ * Host-buffer form of b200gemm_gemm for callers that hold their matrices in
+ * host memory: copies A and B to the device, runs the GEMM, copies C back, and
+ * synchronises `stream`.  With mode == ACCUMULATE the host C is copied in
+ * first.  The device staging buffers belong to the handle and grow on demand.
+ */
+B200GEMM_API int b200gemm_gemm_host(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
+
+/* Synchronises `stream`, reads and clears the device status word; returns
+ * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
+ * *device_code (may be NULL).  The reference has no counterpart: its kernels
+ * never report errors from the device, and its host API returns driver
+ * failures only (gpu/gemm/src/host.rs:616-626 `Result<(), DriverError>`). */
+B200GEMM_API int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_code);
+
+/* Text of the last failure on the calling thread ("" if none). */
+B200GEMM_API const char* b200gemm_last_error_string(void);
+
+B200GEMM_API int b200gemm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GEMM_H_ */

@@ -1,0 +1,82 @@
+"""ctypes binding of the C ABI in ``include/b200gemm.h``.
+
+The library is the product; this module only loads it and declares the
+signatures.  There is no fallback: if the shared library is missing, loading
+raises, and on a machine without a B200 ``b200gemm_create`` fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200gemm.so")
+
+OK, ERR_INVALID, ERR_SHAPE, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
+K_MAJOR, MN_MAJOR = 0, 1
+OUT_F32, OUT_BF16 = 0, 1
+STORE, ACCUMULATE = 0, 1
+FLAG_CTA_GROUP_1, FLAG_CTA_GROUP_2 = 0x1, 0x2
+OP_NN, OP_NT, OP_TN = 0, 1, 2
+
+
+class GemmDesc(C.Structure):
+    """``b200gemm_desc_t``."""
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
+        ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+        ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+        ("a_layout", C.c_int32), ("b_layout", C.c_int32),
+        ("out_type", C.c_int32), ("mode", C.c_int32),
+        ("batch", C.c_int32), ("split_k", C.c_int32),
+        ("batch_stride_a", C.c_int64), ("batch_stride_b", C.c_int64), ("batch_stride_c", C.c_int64),
+        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/b200gemm.h declares.
+SIGNATURES = {
+    "b200gemm_version": (C.c_int, []),
+    "b200gemm_last_error_string": (C.c_char_p, []),
+    "b200gemm_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "b200gemm_destroy": (C.c_int, [C.c_void_p]),
+    "b200gemm_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(GemmDesc)]),
+    "b200gemm_gemm_host": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(GemmDesc)]),
+    "b200gemm_launch_config": (C.c_int, [C.c_void_p, C.POINTER(GemmDesc)] + [C.POINTER(C.c_int32)] * 4),
+    "b200gemm_sgemm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+                                 C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]),
+    "b200gemm_convert_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
+    "b200gemm_convert_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
+    "b200gemm_transpose_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
+    "b200gemm_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load ``libb200gemm.so`` (raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python __graft_entry__.py` "
+                "(there is no fallback implementation)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        _lib = lib
+    return _lib
+
+
+class B200GemmError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200gemm status {code}: {message}")
+        self.code = code
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise B200GemmError(code, load().b200gemm_last_error_string().decode())

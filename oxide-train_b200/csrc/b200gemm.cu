@@ -1,0 +1,462 @@
+// Host side of the C ABI declared in include/b200gemm.h: argument checking,
+// tensor-map encoding, launch planning (tile shape, CTA pairing, split-K) and
+// the launches themselves.  No cuBLAS, no CPU fallback: on a device that is not
+// sm_100 every entry point fails with B200GEMM_ERR_UNSUPPORTED.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/b200gemm.h"
+#include "aux_kernels.cuh"
+#include "gemm_kernel.cuh"
+
+namespace {
+
+using namespace b200;
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                         \
+  do {                                                                                         \
+    cudaError_t e_ = (expr);                                                                   \
+    if (e_ != cudaSuccess)                                                                     \
+      return fail(B200GEMM_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_),  \
+                  __FILE__, __LINE__);                                                         \
+  } while (0)
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+struct b200gemm_context {
+  int device = 0;
+  int sm_count = 0;
+  int* status = nullptr;        // device status word
+  EncodeTiledFn encode = nullptr;
+  // staging for b200gemm_gemm_host
+  void* stage[3] = {nullptr, nullptr, nullptr};
+  size_t stage_bytes[3] = {0, 0, 0};
+  bool smem_opt_in[2][3] = {{false, false, false}, {false, false, false}};
+  std::mutex mu;
+};
+
+namespace {
+
+// ---------------------------------------------------------------- tensor maps
+
+// A 3-D tiled, 128-byte-swizzled map over a row-major [batch][rows][inner]
+// array.  `row_stride` and `batch_stride` are in elements.
+int encode_map(const b200gemm_context* ctx, CUtensorMap* map, CUtensorMapDataType dtype,
+               int elem_bytes, const void* base, uint64_t inner, uint64_t rows, uint64_t batch,
+               uint64_t row_stride, uint64_t batch_stride, uint32_t box_inner, uint32_t box_rows,
+               const char* what) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "%s: base address must be 16-byte aligned", what);
+  if ((row_stride * elem_bytes) % 16 != 0 || (batch > 1 && (batch_stride * elem_bytes) % 16 != 0))
+    return fail(B200GEMM_ERR_SHAPE, "%s: row/batch strides must be multiples of 16 bytes", what);
+  if (box_inner * elem_bytes != 128)
+    return fail(B200GEMM_ERR_INVALID, "%s: inner box must span 128 bytes", what);
+  cuuint64_t dims[3] = {inner, rows, batch};
+  cuuint64_t strides[2] = {row_stride * elem_bytes,
+                           (batch > 1 ? batch_stride : rows * row_stride) * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ctx->encode(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200GEMM_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what,
+                static_cast<int>(r));
+  return B200GEMM_OK;
+}
+
+// ---------------------------------------------------------------- planning
+
+struct Plan {
+  int cta_group = 1;
+  int tile_m = 128;
+  int tiles_m = 0, tiles_n = 0;
+  int k_blocks = 0, split_k = 1, kb_per_split = 0;
+  int grid = 0;
+  int smem = 0;
+  int epi = kEpiF32Tma;
+  int reduce = 0;
+  int64_t lda = 0, ldb = 0, ldc = 0, bsa = 0, bsb = 0, bsc = 0;
+};
+
+int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+int choose_split_k(int64_t items, int k_blocks, int units) {
+  // Efficiency of the last wave when `items * s` work items are dealt to
+  // `units` persistent CTAs/clusters.  Splitting costs one extra pass of
+  // reduce-add traffic over C per slice, so the smallest split that fills the
+  // machine wins, and none is used when the plain launch already does.
+  auto eff = [&](int s) {
+    double total = static_cast<double>(items) * s;
+    double waves = static_cast<double>((static_cast<int64_t>(total) + units - 1) / units);
+    return total / (waves * units);
+  };
+  if (eff(1) >= 0.88) return 1;
+  int best = 1;
+  double best_eff = eff(1);
+  for (int s = 2; s <= 32; ++s) {
+    int per = (k_blocks + s - 1) / s;
+    if (per < 8) break;                                    // keep slices deep enough to pipeline
+    if (static_cast<int64_t>(s - 1) * per >= k_blocks) continue;  // would leave an empty slice
+    double e = eff(s);
+    if (e > best_eff + 0.02) {
+      best_eff = e;
+      best = s;
+      if (e >= 0.95) break;
+    }
+  }
+  return best;
+}
+
+int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
+  if (!d) return fail(B200GEMM_ERR_INVALID, "null descriptor");
+  if (!d->a || !d->b || !d->c) return fail(B200GEMM_ERR_INVALID, "null matrix pointer");
+  if (d->m <= 0 || d->n <= 0 || d->k <= 0 || d->batch < 1)
+    return fail(B200GEMM_ERR_SHAPE, "m, n, k must be positive and batch >= 1");
+  if (d->m > (1ll << 30) || d->n > (1ll << 30) || d->k > (1ll << 30))
+    return fail(B200GEMM_ERR_SHAPE, "extent too large");
+  if (d->a_layout < 0 || d->a_layout > 1 || d->b_layout < 0 || d->b_layout > 1)
+    return fail(B200GEMM_ERR_INVALID, "bad operand layout");
+  if (d->out_type < 0 || d->out_type > 1 || d->mode < 0 || d->mode > 1)
+    return fail(B200GEMM_ERR_INVALID, "bad output type or mode");
+  if (d->split_k < 0) return fail(B200GEMM_ERR_INVALID, "negative split_k");
+  const bool a_mn = d->a_layout == B200GEMM_MN_MAJOR, b_mn = d->b_layout == B200GEMM_MN_MAJOR;
+  p->lda = d->lda ? d->lda : (a_mn ? d->m : d->k);
+  p->ldb = d->ldb ? d->ldb : (b_mn ? d->n : d->k);
+  p->ldc = d->ldc ? d->ldc : d->n;
+  if (p->lda < (a_mn ? d->m : d->k) || p->ldb < (b_mn ? d->n : d->k) || p->ldc < d->n)
+    return fail(B200GEMM_ERR_SHAPE, "leading dimension smaller than the row it strides");
+  p->bsa = d->batch_stride_a ? d->batch_stride_a : p->lda * (a_mn ? d->k : d->m);
+  p->bsb = d->batch_stride_b ? d->batch_stride_b : p->ldb * (b_mn ? d->k : d->n);
+  p->bsc = d->batch_stride_c ? d->batch_stride_c : p->ldc * d->m;
+
+  const bool want2 = (d->flags & B200GEMM_FLAG_CTA_GROUP_2) != 0;
+  const bool want1 = (d->flags & B200GEMM_FLAG_CTA_GROUP_1) != 0;
+  if (want1 && want2) return fail(B200GEMM_ERR_INVALID, "both CTA-group flags set");
+  p->cta_group = want2 ? 2 : (want1 ? 1 : (d->m > 128 ? 2 : 1));
+  p->tile_m = kTileMCta * p->cta_group;
+  p->tiles_m = ceil_div(d->m, p->tile_m);
+  p->tiles_n = ceil_div(d->n, kTileN);
+  p->k_blocks = ceil_div(d->k, kBlockK);
+  const int64_t items = static_cast<int64_t>(d->batch) * p->tiles_m * p->tiles_n;
+  if (items > (1ll << 30)) return fail(B200GEMM_ERR_SHAPE, "too many tiles");
+  const int units = std::max(1, ctx->sm_count / p->cta_group);
+
+  const bool f32 = d->out_type == B200GEMM_OUT_F32;
+  p->split_k = 1;
+  if (f32) {
+    if (d->split_k == 0) p->split_k = choose_split_k(items, p->k_blocks, units);
+    else p->split_k = d->split_k;
+  } else if (d->split_k > 1) {
+    return fail(B200GEMM_ERR_UNSUPPORTED, "split-K needs fp32 output");
+  }
+  if (p->split_k > p->k_blocks) p->split_k = p->k_blocks;
+  p->kb_per_split = ceil_div(p->k_blocks, p->split_k);
+  p->split_k = ceil_div(p->k_blocks, p->kb_per_split);   // drop slices that would be empty
+
+  if (f32) {
+    p->epi = kEpiF32Tma;
+    p->reduce = (d->mode == B200GEMM_ACCUMULATE || p->split_k > 1) ? 1 : 0;
+  } else {
+    p->epi = d->mode == B200GEMM_ACCUMULATE ? kEpiBf16Rmw : kEpiBf16Tma;
+    if (p->epi == kEpiBf16Rmw && ((p->ldc % 8) != 0 || (p->bsc % 8) != 0))
+      return fail(B200GEMM_ERR_SHAPE, "bf16 accumulate needs ldc and batch stride multiples of 8");
+  }
+  const int64_t work = items * p->split_k;
+  p->grid = static_cast<int>(std::min<int64_t>(work, units)) * p->cta_group;
+  p->smem = p->cta_group == 2 ? GemmCfg<2>::kSmemBytes : GemmCfg<1>::kSmemBytes;
+  return B200GEMM_OK;
+}
+
+template <int CG, int EPI>
+int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan,
+               cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<CG, EPI>;
+  // Per-device opt-in to > 48 KiB dynamic shared memory, once per kernel
+  // (the reference's opt_in_dynamic_smem, host.rs:485-505).
+  bool& ready = ctx->smem_opt_in[CG - 1][EPI];
+  if (!ready) {
+    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  GemmCfg<CG>::kSmemBytes));
+    ready = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(plan.grid, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = GemmCfg<CG>::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
+  return B200GEMM_OK;
+}
+
+int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_t* d) {
+  Plan plan;
+  int rc = make_plan(ctx, d, &plan);
+  if (rc) return rc;
+  const bool a_mn = d->a_layout == B200GEMM_MN_MAJOR, b_mn = d->b_layout == B200GEMM_MN_MAJOR;
+
+  GemmParams params;
+  memset(&params, 0, sizeof(params));
+  const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!a_mn) rc = encode_map(ctx, &params.map_a, bf16, 2, d->a, d->k, d->m, d->batch, plan.lda, plan.bsa, 64, kTileMCta, "A");
+  else rc = encode_map(ctx, &params.map_a, bf16, 2, d->a, d->m, d->k, d->batch, plan.lda, plan.bsa, 64, 64, "A");
+  if (rc) return rc;
+  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, d->b, d->k, d->n, d->batch, plan.ldb, plan.bsb, 64, kTileN / plan.cta_group, "B");
+  else rc = encode_map(ctx, &params.map_b, bf16, 2, d->b, d->n, d->k, d->batch, plan.ldb, plan.bsb, 64, 64, "B");
+  if (rc) return rc;
+  if (plan.epi == kEpiF32Tma)
+    rc = encode_map(ctx, &params.map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d->c, d->n, d->m, d->batch, plan.ldc, plan.bsc, 32, 32, "C");
+  else if (plan.epi == kEpiBf16Tma)
+    rc = encode_map(ctx, &params.map_c, bf16, 2, d->c, d->n, d->m, d->batch, plan.ldc, plan.bsc, 64, 32, "C");
+  if (rc) return rc;
+
+  params.status = ctx->status;
+  params.c_bf16 = static_cast<uint16_t*>(d->c);
+  params.ldc = plan.ldc;
+  params.batch_stride_c = plan.bsc;
+  params.m = static_cast<int>(d->m);
+  params.n = static_cast<int>(d->n);
+  params.tiles_m = plan.tiles_m;
+  params.tiles_n = plan.tiles_n;
+  params.batch = d->batch;
+  params.k_blocks = plan.k_blocks;
+  params.split_k = plan.split_k;
+  params.kb_per_split = plan.kb_per_split;
+  params.a_mn = a_mn;
+  params.b_mn = b_mn;
+  params.reduce = plan.reduce;
+
+  if (plan.epi == kEpiF32Tma && d->mode == B200GEMM_STORE && plan.split_k > 1) {
+    // K slices all reduce-add into C, so a store starts from zeros.
+    for (int e = 0; e < d->batch; ++e) {
+      float* ce = static_cast<float*>(d->c) + static_cast<int64_t>(e) * plan.bsc;
+      CUDA_TRY(cudaMemset2DAsync(ce, plan.ldc * sizeof(float), 0, d->n * sizeof(float), d->m, stream));
+    }
+  }
+
+  if (plan.cta_group == 1) {
+    switch (plan.epi) {
+      case kEpiF32Tma: return launch_one<1, kEpiF32Tma>(ctx, params, plan, stream);
+      case kEpiBf16Tma: return launch_one<1, kEpiBf16Tma>(ctx, params, plan, stream);
+      default: return launch_one<1, kEpiBf16Rmw>(ctx, params, plan, stream);
+    }
+  }
+  switch (plan.epi) {
+    case kEpiF32Tma: return launch_one<2, kEpiF32Tma>(ctx, params, plan, stream);
+    case kEpiBf16Tma: return launch_one<2, kEpiBf16Tma>(ctx, params, plan, stream);
+    default: return launch_one<2, kEpiBf16Rmw>(ctx, params, plan, stream);
+  }
+}
+
+int check_handle(b200gemm_handle_t h) {
+  if (!h) return fail(B200GEMM_ERR_INVALID, "null handle");
+  return B200GEMM_OK;
+}
+
+}  // namespace
+
+// ==================================================================== C ABI
+
+extern "C" {
+
+int b200gemm_version(void) { return 100; }
+
+const char* b200gemm_last_error_string(void) { return g_error; }
+
+int b200gemm_create(int device, b200gemm_handle_t* out) {
+  if (!out) return fail(B200GEMM_ERR_INVALID, "null output handle");
+  *out = nullptr;
+  int count = 0;
+  CUDA_TRY(cudaGetDeviceCount(&count));
+  if (device < 0 || device >= count) return fail(B200GEMM_ERR_INVALID, "no CUDA device %d", device);
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(B200GEMM_ERR_UNSUPPORTED,
+                "device %d is compute capability %d.%d; this library is sm_100a only and has no "
+                "fallback path",
+                device, prop.major, prop.minor);
+  CUDA_TRY(cudaSetDevice(device));
+  b200gemm_context* ctx = new (std::nothrow) b200gemm_context();
+  if (!ctx) return fail(B200GEMM_ERR_INVALID, "out of host memory");
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    delete ctx;
+    return fail(B200GEMM_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  e = cudaMalloc(&ctx->status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    delete ctx;
+    return fail(B200GEMM_ERR_CUDA, "status word allocation failed: %s", cudaGetErrorString(e));
+  }
+  *out = ctx;
+  return B200GEMM_OK;
+}
+
+int b200gemm_destroy(b200gemm_handle_t h) {
+  if (!h) return B200GEMM_OK;
+  cudaSetDevice(h->device);
+  for (void* p : h->stage)
+    if (p) cudaFree(p);
+  if (h->status) cudaFree(h->status);
+  delete h;
+  return B200GEMM_OK;
+}
+
+int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  return launch_gemm(h, static_cast<cudaStream_t>(stream), desc);
+}
+
+int b200gemm_launch_config(b200gemm_handle_t h, const b200gemm_desc_t* desc, int32_t* grid,
+                           int32_t* cluster, int32_t* smem_bytes, int32_t* split_k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  Plan plan;
+  rc = make_plan(h, desc, &plan);
+  if (rc) return rc;
+  if (grid) *grid = plan.grid;
+  if (cluster) *cluster = plan.cta_group;
+  if (smem_bytes) *smem_bytes = plan.smem;
+  if (split_k) *split_k = plan.split_k;
+  return B200GEMM_OK;
+}
+
+int b200gemm_sgemm(b200gemm_handle_t h, void* stream, int32_t op, int32_t accumulate,
+                   const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!a || !b || !c) return fail(B200GEMM_ERR_INVALID, "null matrix pointer");
+  if (op < 0 || op > 2) return fail(B200GEMM_ERR_INVALID, "bad op");
+  if (m <= 0 || n <= 0 || k <= 0 || m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30))
+    return fail(B200GEMM_ERR_SHAPE, "bad extent");
+  CUDA_TRY(launch_sgemm(static_cast<cudaStream_t>(stream), op, accumulate != 0, a, b, c,
+                        static_cast<int>(m), static_cast<int>(n), static_cast<int>(k)));
+  return B200GEMM_OK;
+}
+
+int b200gemm_convert_f32_to_bf16(b200gemm_handle_t h, void* stream, const float* src,
+                                 void* dst_bf16, int64_t count) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!src || !dst_bf16) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (count < 0) return fail(B200GEMM_ERR_SHAPE, "negative count");
+  if (count == 0) return B200GEMM_OK;
+  CUDA_TRY(launch_f32_to_bf16(static_cast<cudaStream_t>(stream), src,
+                              static_cast<uint16_t*>(dst_bf16), count, h->sm_count));
+  return B200GEMM_OK;
+}
+
+int b200gemm_convert_bf16_to_f32(b200gemm_handle_t h, void* stream, const void* src_bf16,
+                                 float* dst, int64_t count) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!src_bf16 || !dst) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (count < 0) return fail(B200GEMM_ERR_SHAPE, "negative count");
+  if (count == 0) return B200GEMM_OK;
+  CUDA_TRY(launch_bf16_to_f32(static_cast<cudaStream_t>(stream),
+                              static_cast<const uint16_t*>(src_bf16), dst, count, h->sm_count));
+  return B200GEMM_OK;
+}
+
+int b200gemm_transpose_bf16(b200gemm_handle_t h, void* stream, const void* src, void* dst,
+                            int64_t rows, int64_t cols) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!src || !dst) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (rows <= 0 || cols <= 0 || rows > (1ll << 30) || cols > (1ll << 30))
+    return fail(B200GEMM_ERR_SHAPE, "bad extent");
+  CUDA_TRY(launch_transpose_bf16(static_cast<cudaStream_t>(stream),
+                                 static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst),
+                                 static_cast<int>(rows), static_cast<int>(cols)));
+  return B200GEMM_OK;
+}
+
+int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  Plan plan;
+  rc = make_plan(h, desc, &plan);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  std::lock_guard<std::mutex> lock(h->mu);
+  const size_t c_elem = desc->out_type == B200GEMM_OUT_F32 ? 4 : 2;
+  const size_t bytes[3] = {static_cast<size_t>(plan.bsa) * desc->batch * 2,
+                           static_cast<size_t>(plan.bsb) * desc->batch * 2,
+                           static_cast<size_t>(plan.bsc) * desc->batch * c_elem};
+  for (int i = 0; i < 3; ++i) {
+    if (h->stage_bytes[i] < bytes[i]) {
+      if (h->stage[i]) CUDA_TRY(cudaFree(h->stage[i]));
+      h->stage[i] = nullptr;
+      h->stage_bytes[i] = 0;
+      CUDA_TRY(cudaMalloc(&h->stage[i], bytes[i]));
+      h->stage_bytes[i] = bytes[i];
+    }
+  }
+  CUDA_TRY(cudaMemcpyAsync(h->stage[0], desc->a, bytes[0], cudaMemcpyHostToDevice, stream));
+  CUDA_TRY(cudaMemcpyAsync(h->stage[1], desc->b, bytes[1], cudaMemcpyHostToDevice, stream));
+  if (desc->mode == B200GEMM_ACCUMULATE)
+    CUDA_TRY(cudaMemcpyAsync(h->stage[2], desc->c, bytes[2], cudaMemcpyHostToDevice, stream));
+  b200gemm_desc_t dev = *desc;
+  dev.a = h->stage[0];
+  dev.b = h->stage[1];
+  dev.c = h->stage[2];
+  rc = launch_gemm(h, stream, &dev);
+  if (rc) return rc;
+  CUDA_TRY(cudaMemcpyAsync(desc->c, h->stage[2], bytes[2], cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(cudaStreamSynchronize(stream));
+  return B200GEMM_OK;
+}
+
+int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_code) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  int code = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemcpyAsync(&code, h->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  CUDA_TRY(cudaStreamSynchronize(s));
+  if (device_code) *device_code = code;
+  if (code != 0) {
+    CUDA_TRY(cudaMemsetAsync(h->status, 0, sizeof(int), s));
+    return fail(B200GEMM_ERR_DEVICE, "a kernel gave up waiting (device status %d)", code);
+  }
+  return B200GEMM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,384 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   C[e][M,N] (=|+=) A[e] * B[e]^T          fp32 accumulation in TMEM
+//
+// Roles per CTA (192 threads):
+//   warp 0      TMA producer: streams 128xBLOCK_K A tiles and B tiles through a
+//               multi-stage shared-memory ring, completion on "full" mbarriers
+//   warp 1      MMA issuer (one thread; only the leader CTA of a pair issues):
+//               tcgen05.mma into one of two 256-column TMEM accumulators,
+//               tcgen05.commit releases smem stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld (thread = output row), convert, stage in
+//               128-byte-swizzled shared memory, TMA store / TMA reduce-add
+//
+// kCtaGroup == 1: one CTA owns a 128x256 output tile (UMMA M128 N256).
+// kCtaGroup == 2: a 2-CTA cluster owns a 256x256 tile (UMMA M256 N256,
+//                 cta_group::2); each CTA loads its 128 rows of A and its 128
+//                 rows of B, so B is fetched once per pair without any
+//                 multicast load.
+//
+// Operands may each be K-major ([rows, K], K contiguous) or MN-major
+// ([K, rows], rows contiguous: the layout of a weight-gradient operand or of a
+// [IN, OUT] weight read as B).  The layout only changes the TMA boxes and two
+// descriptor fields, so it is a runtime parameter.
+//
+// The accumulator ping-pong lets the MMA of work item i+1 overlap the drain of
+// item i.  Work items are (batch, tile_m, tile_n, k_split) tuples handed out
+// round-robin to the persistent CTAs/clusters in a grouped raster order.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace b200 {
+
+constexpr int kBlockK = 64;       // bf16 elements per K block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K of one tcgen05.mma for 16-bit inputs
+constexpr int kTileMCta = 128;    // output rows per CTA (= TMEM lanes)
+constexpr int kTileN = 256;       // output columns per tile (= UMMA N)
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;    // two 256-column fp32 accumulators
+constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 B, one per epilogue warp per buffer
+constexpr int kRasterGroupM = 8;  // tile rows walked together so B panels stay in L2
+constexpr int kSubtileBytes = 64 * kBlockK * 2;  // one 64(mn) x 64(k) MN-major box
+
+enum EpilogueKind : int {
+  kEpiF32Tma = 0,       // fp32 C through TMA: store, or reduce-add when p.reduce != 0
+  kEpiBf16Tma = 1,      // bf16 C through TMA store
+  kEpiBf16Rmw = 2,      // bf16 C += acc: read C, add in fp32, round once, write
+};
+
+template <int kCtaGroup>
+struct GemmCfg {
+  static constexpr int kBRowsCta = kTileN / kCtaGroup;            // B rows this CTA loads
+  static constexpr int kABytes = kTileMCta * kBlockK * 2;         // 16 KiB
+  static constexpr int kBBytes = kBRowsCta * kBlockK * 2;         // 32 / 16 KiB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = kCtaGroup == 1 ? 4 : 6;          // 192 KiB of operand ring
+  static constexpr int kTileM = kTileMCta * kCtaGroup;
+  static constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;          // 32 KiB staging
+  static constexpr int kNumBarriers = 2 * kStages + 4;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kEpiBytes + kNumBarriers * 8 + 16 + 1024 /* alignment slack */;
+};
+
+struct GemmParams {
+  CUtensorMap map_a;   // K-major: {K, rows, batch} box {64, 128, 1}; MN-major: {rows, K, batch} box {64, 64, 1}
+  CUtensorMap map_b;   // K-major: box {64, 256 / cta_group, 1}; MN-major: box {64, 64, 1}
+  CUtensorMap map_c;   // {N, M, batch} box {32 (fp32) | 64 (bf16), 32, 1}, 128-byte swizzle
+  int* status;         // device status word, 0 = ok
+  uint16_t* c_bf16;    // only for kEpiBf16Rmw
+  long long ldc;       // elements, only for kEpiBf16Rmw
+  long long batch_stride_c;
+  int m, n;            // logical extents (for the read-modify-write epilogue's bounds)
+  int tiles_m, tiles_n, batch;
+  int k_blocks;        // ceil(K / 64)
+  int split_k;         // >= 1
+  int kb_per_split;    // ceil(k_blocks / split_k); every split is non-empty
+  int a_mn, b_mn;      // 1 = MN-major
+  int reduce;          // kEpiF32Tma: 1 = reduce-add into C
+};
+
+struct WorkItem {
+  int batch, tile_m, tile_n, kb_begin, kb_count;
+};
+
+__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
+  WorkItem w;
+  int split = item % p.split_k;
+  int t = item / p.split_k;
+  int tiles = p.tiles_m * p.tiles_n;
+  w.batch = t / tiles;
+  t -= w.batch * tiles;
+  int per_group = kRasterGroupM * p.tiles_n;
+  int group = t / per_group;
+  int first_m = group * kRasterGroupM;
+  int group_rows = min(p.tiles_m - first_m, kRasterGroupM);
+  int in_group = t - group * per_group;
+  w.tile_m = first_m + in_group % group_rows;
+  w.tile_n = in_group / group_rows;
+  w.kb_begin = split * p.kb_per_split;
+  w.kb_count = min(p.kb_per_split, p.k_blocks - w.kb_begin);
+  return w;
+}
+
+template <int kCtaGroup, int kEpi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<kCtaGroup>;
+  extern __shared__ uint8_t smem_raw[];
+
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
+  uint8_t* smem = smem_raw + (base - raw_addr);
+
+  const uint32_t ring = base;
+  const uint32_t epi = ring + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bars = epi + Cfg::kEpiBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bars - base) + 8 * Cfg::kNumBarriers);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / kCtaGroup;
+  const int num_clusters = gridDim.x / kCtaGroup;
+  const int total_items = p.batch * p.tiles_m * p.tiles_n * p.split_k;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4 * kCtaGroup);   // one arrival per epilogue warp per CTA
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    prefetch_tensormap(&p.map_a);
+    prefetch_tensormap(&p.map_b);
+    if (kEpi != kEpiBf16Rmw) prefetch_tensormap(&p.map_c);
+  }
+  if (warp == 2) {
+    tmem_alloc<kCtaGroup>(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish<kCtaGroup>();
+  }
+  tcgen05_fence_before_sync();
+  if constexpr (kCtaGroup == 2) cluster_sync(); else __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = cluster_id; ok && item < total_items; item += num_clusters) {
+        const WorkItem w = decode_item(p, item);
+        const int m0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta;
+        const int n0 = w.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
+        for (int kb = w.kb_begin; kb < w.kb_begin + w.kb_count; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kDevTimeoutProducer, abort_flag)) {
+            ok = false;
+            break;
+          }
+          // Both CTAs of a pair complete their bytes on the leader's barrier.
+          const uint32_t fb = kCtaGroup == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+          if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
+          const uint32_t a_dst = ring + stage * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kABytes;
+          const int k0 = kb * kBlockK;
+          if (!p.a_mn) {
+            tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, w.batch);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kTileMCta / 64; ++i)
+              tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, w.batch);
+          }
+          if (!p.b_mn) {
+            tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, w.batch);
+          } else {
+#pragma unroll
+            for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
+              tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, w.batch);
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc_bf16(Cfg::kTileM, kTileN, p.a_mn != 0, p.b_mn != 0);
+      // K-major: LBO unused (encoded 1), next K=16 slice is 32 bytes along the swizzled row.
+      // MN-major: LBO = one 64x64 subtile, next K=16 slice is 16 rows of 128 bytes.
+      const uint32_t a_lbo = p.a_mn ? kSubtileBytes : 16, a_kstep = p.a_mn ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn ? kSubtileBytes : 16, b_kstep = p.b_mn ? 2048 : 32;
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
+        const WorkItem w = decode_item(p, item);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        for (int kb = 0; kb < w.kb_count; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = ring + stage * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t da = make_smem_desc(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_bf16<kCtaGroup>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit<kCtaGroup>(empty_bar(stage));   // stage reusable once these MMAs retire
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;                 // TMEM lanes this warp may read
+    const uint32_t lane_base = quarter * 32u;
+    const uint32_t my_epi = epi + (warp - 2) * 2 * kEpiBufBytes;
+    uint32_t chunk_counter = 0;
+    int it = 0;
+    bool ok = true;
+    for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
+      const WorkItem w = decode_item(p, item);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.status, kDevTimeoutEpilogue, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after_sync();
+      const int row0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta + lane_base;
+      const int col0 = w.tile_n * kTileN;
+      const uint32_t t_acc = tmem_base + (lane_base << 16) + acc * kTileN;
+
+      auto release_accumulator = [&]() {
+        tcgen05_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtaGroup == 2) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
+          else mbar_arrive(tmem_empty_bar(acc));
+        }
+      };
+
+      if constexpr (kEpi == kEpiF32Tma) {
+        constexpr int kChunks = kTileN / 32;
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (c == kChunks - 1) release_accumulator();
+          const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+          if (lane == 0) tma_wait_group_read<1>();   // the store that last read this buffer is done
+          __syncwarp();
+          const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]),
+                         "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
+            else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
+            tma_commit_group();
+          }
+          ++chunk_counter;
+        }
+      } else if constexpr (kEpi == kEpiBf16Tma) {
+        constexpr int kChunks = kTileN / 64;
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t packed[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              packed[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          }
+          if (c == kChunks - 1) release_accumulator();
+          const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+          if (lane == 0) tma_wait_group_read<1>();
+          __syncwarp();
+          const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
+                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&p.map_c, buf, col0 + c * 64, row0, w.batch);
+            tma_commit_group();
+          }
+          ++chunk_counter;
+        }
+      } else {
+        // bf16 read-modify-write: thread = row, 32 columns (64 bytes) at a time.
+        constexpr int kChunks = kTileN / 32;
+        const int row = row0 + lane;
+        uint16_t* crow = p.c_bf16 + static_cast<long long>(w.batch) * p.batch_stride_c +
+                         static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (c == kChunks - 1) release_accumulator();
+          const int col = col0 + c * 32;
+          if (row < p.m) {
+            if (col + 32 <= p.n) {
+              uint4* ptr = reinterpret_cast<uint4*>(crow + col);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 old = ptr[q];
+                const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+                uint32_t nw[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float lo = __uint_as_float(o[j] << 16) + __uint_as_float(r[q * 8 + 2 * j]);
+                  const float hi = __uint_as_float(o[j] & 0xffff0000u) + __uint_as_float(r[q * 8 + 2 * j + 1]);
+                  nw[j] = pack_bf16x2(lo, hi);
+                }
+                ptr[q] = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.n; ++j) {
+                const float v = __uint_as_float(static_cast<uint32_t>(crow[col + j]) << 16) + __uint_as_float(r[j]);
+                crow[col + j] = static_cast<uint16_t>(pack_bf16x2(v, 0.f) & 0xffffu);
+              }
+            }
+          }
+        }
+      }
+    }
+    if (kEpi != kEpiBf16Rmw && lane == 0) tma_wait_group<0>();   // all stores landed before exit
+    __syncwarp();
+  }
+
+  // ------------------------------------------------------------ teardown
+  if (*abort_flag) {
+    // Something timed out: give copies that are still in flight time to land
+    // before the shared memory they target is released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tcgen05_fence_before_sync();
+  if constexpr (kCtaGroup == 2) cluster_sync(); else __syncthreads();
+  tcgen05_fence_after_sync();
+  if (warp == 2) tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
+}
+
+}  // namespace b200

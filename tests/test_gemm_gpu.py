@@ -1,0 +1,210 @@
+"""GPU parity of the tcgen05 GEMM against the CPU oracle, through the C ABI.
+
+Shapes and checks follow the reference's own kernel gates
+(gpu/gemm/src/main.rs:147-620): 256^3 in every mode against a CPU matmul on
+bf16-rounded inputs, the MN-major weight-gradient orientation, and the
+integer-periodic operands whose product is exact in fp32 so that bf16 outputs
+can be compared with ``==``.
+"""
+import numpy as np
+import pytest
+
+from _util import THREADS, assert_gemm_close, bf16_operand, from_dev_bf16, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+CTA_GROUPS = [1, 2]
+
+
+@pytest.fixture(scope="module")
+def gemm(pkg):
+    g = pkg.Tcgen05Gemm()
+    yield g
+    g.close()
+
+
+def _flags(pkg, cg):
+    return pkg._lib.FLAG_CTA_GROUP_1 if cg == 1 else pkg._lib.FLAG_CTA_GROUP_2
+
+
+def _tight(out_dtype):
+    # fp32 outputs differ from the oracle only by summation order; bf16 outputs
+    # add one rounding of the result (relative 2^-9).
+    import torch
+    return dict(rel_fro=2e-5, elem=2e-4) if out_dtype == torch.float32 else dict(rel_fro=4e-3, elem=8e-3)
+
+
+# ---- gpu/gemm/src/main.rs:515-620: 256^3, all four modes -------------------
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+def test_256_cubed_store_and_accumulate(pkg, oracle, gemm, cg, out):
+    import torch
+    M = N = K = 256
+    a, av = bf16_operand(oracle, (M, K), 1, kind="uniform")
+    b, bv = bf16_operand(oracle, (N, K), 2, kind="uniform")
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    dt = torch.float32 if out == "f32" else torch.bfloat16
+    c = torch.full((M, N), 7.0, dtype=dt, device="cuda")
+    gemm.gemm(a, b, c, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    got = c.float().cpu().numpy()
+    assert_gemm_close(got, ref, f"store cg{cg} {out}", **_tight(dt))
+    # accumulate on top of a known C
+    c0, c0v = bf16_operand(oracle, (M, N), 3, kind="uniform")
+    c = c0.to(dt).clone()
+    gemm.gemm(a, b, c, accumulate=True, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.float().cpu().numpy(), ref + c0v, f"accumulate cg{cg} {out}", **_tight(dt))
+
+
+# ---- gpu/gemm/src/main.rs:343-391: MN-major (weight-gradient) orientation ---
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("ta,tb", [(True, True), (False, True), (True, False)])
+def test_mn_major_operands(pkg, oracle, gemm, cg, ta, tb):
+    import torch
+    M, N, K = 256, 512, 192
+    a, av = bf16_operand(oracle, (K, M) if ta else (M, K), 4, kind="uniform")
+    b, bv = bf16_operand(oracle, (K, N) if tb else (N, K), 5, kind="uniform")
+    A = av.T if ta else av            # logical [M, K]
+    Bt = bv if tb else bv.T           # logical [K, N]
+    ref = oracle.matmul(np.ascontiguousarray(A), np.ascontiguousarray(Bt), THREADS)
+    c = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    gemm.gemm(a, b, c, transposed_a=ta, transposed_b=tb, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), ref, f"mn-major ta={ta} tb={tb} cg{cg}", rel_fro=2e-5, elem=2e-4)
+
+
+# ---- gpu/gemm/src/main.rs:180-335: many work items, exact equality ----------
+
+def _periodic(lines, depth, mul_l, mul_d, mod, sub):
+    i, d = np.meshgrid(np.arange(lines), np.arange(depth), indexing="ij")
+    return (((i * mul_l + d * mul_d) % mod) - sub).astype(np.float32)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("m,n", [(4096, 2560), (2816, 3584)])
+def test_many_items_are_exact(pkg, oracle, gemm, cg, m, n):
+    import torch
+    K = 256
+    av = _periodic(m, K, 5, 3, 7, 3)        # a_value, main.rs:266-268
+    bv = _periodic(n, K, 4, 5, 21, 10)      # b_value, main.rs:272-274
+    a = to_dev_bf16(oracle.bf16_bits(av))
+    b = to_dev_bf16(oracle.bf16_bits(bv))
+    table = av[:7].astype(np.int64) @ bv[:21].astype(np.int64).T          # exact 7x21 table
+    want = oracle.bf16_round(table.astype(np.float32))
+    full = np.tile(want, (m // 7 + 1, n // 21 + 1))[:m, :n]
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    gemm.store(a, b, c, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    got = from_dev_bf16(c)
+    assert np.array_equal(got, full), f"{int((got != full).sum())} of {m * n} elements wrong"
+    # fp32 output is the exact integer table
+    cf = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    gemm.f32_store(a, b, cf, flags=_flags(pkg, cg))
+    exact = np.tile(table.astype(np.float32), (m // 7 + 1, n // 21 + 1))[:m, :n]
+    assert np.array_equal(cf.cpu().numpy(), exact)
+    # folding the same product into C doubles every element (fp32: exactly)
+    gemm.f32_accumulate(a, b, cf, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert np.array_equal(cf.cpu().numpy(), 2 * exact)
+
+
+# ---- split-K, batches, offsets, ragged edges --------------------------------
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("split", [2, 5])
+def test_split_k_store_and_accumulate(pkg, oracle, gemm, cg, split):
+    import torch
+    M, N, K = 256, 256, 2048
+    a, av = bf16_operand(oracle, (K, M), 6)           # weight-gradient layout
+    b, bv = bf16_operand(oracle, (K, N), 7, std=0.01)
+    ref = oracle.matmul_tn(av, bv, THREADS)
+    c = torch.full((M, N), 3.0, dtype=torch.float32, device="cuda")
+    gemm.f32_store_transposed(a, b, c, split_k=split, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), ref, f"split{split} store", rel_fro=2e-5, elem=2e-4)
+    gemm.f32_accumulate_transposed(a, b, c, split_k=split, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), 2 * ref, f"split{split} accumulate", rel_fro=2e-5, elem=2e-4)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+def test_batched_experts(pkg, oracle, gemm, cg):
+    import torch
+    E, M, N, K = 3, 256, 256, 128
+    a, av = bf16_operand(oracle, (E, M, K), 8, kind="uniform")
+    b, bv = bf16_operand(oracle, (E, N, K), 9, kind="uniform")
+    ref = np.stack([oracle.matmul_nt(av[e], bv[e], THREADS) for e in range(E)])
+    c = torch.zeros((E, M, N), dtype=torch.float32, device="cuda")
+    gemm.f32_store_batched(a, b, c, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), ref, "f32_store_batched", rel_fro=2e-5, elem=2e-4)
+    cb = torch.zeros((E, M, N), dtype=torch.bfloat16, device="cuda")
+    gemm.store_batched(a, b, cb, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(from_dev_bf16(cb), ref, "store_batched", rel_fro=4e-3, elem=8e-3)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+def test_output_region_and_row_stride(pkg, oracle, gemm, cg):
+    import torch
+    M, N, K = 256, 256, 64
+    a, av = bf16_operand(oracle, (M, K), 10, kind="uniform")
+    b, bv = bf16_operand(oracle, (N, K), 11, kind="uniform")
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    buf = torch.full((3 * M * N,), -1.0, dtype=torch.float32, device="cuda")
+    gemm.f32_store_at(a, b, buf, M * N, M * N, N, flags=_flags(pkg, cg))     # middle third
+    assert gemm.device_status() == 0
+    host = buf.cpu().numpy()
+    assert np.all(host[:M * N] == -1.0) and np.all(host[2 * M * N:] == -1.0)  # neighbours untouched
+    assert_gemm_close(host[M * N:2 * M * N].reshape(M, N), ref, "f32_store_at", rel_fro=2e-5, elem=2e-4)
+    # a column block of a wider matrix: ldc > n (the grouped QKV outputs, gpu/model/src/lib.rs:1379)
+    wide = torch.full((M, 3 * N), -1.0, dtype=torch.float32, device="cuda")
+    gemm.f32_store(a, b, wide[:, N:2 * N], flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    w = wide.cpu().numpy()
+    assert np.all(w[:, :N] == -1.0) and np.all(w[:, 2 * N:] == -1.0)
+    assert_gemm_close(w[:, N:2 * N], ref, "ldc > n", rel_fro=2e-5, elem=2e-4)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+def test_ragged_edges_are_clipped(pkg, oracle, gemm, cg, out):
+    import torch
+    M, N, K = 200, 136, 72
+    a, av = bf16_operand(oracle, (M, K), 12, kind="uniform")
+    b, bv = bf16_operand(oracle, (N, K), 13, kind="uniform")
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    dt = torch.float32 if out == "f32" else torch.bfloat16
+    # canary rows after the matrix catch stores past the last row
+    c = torch.full((M + 8, N), 5.0, dtype=dt, device="cuda")
+    gemm.gemm(a, b, c[:M], flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    host = c.float().cpu().numpy()
+    assert np.all(host[M:] == 5.0)
+    assert_gemm_close(host[:M], ref, f"ragged {out}", **_tight(dt))
+    if out == "bf16":
+        c2 = c.clone()
+        gemm.accumulate(a, b, c2[:M], flags=_flags(pkg, cg))
+        assert gemm.device_status() == 0
+        h2 = c2.float().cpu().numpy()
+        assert np.all(h2[M:] == 5.0)
+        assert_gemm_close(h2[:M], host[:M] + ref, "ragged bf16 accumulate", rel_fro=4e-3, elem=1.6e-2)
+
+
+def test_contract_violations_return_status_codes(pkg, gemm):
+    import torch
+    L = pkg._lib
+    a = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros((64, 64), dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        gemm.gemm(a, a[:, :32].contiguous(), c)                      # K mismatch, caught on the host
+    cb = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(pkg.B200GemmError) as e:
+        gemm.gemm(a, a, cb, split_k=2)                               # split-K needs fp32 output
+    assert e.value.code == L.ERR_UNSUPPORTED
+    with pytest.raises(pkg.B200GemmError) as e:
+        gemm.gemm(a[:, 1:], a[:, 1:], c)                             # base not 16-byte aligned
+    assert e.value.code == L.ERR_SHAPE
