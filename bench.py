@@ -1,0 +1,421 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path: the full-step GEMM set of the ~183M dense model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (one "step"): every GEMM of one training step of the dense model
+B=32, T=1024 (M=32768 tokens), D=1536, FF=4096, 12 layers, lm-head 1536->50432:
+per layer the four forward projections (QKV, attention-out, MLP up, MLP down),
+their four input gradients and their four weight gradients (K = 32768 tokens,
+split-K), plus the lm-head trio.  Inputs are seeded synthetic tensors with the
+shapes and value distributions the model has (activations ~N(0,1), weights
+~N(0,0.02), upstream gradients ~N(0,1e-2)), bf16 operands, fp32 accumulation.
+
+Prints ONE JSON line.  `value` is whole-job TFLOP/s with every operand resident
+in HBM; `e2e` repeats the step with the token batch's activations copied from
+pinned host memory and a result word read back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# ---- the workload: BASELINE "configs[1]" -----------------------------------
+M_TOKENS, D_MODEL, D_FF, N_LAYERS, VOCAB_PAD, VOCAB = 32768, 1536, 4096, 12, 50432, 50257
+PROJECTIONS = [("qkv", D_MODEL, 3 * D_MODEL), ("attn_out", D_MODEL, D_MODEL),
+               ("mlp_up", D_MODEL, D_FF), ("mlp_down", D_FF, D_MODEL)]
+
+
+def step_flops(m=M_TOKENS) -> float:
+    per_layer = sum(2.0 * m * i * o for _, i, o in PROJECTIONS) * 3
+    return per_layer * N_LAYERS + 3 * 2.0 * m * D_MODEL * VOCAB_PAD
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": d.get("bf16_tflops_sustained"), "burst": d.get("bf16_tflops"),
+                "hbm_gbs": d.get("hbm_gbs"), "source": "measured"}
+    # Earlier measurement on the same pool, used only when the file is absent.
+    return {"tflops": 1400.0, "burst": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+# ---- clocks ------------------------------------------------------------------
+
+class ClockSampler(threading.Thread):
+    """Polls nvidia-smi for SM clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_flag = threading.Event()
+
+    def run(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop_flag.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                     "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                self.samples.append(float(f[0]))
+                self.max_mhz = float(f[1])
+                for name, val in zip(names, f[2:6]):
+                    if val.lower().startswith("active"):
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop_flag.wait(0.1)
+
+    def stop(self):
+        self._stop_flag.set()
+        self.join(timeout=6)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ---- reference arm: the CPU restatement of the reference's matmul family ------
+
+def cpu_sample(threads: int, rows: int | None = None, k_tokens: int | None = None):
+    """Time the oracle's matmul family on a bounded sample of the workload.
+
+    Forward and input-gradient shapes keep their full K and N but only `rows`
+    token rows; weight-gradient shapes keep their full output but only
+    `k_tokens` of the 32768-token reduction.  Returns (seconds, flops, text)."""
+    from oracle import oracle as orc
+    orc.build()
+    # About 130 MFLOP per sampled row: 128 rows per thread is roughly 10 s of scalar work.
+    rows = min(8192, 128 * threads) if rows is None else rows
+    k_tokens = rows if k_tokens is None else k_tokens
+    flops, secs = 0.0, 0.0
+    for _, i, o in PROJECTIONS:
+        x = orc.bf16_round(orc.normal(rows * i, 1)).reshape(rows, i)
+        w = orc.bf16_round(orc.normal(i * o, 2, 0.0, 0.02)).reshape(i, o)
+        dy = orc.bf16_round(orc.normal(rows * o, 3, 0.0, 0.01)).reshape(rows, o)
+        xs = orc.bf16_round(orc.normal(k_tokens * i, 4)).reshape(k_tokens, i)
+        dys = orc.bf16_round(orc.normal(k_tokens * o, 5, 0.0, 0.01)).reshape(k_tokens, o)
+        t0 = time.perf_counter()
+        orc.matmul(x, w, threads)            # forward      y  = x W
+        orc.matmul_nt(dy, w, threads)        # input grad   dx = dy W^T
+        orc.matmul_tn(xs, dys, threads)      # weight grad  dW = x^T dy
+        secs += time.perf_counter() - t0
+        flops += 2.0 * rows * i * o * 2 + 2.0 * k_tokens * i * o
+    text = (f"{rows} token rows of each forward/input-gradient GEMM (full K, N) and {k_tokens} "
+            f"tokens of each weight-gradient reduction, all four projections")
+    return secs, flops, text
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_sample(threads, rows=8, k_tokens=16)
+    t, f = 0.0, 0.0
+    text = ""
+    for _ in range(args.steps):
+        s, fl, text = cpu_sample(threads)
+        t += s
+        f += fl
+    value = f / t / 1e12
+    line = {
+        "impl": "reference", "metric": "bf16_gemm_tflops_full_step", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step_flops() / (value * 1e12) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": text + "; ms_per_step is extrapolated from the sample's rate"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "full-step GEMM set of the ~183M dense model (BASELINE configs[1]): "
+                        "B=32 T=1024 M=32768 D=1536 FF=4096 L=12, lm-head 1536->50432; "
+                        "forward + input-gradient + weight-gradient layouts",
+            "m_tokens": M_TOKENS, "d_model": D_MODEL, "d_ff": D_FF, "layers": N_LAYERS,
+            "vocab_padded": VOCAB_PAD, "parallelism": f"replicas x{n_gpus} (one token batch per GPU)",
+            "l2": "operands of successive launches differ and exceed the 126 MB L2"}
+
+
+# ---- the GPU arm ----------------------------------------------------------------
+
+class StepBuffers:
+    """All operands of one training step's GEMMs, resident in HBM."""
+
+    def __init__(self, torch, device, seed=0):
+        g = torch.Generator(device=device)
+        g.manual_seed(seed)
+        bf, f32 = torch.bfloat16, torch.float32
+
+        def rnd(shape, std):
+            return (torch.randn(shape, generator=g, device=device, dtype=f32) * std).to(bf)
+
+        self.layers = []
+        for _ in range(N_LAYERS):
+            layer = {}
+            for name, i, o in PROJECTIONS:
+                layer[name] = {
+                    "w": rnd((i, o), 0.02),                                   # [IN, OUT], read in place
+                    "dw": torch.zeros((i, o), device=device, dtype=f32),      # fp32 gradient accumulator
+                }
+            self.layers.append(layer)
+        # Activations and gradients are workspaces shared by the layers, as in a
+        # trainer; each is far larger than L2 on its own.
+        self.x = {i: rnd((M_TOKENS, i), 1.0) for i in (D_MODEL, D_FF)}
+        self.dy = {o: rnd((M_TOKENS, o), 0.01) for o in (D_MODEL, 3 * D_MODEL, D_FF)}
+        self.y = {o: torch.empty((M_TOKENS, o), device=device, dtype=f32)
+                  for o in (D_MODEL, 3 * D_MODEL, D_FF)}
+        self.head_w = rnd((D_MODEL, VOCAB_PAD), 0.02)
+        self.head_dw = torch.zeros((D_MODEL, VOCAB_PAD), device=device, dtype=f32)
+        self.logits = torch.empty((M_TOKENS, VOCAB_PAD), device=device, dtype=bf)
+        self.dh = torch.empty((M_TOKENS, D_MODEL), device=device, dtype=f32)
+
+
+def run_step(gemm, buf):
+    """One pass over the step's GEMMs.  Returns the number of GEMM launches."""
+    n = 0
+    for layer in buf.layers:                       # forward
+        for name, i, o in PROJECTIONS:
+            gemm.f32_store(buf.x[i], layer[name]["w"], buf.y[o], transposed_b=True)   # y = x W
+            n += 1
+    # lm-head forward: logits = h W
+    gemm.store(buf.x[D_MODEL], buf.head_w, buf.logits, transposed_b=True)
+    # lm-head backward: dW += h^T dlogits ; dh = dlogits W^T
+    gemm.f32_accumulate_transposed(buf.x[D_MODEL], buf.logits, buf.head_dw)
+    gemm.f32_store(buf.logits, buf.head_w, buf.dh)
+    n += 3
+    for layer in reversed(buf.layers):             # backward
+        for name, i, o in reversed(PROJECTIONS):
+            gemm.f32_accumulate_transposed(buf.x[i], buf.dy[o], layer[name]["dw"])   # dW += x^T dy
+            gemm.f32_store(buf.dy[o], layer[name]["w"], buf.y[i])                     # dx = dy W^T
+            n += 2
+    return n
+
+
+def per_shape_table(torch, gemm, buf, iters=3):
+    """TFLOP/s of every distinct GEMM of the step, timed alone (reported, not the headline)."""
+    rows = []
+    layer = buf.layers[0]
+
+    def timed(fn, flops):
+        fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / iters
+        return ms, flops / ms / 1e9
+
+    for name, i, o in PROJECTIONS:
+        fl = 2.0 * M_TOKENS * i * o
+        w, dw = layer[name]["w"], layer[name]["dw"]
+        for kind, fn in (
+            ("forward", lambda: gemm.f32_store(buf.x[i], w, buf.y[o], transposed_b=True)),
+            ("input_grad", lambda: gemm.f32_store(buf.dy[o], w, buf.y[i])),
+            ("weight_grad", lambda: gemm.f32_accumulate_transposed(buf.x[i], buf.dy[o], dw)),
+        ):
+            ms, tf = timed(fn, fl)
+            rows.append({"gemm": f"{name}.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
+    fl = 2.0 * M_TOKENS * D_MODEL * VOCAB_PAD
+    for kind, fn in (
+        ("forward", lambda: gemm.store(buf.x[D_MODEL], buf.head_w, buf.logits, transposed_b=True)),
+        ("weight_grad", lambda: gemm.f32_accumulate_transposed(buf.x[D_MODEL], buf.logits, buf.head_dw)),
+        ("input_grad", lambda: gemm.f32_store(buf.logits, buf.head_w, buf.dh)),
+    ):
+        ms, tf = timed(fn, fl)
+        rows.append({"gemm": f"lm_head.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
+    return rows
+
+
+def run_only(args):
+    """Profiling aid: launch ONE named GEMM of the step (e.g. qkv.forward) a few times.
+
+    Holds under 2 GB on the device and launches `warmup + steps` kernels, so a
+    profiler capture of it ends by itself.  Prints a short JSON line."""
+    import torch
+    import __graft_entry__ as entry
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pkg = entry.load_package()
+    gemm = pkg.Tcgen05Gemm(0)
+    name, kind = args.only.split(".")
+    bf, f32 = torch.bfloat16, torch.float32
+    if name == "lm_head":
+        i, o = D_MODEL, VOCAB_PAD
+    else:
+        i, o = {n: (a, b) for n, a, b in PROJECTIONS}[name]
+    m = args.only_tokens
+    x = torch.randn((m, i), device=dev).to(bf)
+    w = (torch.randn((i, o), device=dev) * 0.02).to(bf)
+    dy = (torch.randn((m, o), device=dev) * 0.01).to(bf)
+    if kind == "forward":
+        out = torch.empty((m, o), device=dev, dtype=bf if name == "lm_head" else f32)
+        fn = lambda: gemm.gemm(x, w, out, transposed_b=True)
+    elif kind == "input_grad":
+        out = torch.empty((m, i), device=dev, dtype=f32)
+        fn = lambda: gemm.f32_store(dy, w, out)
+    else:
+        out = torch.zeros((i, o), device=dev, dtype=f32)
+        fn = lambda: gemm.f32_accumulate_transposed(x, dy, out)
+    for _ in range(args.warmup):
+        fn()
+    torch.cuda.synchronize()
+    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        fn()
+    e0.record()
+    torch.cuda.synchronize()
+    ms = s0.elapsed_time(e0) / args.steps
+    print(json.dumps({"only": args.only, "tokens": m, "ms": ms, "tflops": 2.0 * m * i * o / ms / 1e9,
+                      "device_status": gemm.device_status()}), flush=True)
+    gemm.close()
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    pkg = entry.load_package()
+    gemm = pkg.Tcgen05Gemm(local)
+    buf = StepBuffers(torch, device, seed=rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        launches = run_step(gemm, buf)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        run_step(gemm, buf)
+    stop.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = start.elapsed_time(stop) / args.steps
+    status = gemm.device_status()
+
+    # ---- end to end: host token batch in, result word out ------------------------
+    host_x = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
+    host_x.copy_(buf.x[D_MODEL].cpu())
+    host_out = torch.empty(1, dtype=torch.float32).pin_memory()
+    e2e_steps = max(1, min(args.steps, 5))
+
+    def e2e_step():
+        buf.x[D_MODEL].copy_(host_x, non_blocking=True)         # this step's token activations
+        run_step(gemm, buf)
+        host_out.copy_(buf.dh.view(-1)[:1], non_blocking=True)  # one word of the step's last result
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e2.record()
+    barrier()
+    e2e_ms = s2.elapsed_time(e2) / e2e_steps
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    flops = step_flops()
+    value = flops * world / (ms * 1e-3) / 1e12
+    e2e_value = flops * world / (e2e_ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    per_gpu = value / world
+    line = {
+        "metric": "bf16_gemm_tflops_full_step", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "full_step_gemm_ms": ms, "pct_of_nominal_dense_peak": 100.0 * per_gpu / 2250.0,
+        "gpu_launches": launches * args.steps, "device_status": status, "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": 4,
+                "api": "Tcgen05Gemm methods over the C ABI; token activations from pinned host memory"},
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": per_gpu / peaks["tflops"], "traffic": None,
+                     "kernel": "gemm_tcgen05_kernel (every launch of the timed region)",
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
+                     "algorithmic_flops_per_step": flops},
+    }
+    if rank == 0:
+        if not args.no_table:
+            line["per_shape"] = per_shape_table(torch, gemm, buf)
+        if world == 1 and not args.no_cpu:
+            secs, fl, text = cpu_sample(1)
+            line["cpu_baseline"] = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                                    "sample": text + f"; {secs:.1f} s on one host core of {os.cpu_count()}"}
+        print(json.dumps(line), flush=True)
+    gemm.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-table", action="store_true", help="skip the per-shape table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default=None,
+                    help="profiling aid: run one GEMM, e.g. qkv.forward, mlp_up.weight_grad, lm_head.input_grad")
+    ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.only:
+        run_only(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

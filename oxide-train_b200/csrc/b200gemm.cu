@@ -21,6 +21,9 @@ namespace {
 using namespace b200;
 
 thread_local char g_error[512] = "";
+#ifdef B200_PROBE
+long long* g_probe = nullptr;   // diagnostic builds only: device buffer of phase counters
+#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -254,6 +257,9 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
   params.a_mn = a_mn;
   params.b_mn = b_mn;
   params.reduce = plan.reduce;
+#ifdef B200_PROBE
+  params.probe = g_probe;
+#endif
 
   if (plan.epi == kEpiF32Tma && d->mode == B200GEMM_STORE && plan.split_k > 1) {
     // K slices all reduce-add into C, so a store starts from zeros.
@@ -289,6 +295,12 @@ int check_handle(b200gemm_handle_t h) {
 extern "C" {
 
 int b200gemm_version(void) { return 100; }
+
+#ifdef B200_PROBE
+__attribute__((visibility("default"))) void b200gemm_set_probe(long long* device_buffer) {
+  g_probe = device_buffer;
+}
+#endif
 
 const char* b200gemm_last_error_string(void) { return g_error; }
 

@@ -2,9 +2,10 @@
 //
 //   C[e][M,N] (=|+=) A[e] * B[e]^T          fp32 accumulation in TMEM
 //
-// Roles per CTA (192 threads):
-//   warp 0      TMA producer: streams 128xBLOCK_K A tiles and B tiles through a
-//               multi-stage shared-memory ring, completion on "full" mbarriers
+// Roles per CTA (224 threads):
+//   warps 0, 6  TMA producers (alternate K blocks): stream 128xBLOCK_K A tiles and
+//               B tiles through a multi-stage shared-memory ring, completion on
+//               "full" mbarriers
 //   warp 1      MMA issuer (one thread; only the leader CTA of a pair issues):
 //               tcgen05.mma into one of two 256-column TMEM accumulators,
 //               tcgen05.commit releases smem stages and publishes accumulators
@@ -29,13 +30,33 @@
 
 #include "ptx.cuh"
 
+// Optional phase probe (compile with -DB200_PROBE): one thread per role adds the
+// clock cycles it spends in each phase into p.probe[blockIdx.x * 16 + slot].
+// Not compiled into the product library.
+#ifdef B200_PROBE
+#define PROBE_DECL long long probe_t_ = clock64(); const bool probe_on_ = true;
+#define PROBE_DECL_IF(cond) long long probe_t_ = clock64(); const bool probe_on_ = (cond);
+#define PROBE_ADD(slot)                                                        \
+  do {                                                                         \
+    long long now_ = clock64();                                                \
+    if (p.probe && probe_on_) atomicAdd(reinterpret_cast<unsigned long long*>(p.probe) + blockIdx.x * 16 + (slot), \
+                           static_cast<unsigned long long>(now_ - probe_t_));  \
+    probe_t_ = now_;                                                           \
+  } while (0)
+#else
+#define PROBE_DECL
+#define PROBE_DECL_IF(cond)
+#define PROBE_ADD(slot)
+#endif
+
 namespace b200 {
 
 constexpr int kBlockK = 64;       // bf16 elements per K block = one 128-byte swizzle row
 constexpr int kUmmaK = 16;        // K of one tcgen05.mma for 16-bit inputs
 constexpr int kTileMCta = 128;    // output rows per CTA (= TMEM lanes)
 constexpr int kTileN = 256;       // output columns per tile (= UMMA N)
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;
+constexpr int kProducerWarp1 = 6;  // second TMA producer (warp 0 is the first)
 constexpr int kTmemCols = 512;    // two 256-column fp32 accumulators
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 B, one per epilogue warp per buffer
 constexpr int kRasterGroupM = 8;  // tile rows walked together so B panels stay in L2
@@ -76,6 +97,9 @@ struct GemmParams {
   int kb_per_split;    // ceil(k_blocks / split_k); every split is non-empty
   int a_mn, b_mn;      // 1 = MN-major
   int reduce;          // kEpiF32Tma: 1 = reduce-add into C
+#ifdef B200_PROBE
+  long long* probe;
+#endif
 };
 
 struct WorkItem {
@@ -152,20 +176,29 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == kProducerWarp1) {
+    // ------------------------------------------------------------ TMA producers
+    // Two producer threads (in different warps) take alternate K blocks: one
+    // thread cannot issue the 2-5 bulk-tensor copies of a K block as fast as
+    // the tensor cores consume one.
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      const uint32_t which = warp == 0 ? 0u : 1u;
+      uint32_t g = 0;   // K blocks seen so far, over all of this CTA's work items
       bool ok = true;
+      PROBE_DECL_IF(which == 0)
       for (int item = cluster_id; ok && item < total_items; item += num_clusters) {
         const WorkItem w = decode_item(p, item);
         const int m0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta;
         const int n0 = w.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
-        for (int kb = w.kb_begin; kb < w.kb_begin + w.kb_count; ++kb) {
+        for (int kb = w.kb_begin; kb < w.kb_begin + w.kb_count; ++kb, ++g) {
+          if ((g & 1u) != which) continue;
+          const uint32_t stage = g % Cfg::kStages;
+          const uint32_t phase = (g / Cfg::kStages) & 1u;
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kDevTimeoutProducer, abort_flag)) {
             ok = false;
             break;
           }
+          PROBE_ADD(0);
           // Both CTAs of a pair complete their bytes on the leader's barrier.
           const uint32_t fb = kCtaGroup == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
           if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
@@ -186,7 +219,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
             for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
               tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, w.batch);
           }
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          PROBE_ADD(1);
         }
       }
     }
@@ -202,6 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
+      PROBE_DECL
       for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
         const WorkItem w = decode_item(p, item);
         const int acc = it & 1;
@@ -210,6 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           ok = false;
           break;
         }
+        PROBE_ADD(2);
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
         for (int kb = 0; kb < w.kb_count; ++kb) {
@@ -217,6 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
             ok = false;
             break;
           }
+          PROBE_ADD(3);
           tcgen05_fence_after_sync();
           const uint32_t a_addr = ring + stage * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + Cfg::kABytes;
@@ -228,6 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           }
           umma_commit<kCtaGroup>(empty_bar(stage));   // stage reusable once these MMAs retire
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          PROBE_ADD(4);
         }
         if (ok) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
       }
@@ -241,6 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     uint32_t chunk_counter = 0;
     int it = 0;
     bool ok = true;
+    PROBE_DECL_IF(warp == 2 && lane == 0)
     for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
       const WorkItem w = decode_item(p, item);
       const int acc = it & 1;
@@ -249,6 +287,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         ok = false;
         break;
       }
+      PROBE_ADD(5);
       tcgen05_fence_after_sync();
       const int row0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta + lane_base;
       const int col0 = w.tile_n * kTileN;
@@ -271,9 +310,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           tmem_ld_32x32(t_acc + c * 32, r);
           tmem_ld_wait();
           if (c == kChunks - 1) release_accumulator();
+          PROBE_ADD(6);
           const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
           if (lane == 0) tma_wait_group_read<1>();   // the store that last read this buffer is done
           __syncwarp();
+          PROBE_ADD(7);
           const uint32_t row_addr = buf + lane * 128u;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -284,11 +325,13 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           }
           fence_proxy_async_smem();
           __syncwarp();
+          PROBE_ADD(8);
           if (lane == 0) {
             if (p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
             else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
             tma_commit_group();
           }
+          PROBE_ADD(9);
           ++chunk_counter;
         }
       } else if constexpr (kEpi == kEpiBf16Tma) {
