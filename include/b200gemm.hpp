@@ -1,0 +1,132 @@
+// C++ host mirror of the reference's `Tcgen05Gemm` (gpu/gemm/src/host.rs:469-1098)
+// over the C ABI in b200gemm.h.  Header-only; method names, argument meaning and
+// the store / accumulate / transposed / batched / `_at` split follow the
+// reference one for one.  Where the reference panics on a contract violation
+// (host.rs:81-85, 1105-1109, 1168-1171) these methods return the library's
+// status code instead; `last_error()` has the text.
+//
+// A "K-major" operand is stored [rows, K]; a "transposed" (MN-major) operand is
+// stored [K, rows].  Device pointers are the caller's; `stream` is a
+// cudaStream_t passed as void*.
+#ifndef B200GEMM_HPP_
+#define B200GEMM_HPP_
+
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+#include "b200gemm.h"
+
+namespace b200gemm {
+
+/// TMA panel edge, reduction tile and CTA-pair tile (host.rs:13-19).
+constexpr int TC_TILE = 128, TC_BK = 64, TC_M_TILE = 256, TC_N_TILE = 256;
+
+/// A bf16 operand: device pointer + how it is laid out.  Replaces the
+/// reference's `Bf16TmaMap` / `Bf16PairsTmaMap(s)` (host.rs:267-465): the
+/// tensor map is built inside the library from these fields.
+struct Operand {
+  const void* ptr = nullptr;
+  int64_t rows = 0;          // M or N
+  int64_t k = 0;             // reduction extent
+  int64_t ld = 0;            // row stride in elements (0 = dense)
+  int64_t batch_stride = 0;  // elements between experts (0 = dense)
+  b200gemm_layout_t layout = B200GEMM_K_MAJOR;
+};
+
+class Tcgen05Gemm {
+ public:
+  /// Tcgen05Gemm::load (host.rs:508-530).
+  explicit Tcgen05Gemm(int device) {
+    if (b200gemm_create(device, &h_) != B200GEMM_OK) throw std::runtime_error(last_error());
+  }
+  ~Tcgen05Gemm() { b200gemm_destroy(h_); }
+  Tcgen05Gemm(const Tcgen05Gemm&) = delete;
+  Tcgen05Gemm& operator=(const Tcgen05Gemm&) = delete;
+
+  static std::string last_error() { return b200gemm_last_error_string(); }
+  b200gemm_handle_t handle() const { return h_; }
+
+  // ---- bf16 output ---------------------------------------------------------
+  /// C = A.B^T, packed bf16 (host.rs:616).
+  int store(void* stream, const Operand& a, const Operand& b, void* out) const {
+    return run(stream, a, b, out, B200GEMM_OUT_BF16, B200GEMM_STORE, 1);
+  }
+  /// `experts` equal-shaped C = A.B^T in one launch (host.rs:658).
+  int store_batched(void* stream, const Operand& a, const Operand& b, void* out, int experts) const {
+    return run(stream, a, b, out, B200GEMM_OUT_BF16, B200GEMM_STORE, experts);
+  }
+  /// C += A.B^T in bf16 (host.rs:695).
+  int accumulate(void* stream, const Operand& a, const Operand& b, void* out) const {
+    return run(stream, a, b, out, B200GEMM_OUT_BF16, B200GEMM_ACCUMULATE, 1);
+  }
+  /// C += A^T.B, both operands MN-major (host.rs:875).
+  int accumulate_transposed(void* stream, Operand a, Operand b, void* out) const {
+    a.layout = b.layout = B200GEMM_MN_MAJOR;
+    return run(stream, a, b, out, B200GEMM_OUT_BF16, B200GEMM_ACCUMULATE, 1);
+  }
+
+  // ---- fp32 output, overwrite ----------------------------------------------
+  int f32_store(void* stream, const Operand& a, const Operand& b, float* out) const {
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_STORE, 1);
+  }
+  /// Writes out[offset .. offset + m*n) (host.rs:766).
+  int f32_store_at(void* stream, const Operand& a, const Operand& b, float* out, size_t offset) const {
+    return run(stream, a, b, out + offset, B200GEMM_OUT_F32, B200GEMM_STORE, 1);
+  }
+  int f32_store_batched(void* stream, const Operand& a, const Operand& b, float* out, int experts) const {
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_STORE, experts);
+  }
+  int f32_store_transposed(void* stream, Operand a, Operand b, float* out) const {
+    a.layout = b.layout = B200GEMM_MN_MAJOR;
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_STORE, 1);
+  }
+
+  // ---- fp32 output, accumulate (copy-engine reduce-add) ----------------------
+  int f32_accumulate(void* stream, const Operand& a, const Operand& b, float* out) const {
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_ACCUMULATE, 1);
+  }
+  int f32_accumulate_at(void* stream, const Operand& a, const Operand& b, float* out, size_t offset) const {
+    return run(stream, a, b, out + offset, B200GEMM_OUT_F32, B200GEMM_ACCUMULATE, 1);
+  }
+  int f32_accumulate_transposed(void* stream, Operand a, Operand b, float* out) const {
+    a.layout = b.layout = B200GEMM_MN_MAJOR;
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_ACCUMULATE, 1);
+  }
+  int f32_accumulate_transposed_at(void* stream, Operand a, Operand b, float* out, size_t offset) const {
+    return f32_accumulate_transposed(stream, a, b, out + offset);
+  }
+  int f32_accumulate_transposed_batched(void* stream, Operand a, Operand b, float* out, int experts) const {
+    a.layout = b.layout = B200GEMM_MN_MAJOR;
+    return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_ACCUMULATE, experts);
+  }
+
+  /// Output row stride (elements) for the next calls; 0 = dense.  Lets a GEMM
+  /// write one column block of a wider matrix (the grouped QKV projections,
+  /// gpu/model/src/lib.rs:1379-1562).
+  void set_ldc(int64_t ldc, int64_t batch_stride_c = 0) { ldc_ = ldc; bsc_ = batch_stride_c; }
+  /// 0 = let the library choose, 1 = never split, n = n slices (fp32 output only).
+  void set_split_k(int split_k) { split_k_ = split_k; }
+
+ private:
+  int run(void* stream, const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,
+          b200gemm_mode_t mode, int experts) const {
+    b200gemm_desc_t d{};
+    d.a = a.ptr; d.b = b.ptr; d.c = out;
+    d.m = a.rows; d.n = b.rows; d.k = a.k;
+    d.lda = a.ld; d.ldb = b.ld; d.ldc = ldc_;
+    d.a_layout = a.layout; d.b_layout = b.layout;
+    d.out_type = out_type; d.mode = mode;
+    d.batch = experts; d.split_k = split_k_;
+    d.batch_stride_a = a.batch_stride; d.batch_stride_b = b.batch_stride; d.batch_stride_c = bsc_;
+    if (a.k != b.k) return B200GEMM_ERR_SHAPE;
+    return b200gemm_gemm(h_, stream, &d);
+  }
+
+  b200gemm_handle_t h_ = nullptr;
+  int64_t ldc_ = 0, bsc_ = 0;
+  int split_k_ = 0;
+};
+
+}  // namespace b200gemm
+#endif  // B200GEMM_HPP_
