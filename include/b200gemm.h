@@ -145,6 +145,55 @@ B200GEMM_API int b200gemm_transpose_bf16(b200gemm_handle_t h, void* stream, cons
  */
 B200GEMM_API int b200gemm_gemm_host(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
 
+/*
+ * lm-head GEMM fused with the softmax cross-entropy classifier.
+ *
+ * Replaces, in the reference, GpuBf16Head::forward_into + cross_entropy_into
+ * (gpu/model/src/lib.rs:3076-3096, 6977-7013: a bf16 `store` of the [m, v]
+ * logits followed by fused_classifier_forward_bf16 and loss_mean_with_aux,
+ * gpu/ops/src/lib.rs:1721-1829, 2852-2904).  Here the logits
+ *     logits[m, v] = hidden[m, k] . W
+ * live only in tensor memory: the GEMM's epilogue keeps a running (max,
+ * sum-exp) per row, so the [m, v] matrix is never written to HBM.
+ *
+ *   hidden    device bf16 [m, k], row stride k
+ *   weight    device bf16; w_layout == B200GEMM_MN_MAJOR: stored [k, v] (the
+ *             reference's [IN, OUT] master), == B200GEMM_K_MAJOR: stored [v, k]
+ *   targets   device int32 [m], each in [0, classes)
+ *   v         padded vocabulary (row stride of a [k, v] weight); columns at or
+ *             beyond `classes` are ignored (gpu/ops/src/lib.rs:1721-1829)
+ *   lse       device fp32 [m] out: max + ln(sum exp) per row (input of backward)
+ *   row_loss  device fp32 [m] out, may be NULL: lse - logit[target]
+ *   loss      device fp32 [1] out, may be NULL: mean of row_loss (f64 row sum)
+ *   workspace device scratch of at least b200gemm_lmhead_ce_workspace_bytes(m)
+ *             bytes, 256-byte aligned; contents need not be preserved between calls
+ */
+B200GEMM_API size_t b200gemm_lmhead_ce_workspace_bytes(int64_t m);
+B200GEMM_API int b200gemm_lmhead_ce_forward(b200gemm_handle_t h, void* stream, const void* hidden,
+                                            const void* weight, int32_t w_layout,
+                                            const int32_t* targets, int64_t m, int64_t k, int64_t v,
+                                            int64_t classes, float* lse, float* row_loss,
+                                            float* loss, void* workspace, size_t workspace_bytes);
+
+/*
+ * Backward of the above (reference: fused_classifier_backward_in_place_bf16 +
+ * GpuBf16Head::backward_weight / backward_input, gpu/ops/src/lib.rs:1843-2001,
+ * gpu/model/src/lib.rs:3103-3145, 5750-5784).  The logits are recomputed tile
+ * by tile and turned in the GEMM's epilogue into
+ *     dlogits = (dy / m) * (exp(logit - lse) - onehot(target)),  0 in padded columns
+ * written once as bf16 [m, v] (`dlogits`, caller-provided); then
+ *     d_hidden[m, k] (fp32)  =  dlogits . W^T
+ *     d_weight (fp32, same shape as W)  (=|+=)  hidden^T . dlogits
+ * `accumulate_dw` != 0 adds into d_weight.  `d_hidden` or `d_weight` may be NULL
+ * to skip that product.
+ */
+B200GEMM_API int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, const void* hidden,
+                                             const void* weight, int32_t w_layout,
+                                             const int32_t* targets, const float* lse, float dy,
+                                             int64_t m, int64_t k, int64_t v, int64_t classes,
+                                             void* dlogits_bf16, float* d_hidden, float* d_weight,
+                                             int32_t accumulate_dw);
+
 /* Synchronises `stream`, reads and clears the device status word; returns
  * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
  * *device_code (may be NULL).  The reference has no counterpart: its kernels

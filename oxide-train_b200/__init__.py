@@ -6,5 +6,6 @@ done by ``libb200gemm.so`` (hand-written CUDA, built from ``csrc/``).
 from . import _lib
 from ._lib import B200GemmError, GemmDesc
 from .gemm import Tcgen05Gemm
+from .lmhead import FusedLmHead
 
-__all__ = ["Tcgen05Gemm", "B200GemmError", "GemmDesc", "_lib"]
+__all__ = ["Tcgen05Gemm", "FusedLmHead", "B200GemmError", "GemmDesc", "_lib"]

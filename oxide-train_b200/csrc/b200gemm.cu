@@ -14,6 +14,7 @@
 
 #include "../../include/b200gemm.h"
 #include "aux_kernels.cuh"
+#include "ce_kernels.cuh"
 #include "gemm_kernel.cuh"
 
 namespace {
@@ -56,7 +57,7 @@ struct b200gemm_context {
   // staging for b200gemm_gemm_host
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
-  bool smem_opt_in[2][3] = {{false, false, false}, {false, false, false}};
+  bool smem_opt_in[2][8] = {};   // [cta_group - 1][epilogue kind]
   std::mutex mu;
 };
 
@@ -193,10 +194,9 @@ int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
   return B200GEMM_OK;
 }
 
-template <int CG, int EPI>
-int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan,
-               cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<CG, EPI>;
+template <int CG, int EPI, int SCHED>
+int launch_kernel(b200gemm_context* ctx, const GemmParams& params, int grid, cudaStream_t stream) {
+  auto kernel = gemm_tcgen05_kernel<CG, EPI, SCHED>;
   // Per-device opt-in to > 48 KiB dynamic shared memory, once per kernel
   // (the reference's opt_in_dynamic_smem, host.rs:485-505).
   bool& ready = ctx->smem_opt_in[CG - 1][EPI];
@@ -206,7 +206,7 @@ int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan
     ready = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(plan.grid, 1, 1);
+  cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = GemmCfg<CG>::kSmemBytes;
   cfg.stream = stream;
@@ -219,6 +219,12 @@ int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan
   cfg.numAttrs = 1;
   CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, params));
   return B200GEMM_OK;
+}
+
+template <int CG, int EPI>
+int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan,
+               cudaStream_t stream) {
+  return launch_kernel<CG, EPI, kSchedDense>(ctx, params, plan.grid, stream);
 }
 
 int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_t* d) {
@@ -281,6 +287,178 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
     case kEpiBf16Tma: return launch_one<2, kEpiBf16Tma>(ctx, params, plan, stream);
     default: return launch_one<2, kEpiBf16Rmw>(ctx, params, plan, stream);
   }
+}
+
+
+// ---------------------------------------------------------------- lm-head + cross entropy
+
+constexpr int kCeMaxChunks = 8;
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct CeWorkspace {
+  CeAccum* accum;
+  float* target_logit;
+  float2* partials;
+};
+
+size_t ce_workspace_bytes(int64_t m) {
+  return 256 + align_up(static_cast<size_t>(m) * sizeof(float), 256) +
+         static_cast<size_t>(kCeMaxChunks) * m * sizeof(float2);
+}
+
+CeWorkspace ce_carve(void* ws, int64_t m) {
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  CeWorkspace w;
+  w.accum = reinterpret_cast<CeAccum*>(p);
+  w.target_logit = reinterpret_cast<float*>(p + 256);
+  w.partials = reinterpret_cast<float2*>(p + 256 + align_up(static_cast<size_t>(m) * sizeof(float), 256));
+  return w;
+}
+
+int ce_check(const void* hidden, const void* weight, int32_t w_layout, const int32_t* targets,
+             int64_t m, int64_t k, int64_t v, int64_t classes) {
+  if (!hidden || !weight || !targets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (w_layout < 0 || w_layout > 1) return fail(B200GEMM_ERR_INVALID, "bad weight layout");
+  if (m <= 0 || k <= 0 || v <= 0 || classes <= 0 || classes > v)
+    return fail(B200GEMM_ERR_SHAPE, "need m, k, v > 0 and 0 < classes <= v");
+  if (m > (1ll << 30) || k > (1ll << 30) || v > (1ll << 30)) return fail(B200GEMM_ERR_SHAPE, "extent too large");
+  if ((k % 8) != 0 || (v % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "k and v must be multiples of 8 (16-byte rows)");
+  return B200GEMM_OK;
+}
+
+// Operand maps of logits = hidden . W for a CTA-pair launch.
+int ce_encode_operands(b200gemm_context* ctx, GemmParams* params, const void* hidden,
+                       const void* weight, int32_t w_layout, int64_t m, int64_t k, int64_t v) {
+  const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int rc = encode_map(ctx, &params->map_a, bf16, 2, hidden, k, m, 1, k, 0, 64, kTileMCta, "hidden");
+  if (rc) return rc;
+  if (w_layout == B200GEMM_MN_MAJOR)   // stored [k, v]
+    rc = encode_map(ctx, &params->map_b, bf16, 2, weight, v, k, 1, v, 0, 64, 64, "weight");
+  else                                  // stored [v, k]
+    rc = encode_map(ctx, &params->map_b, bf16, 2, weight, k, v, 1, k, 0, 64, kTileN / 2, "weight");
+  params->a_mn = 0;
+  params->b_mn = w_layout == B200GEMM_MN_MAJOR;
+  return rc;
+}
+
+int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, const void* weight,
+               int32_t w_layout, const int32_t* targets, int64_t m, int64_t k, int64_t v,
+               int64_t classes, float* lse, float* row_loss, float* loss, void* workspace,
+               size_t workspace_bytes) {
+  int rc = ce_check(hidden, weight, w_layout, targets, m, k, v, classes);
+  if (rc) return rc;
+  if (!lse) return fail(B200GEMM_ERR_INVALID, "lse output is required");
+  if (!workspace || workspace_bytes < ce_workspace_bytes(m) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return fail(B200GEMM_ERR_INVALID, "workspace missing, too small (%zu needed) or not 256-byte aligned",
+                ce_workspace_bytes(m));
+  const CeWorkspace ws = ce_carve(workspace, m);
+  GemmParams params;
+  memset(&params, 0, sizeof(params));
+  rc = ce_encode_operands(ctx, &params, hidden, weight, w_layout, m, k, v);
+  if (rc) return rc;
+  params.status = ctx->status;
+  params.m = static_cast<int>(m);
+  params.n = static_cast<int>(v);
+  params.tiles_m = ceil_div(m, 2 * kTileMCta);
+  params.tiles_n = ceil_div(classes, kTileN);    // tiles that are all padding are never computed
+  params.batch = 1;
+  params.k_blocks = ceil_div(k, kBlockK);
+  params.split_k = 1;
+  params.kb_per_split = params.k_blocks;
+  params.targets = targets;
+  params.ce_partials = ws.partials;
+  params.ce_target_logit = ws.target_logit;
+  params.ce_classes = static_cast<int>(classes);
+  // Vocabulary chunks: enough (row block, chunk) items to fill the last wave
+  // of the persistent clusters, few enough that the merge stays negligible.
+  const int units = std::max(1, ctx->sm_count / 2);
+  int best = 1;
+  double best_eff = 0.0;
+  for (int c = 1; c <= std::min(kCeMaxChunks, params.tiles_n); ++c) {
+    const int64_t items = static_cast<int64_t>(params.tiles_m) * c;
+    const double eff = static_cast<double>(items) / (static_cast<double>((items + units - 1) / units) * units);
+    if (eff > best_eff + 0.01) {
+      best_eff = eff;
+      best = c;
+    }
+  }
+  params.ce_chunks = best;
+  const int64_t items = static_cast<int64_t>(params.tiles_m) * params.ce_chunks;
+  const int grid = static_cast<int>(std::min<int64_t>(items, units)) * 2;
+  CUDA_TRY(cudaMemsetAsync(ws.accum, 0, sizeof(CeAccum), stream));
+  rc = launch_kernel<2, kEpiCeForward, kSchedCeForward>(ctx, params, grid, stream);
+  if (rc) return rc;
+  const int blocks = static_cast<int>(std::min<int64_t>((m + 255) / 256, ctx->sm_count * 4));
+  ce_combine_kernel<<<blocks, 256, 0, stream>>>(ws.partials, ws.target_logit, static_cast<int>(m),
+                                                params.ce_chunks, lse, row_loss, loss, ws.accum);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int ce_backward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, const void* weight,
+                int32_t w_layout, const int32_t* targets, const float* lse, float dy, int64_t m,
+                int64_t k, int64_t v, int64_t classes, void* dlogits, float* d_hidden,
+                float* d_weight, int32_t accumulate_dw) {
+  int rc = ce_check(hidden, weight, w_layout, targets, m, k, v, classes);
+  if (rc) return rc;
+  if (!lse || !dlogits) return fail(B200GEMM_ERR_INVALID, "lse and dlogits are required");
+  // 1. recompute the logits tile by tile; the epilogue writes dlogits (bf16).
+  GemmParams params;
+  memset(&params, 0, sizeof(params));
+  rc = ce_encode_operands(ctx, &params, hidden, weight, w_layout, m, k, v);
+  if (rc) return rc;
+  rc = encode_map(ctx, &params.map_c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dlogits, v, m, 1, v, 0, 64, 32, "dlogits");
+  if (rc) return rc;
+  params.status = ctx->status;
+  params.m = static_cast<int>(m);
+  params.n = static_cast<int>(v);
+  params.tiles_m = ceil_div(m, 2 * kTileMCta);
+  params.tiles_n = ceil_div(v, kTileN);           // padded columns are written as zeros
+  params.batch = 1;
+  params.k_blocks = ceil_div(k, kBlockK);
+  params.split_k = 1;
+  params.kb_per_split = params.k_blocks;
+  params.targets = targets;
+  params.ce_lse = lse;
+  params.ce_scale = dy / static_cast<float>(m);
+  params.ce_classes = static_cast<int>(classes);
+  const int units = std::max(1, ctx->sm_count / 2);
+  const int64_t items = static_cast<int64_t>(params.tiles_m) * params.tiles_n;
+  const int grid = static_cast<int>(std::min<int64_t>(items, units)) * 2;
+  rc = launch_kernel<2, kEpiCeBackward, kSchedDense>(ctx, params, grid, stream);
+  if (rc) return rc;
+  // 2. d_hidden[m, k] = dlogits[m, v] . W^T
+  if (d_hidden) {
+    b200gemm_desc_t d;
+    memset(&d, 0, sizeof(d));
+    d.a = dlogits; d.b = weight; d.c = d_hidden;
+    d.m = m; d.n = k; d.k = v;
+    d.a_layout = B200GEMM_K_MAJOR;
+    // W stored [k, v] is B[n = k, K = v] K-major; stored [v, k] it is MN-major.
+    d.b_layout = w_layout == B200GEMM_MN_MAJOR ? B200GEMM_K_MAJOR : B200GEMM_MN_MAJOR;
+    d.out_type = B200GEMM_OUT_F32; d.mode = B200GEMM_STORE; d.batch = 1;
+    rc = launch_gemm(ctx, stream, &d);
+    if (rc) return rc;
+  }
+  // 3. d_weight (=|+=) hidden^T . dlogits, in the weight's own orientation
+  if (d_weight) {
+    b200gemm_desc_t d;
+    memset(&d, 0, sizeof(d));
+    d.a_layout = d.b_layout = B200GEMM_MN_MAJOR;   // both operands are [K = m rows, ...]
+    d.k = m;
+    if (w_layout == B200GEMM_MN_MAJOR) { d.a = hidden; d.b = dlogits; d.m = k; d.n = v; }
+    else { d.a = dlogits; d.b = hidden; d.m = v; d.n = k; }
+    d.c = d_weight;
+    d.out_type = B200GEMM_OUT_F32;
+    d.mode = accumulate_dw ? B200GEMM_ACCUMULATE : B200GEMM_STORE;
+    d.batch = 1;
+    rc = launch_gemm(ctx, stream, &d);
+    if (rc) return rc;
+  }
+  return B200GEMM_OK;
 }
 
 int check_handle(b200gemm_handle_t h) {
@@ -418,6 +596,30 @@ int b200gemm_transpose_bf16(b200gemm_handle_t h, void* stream, const void* src, 
                                  static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst),
                                  static_cast<int>(rows), static_cast<int>(cols)));
   return B200GEMM_OK;
+}
+
+size_t b200gemm_lmhead_ce_workspace_bytes(int64_t m) { return m > 0 ? ce_workspace_bytes(m) : 0; }
+
+int b200gemm_lmhead_ce_forward(b200gemm_handle_t h, void* stream, const void* hidden,
+                               const void* weight, int32_t w_layout, const int32_t* targets,
+                               int64_t m, int64_t k, int64_t v, int64_t classes, float* lse,
+                               float* row_loss, float* loss, void* workspace,
+                               size_t workspace_bytes) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  return ce_forward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, m, k, v,
+                    classes, lse, row_loss, loss, workspace, workspace_bytes);
+}
+
+int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, const void* hidden,
+                                const void* weight, int32_t w_layout, const int32_t* targets,
+                                const float* lse, float dy, int64_t m, int64_t k, int64_t v,
+                                int64_t classes, void* dlogits_bf16, float* d_hidden,
+                                float* d_weight, int32_t accumulate_dw) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  return ce_backward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, lse, dy,
+                     m, k, v, classes, dlogits_bf16, d_hidden, d_weight, accumulate_dw);
 }
 
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {

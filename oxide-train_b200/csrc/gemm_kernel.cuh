@@ -23,9 +23,17 @@
 // [IN, OUT] weight read as B).  The layout only changes the TMA boxes and two
 // descriptor fields, so it is a runtime parameter.
 //
-// The accumulator ping-pong lets the MMA of work item i+1 overlap the drain of
-// item i.  Work items are (batch, tile_m, tile_n, k_split) tuples handed out
-// round-robin to the persistent CTAs/clusters in a grouped raster order.
+// The accumulator ping-pong lets the MMA of tile i+1 overlap the drain of tile
+// i.  Tiles are handed out to the persistent CTAs/clusters by one of three
+// schedules (template parameter kSched):
+//   kSchedDense     (batch, tile_m, tile_n, k_slice) items, grouped raster order
+//   kSchedCeForward (row block, vocabulary chunk) items, each a run of
+//                   consecutive column tiles whose epilogue carries the running
+//                   softmax statistics of its rows
+//   kSchedGrouped   variable-length row groups (experts) found through a
+//                   device-side offsets array
+//
+// Epilogues (template parameter kEpi) are listed at EpilogueKind.
 #pragma once
 
 #include "ptx.cuh"
@@ -61,12 +69,18 @@ constexpr int kTmemCols = 512;    // two 256-column fp32 accumulators
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 B, one per epilogue warp per buffer
 constexpr int kRasterGroupM = 8;  // tile rows walked together so B panels stay in L2
 constexpr int kSubtileBytes = 64 * kBlockK * 2;  // one 64(mn) x 64(k) MN-major box
+constexpr int kMaxGroups = 256;   // experts a grouped launch can address
 
 enum EpilogueKind : int {
   kEpiF32Tma = 0,       // fp32 C through TMA: store, or reduce-add when p.reduce != 0
   kEpiBf16Tma = 1,      // bf16 C through TMA store
   kEpiBf16Rmw = 2,      // bf16 C += acc: read C, add in fp32, round once, write
+  kEpiCeForward = 3,    // no C: per-row running (max, sum-exp) and the target's logit
+  kEpiCeBackward = 4,   // bf16 C = scale * (exp(acc - lse[row]) - [col == target[row]]), padding = 0
+  kEpiBf16Grouped = 5,  // bf16 C for ragged row groups, optional SiLU; rows past the group are not written
 };
+
+enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2 };
 
 template <int kCtaGroup>
 struct GemmCfg {
@@ -87,49 +101,132 @@ struct GemmParams {
   CUtensorMap map_b;   // K-major: box {64, 256 / cta_group, 1}; MN-major: box {64, 64, 1}
   CUtensorMap map_c;   // {N, M, batch} box {32 (fp32) | 64 (bf16), 32, 1}, 128-byte swizzle
   int* status;         // device status word, 0 = ok
-  uint16_t* c_bf16;    // only for kEpiBf16Rmw
-  long long ldc;       // elements, only for kEpiBf16Rmw
+  uint16_t* c_bf16;    // direct-store epilogues (kEpiBf16Rmw, kEpiBf16Grouped)
+  long long ldc;       // elements, direct-store epilogues
   long long batch_stride_c;
-  int m, n;            // logical extents (for the read-modify-write epilogue's bounds)
+  int m, n;            // logical extents (bounds of the direct-store epilogues)
   int tiles_m, tiles_n, batch;
   int k_blocks;        // ceil(K / 64)
   int split_k;         // >= 1
   int kb_per_split;    // ceil(k_blocks / split_k); every split is non-empty
   int a_mn, b_mn;      // 1 = MN-major
   int reduce;          // kEpiF32Tma: 1 = reduce-add into C
+  // ---- cross-entropy epilogues
+  const int* targets;  // [m] class index per row
+  float2* ce_partials; // kEpiCeForward: [ce_chunks][m] running (max, sum-exp) per vocabulary chunk
+  float* ce_target_logit;  // kEpiCeForward: [m], written by the chunk that holds the target column
+  const float* ce_lse; // kEpiCeBackward: [m] log-sum-exp per row
+  float ce_scale;      // kEpiCeBackward: upstream gradient / rows
+  int ce_classes;      // columns at or beyond this index are padding
+  int ce_chunks;       // kSchedCeForward: vocabulary chunks per row block
+  // ---- grouped (ragged) rows
+  const int* group_offsets;  // [groups + 1] first row of each group; rows of group g use B[g]
+  int groups;
+  int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
 #ifdef B200_PROBE
   long long* probe;
 #endif
 };
 
-struct WorkItem {
-  int batch, tile_m, tile_n, kb_begin, kb_count;
+struct Tile {
+  int batch;       // index into the batch / expert dimension of B (and of A, C when dense)
+  int m0;          // first output row of the CLUSTER's tile
+  int m_end;       // rows at or beyond this are outside the tile's group (grouped schedule)
+  int tile_n;
+  int kb_begin, kb_count;
+  int first, last;  // position inside a kSchedCeForward run
 };
 
-__device__ __forceinline__ WorkItem decode_item(const GemmParams& p, int item) {
-  WorkItem w;
-  int split = item % p.split_k;
-  int t = item / p.split_k;
-  int tiles = p.tiles_m * p.tiles_n;
-  w.batch = t / tiles;
-  t -= w.batch * tiles;
-  int per_group = kRasterGroupM * p.tiles_n;
-  int group = t / per_group;
-  int first_m = group * kRasterGroupM;
-  int group_rows = min(p.tiles_m - first_m, kRasterGroupM);
-  int in_group = t - group * per_group;
-  w.tile_m = first_m + in_group % group_rows;
-  w.tile_n = in_group / group_rows;
-  w.kb_begin = split * p.kb_per_split;
-  w.kb_count = min(p.kb_per_split, p.k_blocks - w.kb_begin);
-  return w;
+// Iterates the tiles of one CTA/cluster.  All three roles run the same
+// iterator, so they agree on the order without talking to each other.
+template <int kSched, int kTileM>
+struct TileWalk {
+  const GemmParams& p;
+  const int* group_tile_start;   // shared memory, kSchedGrouped: [groups + 1] first m-tile of each group
+  int item, inner, step;
+
+  __device__ TileWalk(const GemmParams& p_, const int* gts, int cluster_id, int num_clusters)
+      : p(p_), group_tile_start(gts), item(cluster_id), inner(0), step(num_clusters) {}
+
+  __device__ int total_items() const {
+    if constexpr (kSched == kSchedDense) return p.batch * p.tiles_m * p.tiles_n * p.split_k;
+    else if constexpr (kSched == kSchedCeForward) return p.tiles_m * p.ce_chunks;
+    else return group_tile_start[p.groups] * p.tiles_n;
+  }
+
+  __device__ bool get(Tile& t) const {
+    if (item >= total_items()) return false;
+    t.first = 1;
+    t.last = 1;
+    t.kb_begin = 0;
+    t.kb_count = p.k_blocks;
+    t.m_end = p.m;
+    if constexpr (kSched == kSchedDense) {
+      int split = item % p.split_k;
+      int r = item / p.split_k;
+      int tiles = p.tiles_m * p.tiles_n;
+      t.batch = r / tiles;
+      r -= t.batch * tiles;
+      int per_group = kRasterGroupM * p.tiles_n;
+      int group = r / per_group;
+      int first_m = group * kRasterGroupM;
+      int group_rows = min(p.tiles_m - first_m, kRasterGroupM);
+      int in_group = r - group * per_group;
+      t.m0 = (first_m + in_group % group_rows) * kTileM;
+      t.tile_n = in_group / group_rows;
+      t.kb_begin = split * p.kb_per_split;
+      t.kb_count = min(p.kb_per_split, p.k_blocks - t.kb_begin);
+    } else if constexpr (kSched == kSchedCeForward) {
+      // Row blocks vary fastest, so the clusters running side by side walk the
+      // same vocabulary chunk (shared W tiles in L2) on different rows.
+      int chunk = item / p.tiles_m;
+      int row_block = item - chunk * p.tiles_m;
+      int base = p.tiles_n / p.ce_chunks, rem = p.tiles_n % p.ce_chunks;
+      int first_tile = chunk * base + min(chunk, rem);
+      int count = base + (chunk < rem ? 1 : 0);
+      t.batch = 0;
+      t.m0 = row_block * kTileM;
+      t.tile_n = first_tile + inner;
+      t.first = inner == 0;
+      t.last = inner == count - 1;
+    } else {
+      // item -> (m-tile over all groups, n-tile); n varies slowest so that the
+      // clusters running together share few B panels.
+      int total_m = group_tile_start[p.groups];
+      int tn = item / total_m;
+      int tm = item - tn * total_m;
+      int g = 0;
+      while (g + 1 < p.groups && group_tile_start[g + 1] <= tm) ++g;
+      t.batch = g;
+      t.m0 = p.group_offsets[g] + (tm - group_tile_start[g]) * kTileM;
+      t.m_end = p.group_offsets[g + 1];
+      t.tile_n = tn;
+    }
+    return true;
+  }
+
+  __device__ void next(const Tile& t) {
+    if constexpr (kSched == kSchedCeForward) {
+      if (!t.last) { ++inner; return; }
+      inner = 0;
+    }
+    item += step;
+  }
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
-template <int kCtaGroup, int kEpi>
+template <int kCtaGroup, int kEpi, int kSched>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<kCtaGroup>;
+  using Walk = TileWalk<kSched, Cfg::kTileM>;
   extern __shared__ uint8_t smem_raw[];
+  __shared__ int group_tile_start[kSched == kSchedGrouped ? kMaxGroups + 1 : 1];
 
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
@@ -150,7 +247,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t cta_rank = kCtaGroup == 2 ? cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
-  const int total_items = p.batch * p.tiles_m * p.tiles_n * p.split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -165,7 +261,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     fence_mbar_init();
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
-    if (kEpi != kEpiBf16Rmw) prefetch_tensormap(&p.map_c);
+    if (kEpi == kEpiF32Tma || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || kEpi == kEpiBf16Grouped)
+      prefetch_tensormap(&p.map_c);
+  }
+  if constexpr (kSched == kSchedGrouped) {
+    // Every CTA derives the same tile table from the offsets array.
+    if (warp == 3 && lane == 0) {
+      int run = 0;
+      for (int g = 0; g < p.groups; ++g) {
+        group_tile_start[g] = run;
+        int rows = p.group_offsets[g + 1] - p.group_offsets[g];
+        run += (max(rows, 0) + Cfg::kTileM - 1) / Cfg::kTileM;
+      }
+      group_tile_start[p.groups] = run;
+    }
   }
   if (warp == 2) {
     tmem_alloc<kCtaGroup>(smem_u32(tmem_slot), kTmemCols);
@@ -183,14 +292,16 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // the tensor cores consume one.
     if (lane == 0) {
       const uint32_t which = warp == 0 ? 0u : 1u;
-      uint32_t g = 0;   // K blocks seen so far, over all of this CTA's work items
+      uint32_t g = 0;   // K blocks seen so far, over all of this CTA's tiles
       bool ok = true;
       PROBE_DECL_IF(which == 0)
-      for (int item = cluster_id; ok && item < total_items; item += num_clusters) {
-        const WorkItem w = decode_item(p, item);
-        const int m0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta;
-        const int n0 = w.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
-        for (int kb = w.kb_begin; kb < w.kb_begin + w.kb_count; ++kb, ++g) {
+      Walk walk(p, group_tile_start, cluster_id, num_clusters);
+      Tile t;
+      for (; ok && walk.get(t); walk.next(t)) {
+        const int m0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta;
+        const int n0 = t.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
+        const int a_batch = kSched == kSchedGrouped ? 0 : t.batch;   // grouped A is one [rows, K] matrix
+        for (int kb = t.kb_begin; kb < t.kb_begin + t.kb_count; ++kb, ++g) {
           if ((g & 1u) != which) continue;
           const uint32_t stage = g % Cfg::kStages;
           const uint32_t phase = (g / Cfg::kStages) & 1u;
@@ -206,18 +317,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           const int k0 = kb * kBlockK;
           if (!p.a_mn) {
-            tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, w.batch);
+            tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, a_batch);
           } else {
 #pragma unroll
             for (int i = 0; i < kTileMCta / 64; ++i)
-              tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, w.batch);
+              tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
           }
           if (!p.b_mn) {
-            tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, w.batch);
+            tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, t.batch);
           } else {
 #pragma unroll
             for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
-              tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, w.batch);
+              tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, t.batch);
           }
           PROBE_ADD(1);
         }
@@ -236,8 +347,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       int it = 0;
       bool ok = true;
       PROBE_DECL
-      for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
-        const WorkItem w = decode_item(p, item);
+      Walk walk(p, group_tile_start, cluster_id, num_clusters);
+      Tile t;
+      for (; ok && walk.get(t); walk.next(t), ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag)) {
@@ -247,7 +359,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         PROBE_ADD(2);
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < w.kb_count; ++kb) {
+        for (int kb = 0; kb < t.kb_count; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag)) {
             ok = false;
             break;
@@ -278,9 +390,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     uint32_t chunk_counter = 0;
     int it = 0;
     bool ok = true;
+    // kEpiCeForward: running statistics of this thread's row over a chunk of the vocabulary.
+    float run_max = -INFINITY, run_sum = 0.f, target_logit = 0.f;
+    bool have_target = false;
+    constexpr float kLog2e = 1.4426950408889634f;
     PROBE_DECL_IF(warp == 2 && lane == 0)
-    for (int item = cluster_id; ok && item < total_items; item += num_clusters, ++it) {
-      const WorkItem w = decode_item(p, item);
+    Walk walk(p, group_tile_start, cluster_id, num_clusters);
+    Tile t;
+    for (; ok && walk.get(t); walk.next(t), ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.status, kDevTimeoutEpilogue, abort_flag)) {
@@ -289,8 +406,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       }
       PROBE_ADD(5);
       tcgen05_fence_after_sync();
-      const int row0 = w.tile_m * Cfg::kTileM + static_cast<int>(cta_rank) * kTileMCta + lane_base;
-      const int col0 = w.tile_n * kTileN;
+      const int row0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta + lane_base;   // warp's first row
+      const int col0 = t.tile_n * kTileN;
       const uint32_t t_acc = tmem_base + (lane_base << 16) + acc * kTileN;
 
       auto release_accumulator = [&]() {
@@ -299,6 +416,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         if (lane == 0) {
           if constexpr (kCtaGroup == 2) mbar_arrive_cluster(map_to_cta(tmem_empty_bar(acc), 0));
           else mbar_arrive(tmem_empty_bar(acc));
+        }
+      };
+      // Write 32 rows x 128 bytes (this thread's 8 x 16 bytes) into a staging
+      // buffer with the 128-byte swizzle the C tensor map expects.
+      auto stage_row = [&](uint32_t buf, const uint32_t* v) {
+        const uint32_t row_addr = buf + lane * 128u;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t dst = row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * j]),
+                       "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                       : "memory");
         }
       };
 
@@ -315,27 +444,34 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           if (lane == 0) tma_wait_group_read<1>();   // the store that last read this buffer is done
           __syncwarp();
           PROBE_ADD(7);
-          const uint32_t row_addr = buf + lane * 128u;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t dst = row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(r[4 * j]),
-                         "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
-                         : "memory");
-          }
+          stage_row(buf, r);
           fence_proxy_async_smem();
           __syncwarp();
           PROBE_ADD(8);
           if (lane == 0) {
-            if (p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
-            else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, w.batch);
+            if (p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
+            else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
             tma_commit_group();
           }
           PROBE_ADD(9);
           ++chunk_counter;
         }
-      } else if constexpr (kEpi == kEpiBf16Tma) {
+      } else if constexpr (kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || kEpi == kEpiBf16Grouped) {
         constexpr int kChunks = kTileN / 64;
+        const int row = row0 + lane;
+        // kEpiCeBackward: p = exp(logit - lse) computed as exp2(logit*log2e - lse*log2e).
+        float neg_lse2 = 0.f;
+        int target = -1;
+        if constexpr (kEpi == kEpiCeBackward) {
+          if (row < p.m) {
+            neg_lse2 = -p.ce_lse[row] * kLog2e;
+            target = p.targets[row];
+          }
+        }
+        // kEpiBf16Grouped: a warp whose 32 rows all belong to the group uses the
+        // TMA store; a warp that straddles the group's end writes row by row.
+        bool warp_inside = true;
+        if constexpr (kEpi == kEpiBf16Grouped) warp_inside = row0 + 32 <= t.m_end;
 #pragma unroll 1
         for (int c = 0; c < kChunks; ++c) {
           uint32_t packed[32];
@@ -344,35 +480,105 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * 64 + h * 32, r);
             tmem_ld_wait();
+            if constexpr (kEpi == kEpiCeBackward) {
+              const int cbase = col0 + c * 64 + h * 32;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int col = cbase + j;
+                float g = p.ce_scale * fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, neg_lse2));
+                if (col == target) g -= p.ce_scale;
+                if (col >= p.ce_classes) g = 0.f;
+                r[j] = __float_as_uint(g);
+              }
+            }
+            if constexpr (kEpi == kEpiBf16Grouped) {
+              if (p.act_silu) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const float x = __uint_as_float(r[j]);
+                  r[j] = __float_as_uint(x / (1.f + fast_exp2(-x * kLog2e)));
+                }
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               packed[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           }
           if (c == kChunks - 1) release_accumulator();
-          const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
-          if (lane == 0) tma_wait_group_read<1>();
-          __syncwarp();
-          const uint32_t row_addr = buf + lane * 128u;
+          if (warp_inside) {
+            const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+            if (lane == 0) tma_wait_group_read<1>();
+            __syncwarp();
+            stage_row(buf, packed);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&p.map_c, buf, col0 + c * 64, row0, kSched == kSchedGrouped ? 0 : t.batch);
+              tma_commit_group();
+            }
+            ++chunk_counter;
+          } else if (row < t.m_end) {
+            uint16_t* crow = p.c_bf16 + static_cast<long long>(row) * p.ldc;
+            const int col = col0 + c * 64;
+            if (col + 64 <= p.n) {
+              uint4* ptr = reinterpret_cast<uint4*>(crow + col);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t dst = row_addr + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * j]),
-                         "r"(packed[4 * j + 1]), "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
-                         : "memory");
+              for (int q = 0; q < 8; ++q)
+                ptr[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 64 && col + j < p.n; ++j)
+                crow[col + j] = static_cast<uint16_t>((packed[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+            }
           }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_3d(&p.map_c, buf, col0 + c * 64, row0, w.batch);
-            tma_commit_group();
-          }
-          ++chunk_counter;
         }
-      } else {
-        // bf16 read-modify-write: thread = row, 32 columns (64 bytes) at a time.
+      } else if constexpr (kEpi == kEpiCeForward) {
+        // Online softmax over this tile's 256 columns of the thread's row.
         constexpr int kChunks = kTileN / 32;
         const int row = row0 + lane;
-        uint16_t* crow = p.c_bf16 + static_cast<long long>(w.batch) * p.batch_stride_c +
+        if (t.first) {
+          run_max = -INFINITY;
+          run_sum = 0.f;
+          have_target = false;
+        }
+        const int target = row < p.m ? p.targets[row] : -1;
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          const int cbase = col0 + c * 32;
+          if (cbase >= p.ce_classes) {            // whole chunk is padding (warp-uniform)
+            if (c == kChunks - 1) release_accumulator();
+            continue;
+          }
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (c == kChunks - 1) release_accumulator();
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __uint_as_float(r[j]);
+            if (cbase + j >= p.ce_classes) v = -INFINITY;
+            if (cbase + j == target) { target_logit = v; have_target = true; }
+            r[j] = __float_as_uint(v);
+            cmax = fmaxf(cmax, v);
+          }
+          const float new_max = fmaxf(run_max, cmax);
+          const float m2 = new_max * kLog2e;
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s += fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, -m2));
+          run_sum = run_sum * fast_exp2((run_max - new_max) * kLog2e) + s;
+          run_max = new_max;
+        }
+        if (t.last && row < p.m) {
+          const int chunk = walk.item / p.tiles_m;
+          p.ce_partials[static_cast<long long>(chunk) * p.m + row] = make_float2(run_max, run_sum);
+          if (have_target) p.ce_target_logit[row] = target_logit;
+        }
+      } else {
+        // kEpiBf16Rmw: bf16 read-modify-write, thread = row, 32 columns (64 bytes) at a time.
+        constexpr int kChunks = kTileN / 32;
+        const int row = row0 + lane;
+        uint16_t* crow = p.c_bf16 + static_cast<long long>(t.batch) * p.batch_stride_c +
                          static_cast<long long>(row) * p.ldc;
 #pragma unroll 1
         for (int c = 0; c < kChunks; ++c) {
@@ -407,7 +613,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
-    if (kEpi != kEpiBf16Rmw && lane == 0) tma_wait_group<0>();   // all stores landed before exit
+    if (lane == 0) tma_wait_group<0>();   // all TMA stores of this warp landed before exit
     __syncwarp();
   }
 

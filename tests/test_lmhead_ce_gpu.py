@@ -1,0 +1,109 @@
+"""GPU parity of the fused lm-head + softmax cross-entropy against the CPU oracle.
+
+The oracle path is the reference's CPU one: ``Linear::forward`` (a matmul,
+crates/nn/src/linear.rs:42-44) feeding ``SoftmaxCrossEntropy``
+(crates/nn/src/cross_entropy.rs:28-72), then ``Linear::backward``.  Tolerances
+follow the reference's classifier gate (gpu/ops/src/main.rs:1984-2110: loss
+5e-5, dlogits 4e-3 relative, padded columns exactly zero) and the GEMM contract
+for the two gradient products.
+"""
+import numpy as np
+import pytest
+
+from _util import THREADS, assert_gemm_close, bf16_operand, from_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gemm(pkg):
+    g = pkg.Tcgen05Gemm()
+    yield g
+    g.close()
+
+
+def _oracle_head(oracle, hv, wv_kv, targets, classes):
+    logits = oracle.matmul(hv, wv_kv, THREADS)
+    loss, probs, row_loss = oracle.xent_forward(logits, targets, classes)
+    dlogits = oracle.xent_backward(probs, targets, classes)
+    z = logits[:, :classes].astype(np.float64)
+    lse = np.log(np.exp(z - z.max(1, keepdims=True)).sum(1)) + z.max(1)
+    return logits, loss, row_loss, lse, dlogits
+
+
+@pytest.mark.parametrize("m,k,v,classes", [(512, 256, 1024, 1000), (300, 192, 520, 515), (256, 64, 256, 256)])
+@pytest.mark.parametrize("layout", ["in_out", "out_in"])
+def test_fused_head_matches_oracle(pkg, oracle, gemm, m, k, v, classes, layout):
+    import torch
+    h, hv = bf16_operand(oracle, (m, k), 21)
+    w_kv, wv = bf16_operand(oracle, (k, v), 22, std=0.3)
+    targets = (oracle.uniform(m, 23) * 0.5 + 0.5) * classes
+    targets = np.clip(targets.astype(np.int32), 0, classes - 1)
+    logits, loss, row_loss, lse, dlogits = _oracle_head(oracle, hv, wv, targets, classes)
+    w = w_kv if layout == "in_out" else w_kv.t().contiguous()
+    t = torch.from_numpy(targets).cuda()
+    head = pkg.FusedLmHead(gemm, classes, layout)
+    g_loss, g_lse, g_row = head.forward(h, w, t)
+    assert gemm.device_status() == 0
+    assert abs(float(g_loss.item()) - float(loss)) <= 5e-5 * max(1.0, abs(float(loss)))
+    assert np.allclose(g_lse.cpu().numpy(), lse, atol=2e-4, rtol=1e-5)
+    assert np.allclose(g_row.cpu().numpy(), row_loss, atol=2e-4, rtol=1e-5)
+
+    g_dl, g_dh, g_dw = head.backward(h, w, t, g_lse)
+    assert gemm.device_status() == 0
+    dl = from_dev_bf16(g_dl)
+    assert np.all(dl[:, classes:] == 0.0)                      # padded columns are exactly zero
+    scale = np.abs(dlogits).max()
+    assert np.max(np.abs(dl - dlogits)) <= 4e-3 * scale + 1e-8  # bf16 rounding of the gradient
+    # gradient products, from the dlogits the kernel actually produced (bf16)
+    dh_ref = oracle.matmul_nt(dl, wv, THREADS)                  # dlogits . W^T
+    dw_ref = oracle.matmul_tn(hv, dl, THREADS)                  # hidden^T . dlogits, [k, v]
+    assert_gemm_close(g_dh.cpu().numpy(), dh_ref, "d_hidden", rel_fro=1e-4, elem=1e-3)
+    got_dw = g_dw.cpu().numpy() if layout == "in_out" else g_dw.cpu().numpy().T
+    assert_gemm_close(got_dw, dw_ref, "d_weight", rel_fro=1e-4, elem=1e-3)
+    # and against the full-precision oracle gradients, at the GEMM contract's tolerance
+    assert_gemm_close(g_dh.cpu().numpy(), oracle.matmul_nt(dlogits, wv, THREADS), "d_hidden vs fp32 path")
+    # accumulate into an existing d_weight
+    _, _, g_dw2 = head.backward(h, w, t, g_lse, d_weight=g_dw.clone(), accumulate_dw=True, want_d_hidden=False)
+    assert_gemm_close(g_dw2.cpu().numpy(), 2 * g_dw.cpu().numpy(), "d_weight accumulate", rel_fro=1e-5, elem=1e-4)
+
+
+def test_fused_head_full_size_properties(pkg, oracle, gemm):
+    """BASELINE size (32768 x 1536 x 50432, 50257 classes): sampled rows against the
+    oracle and size-independent properties of the gradient."""
+    import torch
+    m, k, v, classes = 32768, 1536, 50432, 50257
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    h = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((k, v), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+    t = torch.randint(0, classes, (m,), generator=gen, device="cuda", dtype=torch.int32)
+    head = pkg.FusedLmHead(gemm, classes, "in_out")
+    loss, lse, row_loss = head.forward(h, w, t)
+    assert gemm.device_status() == 0
+    rows = np.array([0, 1, 127, 128, 255, 256, 4095, 16384, 32767, 20001])
+    hv = h[rows].float().cpu().numpy()
+    wv = w.float().cpu().numpy()
+    tv = t.cpu().numpy()
+    logits = oracle.matmul(hv, wv, THREADS)
+    _, probs, rl = oracle.xent_forward(logits, tv[rows], classes)
+    assert np.allclose(row_loss.cpu().numpy()[rows], rl, atol=5e-4, rtol=1e-5)
+    assert abs(float(loss.item()) - float(row_loss.double().mean().item())) < 1e-5
+    # logits ~ N(0, k * 0.02^2): the expected loss is ln(classes) + variance / 2
+    assert abs(float(loss.item()) - (np.log(classes) + 0.5 * k * 0.02 ** 2)) < 0.05
+    dl, dh, dw = head.backward(h, w, t, lse)
+    assert gemm.device_status() == 0
+    assert torch.all(dl[:, classes:] == 0).item()
+    sums = dl.float().sum(dim=1)
+    assert float(sums.abs().max().item()) < 1e-5                     # rows of p - onehot sum to 0
+    # the oracle divides by its own row count; rescale to the kernel's 1 / m
+    ref_dl = oracle.xent_backward(probs, tv[rows], classes, dy=len(rows) / m)
+    got = dl[rows].float().cpu().numpy()
+    assert np.max(np.abs(got - ref_dl)) <= 4e-3 * np.abs(ref_dl).max()
+    # d_hidden of the sampled rows from the kernel's own dlogits
+    ref_dh = oracle.matmul_nt(got, wv, THREADS)
+    assert_gemm_close(dh[rows].cpu().numpy(), ref_dh, "d_hidden rows", rel_fro=1e-4, elem=1e-3)
+    # d_weight: a sampled column block against a torch fp32 product of the same operands
+    cols = slice(50000, 50432)
+    ref_dw = (h.float().t() @ dl[:, cols].float()).cpu().numpy()
+    assert_gemm_close(dw[:, cols].cpu().numpy(), ref_dw, "d_weight block", rel_fro=1e-3, elem=1e-3)
