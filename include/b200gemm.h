@@ -194,6 +194,65 @@ B200GEMM_API int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, 
                                              void* dlogits_bf16, float* d_hidden, float* d_weight,
                                              int32_t accumulate_dw);
 
+/*
+ * Grouped ("ragged") expert GEMM over a routed token permutation (new: the
+ * reference multiplies fixed-capacity bins, dead rows included,
+ * gpu/model/src/lib.rs:1717-1748, 1913-2154).
+ *
+ *   for g in [0, groups):  rows r in [offsets[g], offsets[g+1])
+ *       C[r, 0:n] = act( A[r, 0:k] . B[g]^T )            bf16 out, fp32 accumulate
+ *
+ *   a        device bf16 [total_rows, k], row stride lda (0 = k)
+ *   b        device bf16, `groups` matrices `batch_stride_b` elements apart
+ *            (0 = dense): b_layout K_MAJOR [n, k] or MN_MAJOR [k, n], row stride ldb
+ *   c        device bf16 [total_rows, n], row stride ldc (0 = n; multiple of 8)
+ *   offsets  DEVICE int32 [groups + 1], non-decreasing, offsets[groups] <= total_rows
+ *            (the expert offsets the router produces; never read on the host)
+ *   activation 0 = none, 1 = SiLU x*sigmoid(x) (crates/nn/src/swiglu.rs:22-28)
+ * Rows of C outside every group are left untouched.  groups <= 256.
+ */
+B200GEMM_API int b200gemm_grouped_gemm(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                       const void* b, int32_t b_layout, int64_t ldb,
+                                       int64_t batch_stride_b, void* c, int64_t ldc,
+                                       const int32_t* offsets, int32_t groups, int64_t total_rows,
+                                       int64_t n, int64_t k, int32_t activation);
+
+/*
+ * MoE routing integers and gates (crates/nn/src/moe.rs:205-254 `MoeFfn::route`;
+ * GPU counterparts gpu/ops/src/lib.rs:2435-2511 router_softmax_topk, :2569-2705
+ * moe_bin_assign_parallel).  All pointers are device pointers.
+ *   scores   fp32 [tokens, experts]: probabilities (scores_are_logits = 0) or raw
+ *            router logits (!= 0); selection order is by descending score, ties to
+ *            the lower expert index
+ *   selected uint32 [tokens*top_k]        gates fp32 [tokens*top_k]
+ *   slots    uint32 [tokens*top_k]: arrival order within the expert in flattened
+ *            (token, rank) order; 0xFFFFFFFF when the expert was at `capacity`
+ *   assignment_counts, accepted_counts uint32 [experts]
+ *   offsets  int32 [experts + 1]: exclusive prefix sum of accepted_counts
+ *   dest_row uint32 [tokens*top_k]: offsets[selected] + slot (0xFFFFFFFF if dropped)
+ * experts <= 256, top_k <= 16 and <= experts.  Integer outputs are bit-exact
+ * with the reference's CPU router; so are the gates when scores are probabilities.
+ */
+B200GEMM_API int b200gemm_moe_route(b200gemm_handle_t h, void* stream, const float* scores,
+                                    int32_t scores_are_logits, int64_t tokens, int32_t experts,
+                                    int32_t top_k, int64_t capacity, uint32_t* selected, float* gates,
+                                    uint32_t* slots, uint32_t* assignment_counts,
+                                    uint32_t* accepted_counts, int32_t* offsets, uint32_t* dest_row);
+
+/* Dispatch (gpu/ops/src/lib.rs:2913-2953 moe_scatter_packed_quad):
+ * x_permuted[dest_row[t*top_k + r], :] = x[t, :], bf16, d a multiple of 8. */
+B200GEMM_API int b200gemm_moe_scatter(b200gemm_handle_t h, void* stream, const void* x,
+                                      const uint32_t* dest_row, int64_t tokens, int32_t top_k,
+                                      int64_t d, void* x_permuted);
+
+/* Combine (gpu/ops/src/lib.rs:3064-3130 moe_gather_combine_add_quad_packed):
+ * out[t, :] = residual[t, :] + sum_r gates[t,r] * y_permuted[dest_row[t,r], :], ranks
+ * added in order in fp32.  residual may be NULL.  out_type: b200gemm_out_t. */
+B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permuted,
+                                      const uint32_t* dest_row, const float* gates,
+                                      const void* residual, int64_t tokens, int32_t top_k, int64_t d,
+                                      void* out, int32_t out_type);
+
 /* Synchronises `stream`, reads and clears the device status word; returns
  * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
  * *device_code (may be NULL).  The reference has no counterpart: its kernels

@@ -7,5 +7,7 @@ from . import _lib
 from ._lib import B200GemmError, GemmDesc
 from .gemm import Tcgen05Gemm
 from .lmhead import FusedLmHead
+from . import moe
+from .moe import GroupedExpertFfn
 
-__all__ = ["Tcgen05Gemm", "FusedLmHead", "B200GemmError", "GemmDesc", "_lib"]
+__all__ = ["Tcgen05Gemm", "FusedLmHead", "GroupedExpertFfn", "moe", "B200GemmError", "GemmDesc", "_lib"]

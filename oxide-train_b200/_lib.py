@@ -49,6 +49,15 @@ SIGNATURES = {
     "b200gemm_convert_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "b200gemm_transpose_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200gemm_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
+    "b200gemm_grouped_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,
+                                        C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,
+                                        C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "b200gemm_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
+                                     C.c_int32, C.c_int64] + [C.c_void_p] * 7),
+    "b200gemm_moe_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                       C.c_int64, C.c_void_p]),
+    "b200gemm_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_int64, C.c_int32, C.c_int64, C.c_void_p, C.c_int32]),
     "b200gemm_lmhead_ce_workspace_bytes": (C.c_size_t, [C.c_int64]),
     "b200gemm_lmhead_ce_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                              C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,

@@ -16,6 +16,7 @@
 #include "aux_kernels.cuh"
 #include "ce_kernels.cuh"
 #include "gemm_kernel.cuh"
+#include "moe_kernels.cuh"
 
 namespace {
 
@@ -461,6 +462,69 @@ int ce_backward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, 
   return B200GEMM_OK;
 }
 
+
+// ---------------------------------------------------------------- grouped expert GEMM
+
+int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int64_t lda,
+                 const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b, void* c,
+                 int64_t ldc, const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
+                 int64_t k, int32_t activation) {
+  if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 1)
+    return fail(B200GEMM_ERR_INVALID, "bad layout or activation");
+  if (groups < 1 || groups > kMaxGroups) return fail(B200GEMM_ERR_SHAPE, "groups must be in [1, %d]", kMaxGroups);
+  if (total_rows <= 0 || n <= 0 || k <= 0 || total_rows > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30))
+    return fail(B200GEMM_ERR_SHAPE, "bad extent");
+  const bool b_mn = b_layout == B200GEMM_MN_MAJOR;
+  lda = lda ? lda : k;
+  ldb = ldb ? ldb : (b_mn ? n : k);
+  ldc = ldc ? ldc : n;
+  if (lda < k || ldb < (b_mn ? n : k) || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
+  if ((ldc % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "ldc must be a multiple of 8");
+  const int64_t bsb = batch_stride_b ? batch_stride_b : ldb * (b_mn ? k : n);
+  GemmParams params;
+  memset(&params, 0, sizeof(params));
+  const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  int rc = encode_map(ctx, &params.map_a, bf16, 2, a, k, total_rows, 1, lda, 0, 64, kTileMCta, "A");
+  if (rc) return rc;
+  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, n, groups, ldb, bsb, 64, kTileN / 2, "B");
+  else rc = encode_map(ctx, &params.map_b, bf16, 2, b, n, k, groups, ldb, bsb, 64, 64, "B");
+  if (rc) return rc;
+  rc = encode_map(ctx, &params.map_c, bf16, 2, c, n, total_rows, 1, ldc, 0, 64, 32, "C");
+  if (rc) return rc;
+  params.status = ctx->status;
+  params.c_bf16 = static_cast<uint16_t*>(c);
+  params.ldc = ldc;
+  params.m = static_cast<int>(total_rows);
+  params.n = static_cast<int>(n);
+  params.tiles_n = ceil_div(n, kTileN);
+  params.tiles_m = 0;
+  params.batch = groups;
+  params.k_blocks = ceil_div(k, kBlockK);
+  params.split_k = 1;
+  params.kb_per_split = params.k_blocks;
+  params.b_mn = b_mn;
+  params.group_offsets = offsets;
+  params.groups = groups;
+  params.act_silu = activation;
+  // The tile count depends on the device-side offsets; bound it from above
+  // (each group wastes at most one partial tile) and let surplus clusters exit.
+  const int units = std::max(1, ctx->sm_count / 2);
+  const int64_t max_items = (ceil_div(total_rows, 2 * kTileMCta) + static_cast<int64_t>(groups)) * params.tiles_n;
+  const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
+  return launch_kernel<2, kEpiBf16Grouped, kSchedGrouped>(ctx, params, grid, stream);
+}
+
+// ---------------------------------------------------------------- MoE routing
+
+int moe_check(int64_t tokens, int32_t experts, int32_t top_k) {
+  if (tokens <= 0 || tokens > (1ll << 28)) return fail(B200GEMM_ERR_SHAPE, "bad token count");
+  if (experts < 1 || experts > kMoeMaxExperts) return fail(B200GEMM_ERR_SHAPE, "experts must be in [1, %d]", kMoeMaxExperts);
+  if (top_k < 1 || top_k > kMoeMaxTopK || top_k > experts)
+    return fail(B200GEMM_ERR_SHAPE, "top_k must be in [1, min(%d, experts)]", kMoeMaxTopK);
+  return B200GEMM_OK;
+}
+
 int check_handle(b200gemm_handle_t h) {
   if (!h) return fail(B200GEMM_ERR_INVALID, "null handle");
   return B200GEMM_OK;
@@ -620,6 +684,80 @@ int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, const void* h
   if (rc) return rc;
   return ce_backward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, lse, dy,
                      m, k, v, classes, dlogits_bf16, d_hidden, d_weight, accumulate_dw);
+}
+
+int b200gemm_grouped_gemm(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                          const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b,
+                          void* c, int64_t ldc, const int32_t* offsets, int32_t groups,
+                          int64_t total_rows, int64_t n, int64_t k, int32_t activation) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b,
+                      c, ldc, offsets, groups, total_rows, n, k, activation);
+}
+
+int b200gemm_moe_route(b200gemm_handle_t h, void* stream_, const float* scores,
+                       int32_t scores_are_logits, int64_t tokens, int32_t experts, int32_t top_k,
+                       int64_t capacity, uint32_t* selected, float* gates, uint32_t* slots,
+                       uint32_t* assignment_counts, uint32_t* accepted_counts, int32_t* offsets,
+                       uint32_t* dest_row) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!scores || !selected || !gates || !slots || !assignment_counts || !accepted_counts ||
+      !offsets || !dest_row)
+    return fail(B200GEMM_ERR_INVALID, "null pointer");
+  rc = moe_check(tokens, experts, top_k);
+  if (rc) return rc;
+  if (capacity <= 0) return fail(B200GEMM_ERR_SHAPE, "capacity must be positive");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const long long pairs = tokens * top_k;
+  const int topk_blocks = static_cast<int>((tokens * 32 + 255) / 256);
+  moe_topk_kernel<<<topk_blocks, 256, 0, stream>>>(scores, scores_are_logits, tokens, experts, top_k,
+                                                   selected, gates);
+  CUDA_TRY(cudaGetLastError());
+  moe_slot_kernel<<<experts, 256, 0, stream>>>(selected, pairs, capacity, slots, assignment_counts,
+                                               accepted_counts);
+  CUDA_TRY(cudaGetLastError());
+  moe_offsets_kernel<<<1, 32, 0, stream>>>(accepted_counts, experts, offsets);
+  CUDA_TRY(cudaGetLastError());
+  moe_dest_kernel<<<stream_grid(pairs, h->sm_count), 256, 0, stream>>>(selected, slots, offsets, pairs, dest_row);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_moe_scatter(b200gemm_handle_t h, void* stream, const void* x, const uint32_t* dest_row,
+                         int64_t tokens, int32_t top_k, int64_t d, void* x_permuted) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!x || !dest_row || !x_permuted) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (tokens <= 0 || top_k < 1 || d <= 0 || (d % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "need tokens, top_k > 0 and d a multiple of 8");
+  if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_permuted)) & 15u) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "buffers must be 16-byte aligned");
+  const long long pairs = tokens * top_k;
+  moe_scatter_kernel<<<stream_grid(pairs * 32, h->sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), dest_row, pairs, top_k, d, static_cast<uint16_t*>(x_permuted));
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permuted,
+                         const uint32_t* dest_row, const float* gates, const void* residual,
+                         int64_t tokens, int32_t top_k, int64_t d, void* out, int32_t out_type) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!y_permuted || !dest_row || !gates || !out) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (tokens <= 0 || top_k < 1 || d <= 0 || (d % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "need tokens, top_k > 0 and d a multiple of 8");
+  if (out_type < 0 || out_type > 1) return fail(B200GEMM_ERR_INVALID, "bad output type");
+  const int grid = stream_grid(tokens * 32, h->sm_count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_type == B200GEMM_OUT_BF16)
+    moe_combine_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(y_permuted), dest_row, gates,
+                                                  static_cast<const uint16_t*>(residual), tokens, top_k, d, out);
+  else
+    moe_combine_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(y_permuted), dest_row, gates,
+                                                   static_cast<const uint16_t*>(residual), tokens, top_k, d, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
 }
 
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {

@@ -1,0 +1,257 @@
+// Mixture-of-experts routing beside the grouped expert GEMM: top-k selection,
+// deterministic slot assignment, expert offsets, the token permutation
+// (dispatch) and the gate-weighted combine.  Integer outputs follow the
+// reference's CPU router bit for bit (crates/nn/src/moe.rs:205-254); these are
+// latency/HBM-bound kernels, not tensor-core work.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr uint32_t kMoeDropped = 0xFFFFFFFFu;   // u32::MAX marks a dropped assignment
+constexpr int kMoeMaxExperts = 256;
+constexpr int kMoeMaxTopK = 16;
+
+// f32::total_cmp as an integer key (crates/nn/src/moe.rs:217-219 sorts with it).
+__device__ __forceinline__ int total_order_key(float f) {
+  int b = __float_as_int(f);
+  return b ^ static_cast<int>(static_cast<unsigned>(b >> 31) >> 1);
+}
+
+// One warp per token.  Picks the top_k experts by descending score, ties to the
+// lower expert index (moe.rs:215-220), and the renormalised gate weights.
+//   scores_are_logits == 0: scores are probabilities; gate = p / sum_topk(p) with
+//       the denominator summed in f64 in rank order and rounded to f32 (moe.rs:222-225)
+//   scores_are_logits != 0: gate = softmax over the selected logits (the same
+//       quantity, computed without forming the full softmax)
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ scores,
+                                                       int scores_are_logits, long long tokens,
+                                                       int experts, int top_k,
+                                                       uint32_t* __restrict__ selected,
+                                                       float* __restrict__ gates) {
+  const int lane = threadIdx.x & 31;
+  const long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (token >= tokens) return;
+  const float* row = scores + token * experts;
+  constexpr int kPerLane = kMoeMaxExperts / 32;
+  float val[kPerLane];
+  int key[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    val[i] = e < experts ? row[e] : 0.f;
+    key[i] = e < experts ? total_order_key(val[i]) : INT_MIN;
+  }
+  unsigned taken = 0;   // bit i: this lane's i-th expert was already selected
+  float sel_val[kMoeMaxTopK];
+  int sel_idx[kMoeMaxTopK];
+  for (int rank = 0; rank < top_k; ++rank) {
+    // best of this lane: highest key, then lowest index
+    long long best = LLONG_MIN;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < experts && !((taken >> i) & 1u)) {
+        const long long cand = (static_cast<long long>(key[i]) << 32) |
+                               static_cast<long long>(0xFFFFFFFFu - static_cast<unsigned>(e));
+        best = cand > best ? cand : best;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const long long other = __shfl_xor_sync(0xffffffffu, best, off);
+      best = other > best ? other : best;
+    }
+    const int e = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned>(best & 0xFFFFFFFFll));
+    if ((e & 31) == lane) taken |= 1u << (e >> 5);
+    // the owner lane broadcasts the value
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (i == (e >> 5)) v = val[i];
+    v = __shfl_sync(0xffffffffu, v, e & 31);
+    sel_val[rank] = v;
+    sel_idx[rank] = e;
+  }
+  if (lane == 0) {
+    const long long base = token * top_k;
+    if (!scores_are_logits) {
+      double denom = 0.0;
+      for (int r = 0; r < top_k; ++r) denom += static_cast<double>(sel_val[r]);
+      const float d = static_cast<float>(denom);
+      for (int r = 0; r < top_k; ++r) {
+        selected[base + r] = static_cast<uint32_t>(sel_idx[r]);
+        gates[base + r] = sel_val[r] / d;
+      }
+    } else {
+      const float mx = sel_val[0];   // rank 0 is the largest
+      float ex[kMoeMaxTopK];
+      float sum = 0.f;
+      for (int r = 0; r < top_k; ++r) {
+        ex[r] = expf(sel_val[r] - mx);
+        sum += ex[r];
+      }
+      for (int r = 0; r < top_k; ++r) {
+        selected[base + r] = static_cast<uint32_t>(sel_idx[r]);
+        gates[base + r] = ex[r] / sum;
+      }
+    }
+  }
+}
+
+// One block per expert walks every (token, rank) pair in order and hands out
+// slots by arrival (moe.rs:228-236): slot = number of earlier pairs routed to
+// the same expert; pairs beyond `capacity` are dropped.  Deterministic by
+// construction: no atomics decide an order.
+__global__ void __launch_bounds__(256) moe_slot_kernel(const uint32_t* __restrict__ selected,
+                                                       long long pairs, long long capacity,
+                                                       uint32_t* __restrict__ slots,
+                                                       uint32_t* __restrict__ assignment_counts,
+                                                       uint32_t* __restrict__ accepted_counts) {
+  __shared__ unsigned warp_totals[8];
+  const uint32_t expert = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long running = 0;
+  for (long long base = 0; base < pairs; base += 256 * 4) {
+    const long long q0 = base + static_cast<long long>(threadIdx.x) * 4;
+    unsigned flags = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (q0 + j < pairs && selected[q0 + j] == expert) flags |= 1u << j;
+    const unsigned mine = __popc(flags);
+    unsigned incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    if (lane == 31) warp_totals[warp] = incl;
+    __syncthreads();
+    unsigned warp_base = 0, tile_total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) warp_base += warp_totals[w];
+      tile_total += warp_totals[w];
+    }
+    unsigned long long slot = running + warp_base + (incl - mine);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if ((flags >> j) & 1u) {
+        slots[q0 + j] = slot < static_cast<unsigned long long>(capacity) ? static_cast<uint32_t>(slot)
+                                                                        : kMoeDropped;
+        ++slot;
+      }
+    }
+    running += tile_total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    assignment_counts[expert] = static_cast<uint32_t>(running);
+    accepted_counts[expert] = static_cast<uint32_t>(
+        running < static_cast<unsigned long long>(capacity) ? running : capacity);
+  }
+}
+
+// offsets[e] = number of accepted rows of experts before e; offsets[experts] = total.
+__global__ void moe_offsets_kernel(const uint32_t* __restrict__ accepted_counts, int experts,
+                                   int* __restrict__ offsets) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = run;
+      run += static_cast<int>(accepted_counts[e]);
+    }
+    offsets[experts] = run;
+  }
+}
+
+// dest_row[pair] = offsets[selected] + slot, or kMoeDropped.
+__global__ void __launch_bounds__(256) moe_dest_kernel(const uint32_t* __restrict__ selected,
+                                                       const uint32_t* __restrict__ slots,
+                                                       const int* __restrict__ offsets,
+                                                       long long pairs,
+                                                       uint32_t* __restrict__ dest_row) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long q = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; q < pairs; q += stride) {
+    const uint32_t s = slots[q];
+    dest_row[q] = s == kMoeDropped ? kMoeDropped : static_cast<uint32_t>(offsets[selected[q]]) + s;
+  }
+}
+
+// Dispatch: x_permuted[dest_row[token * top_k + rank], :] = x[token, :].  One warp
+// per pair, 16-byte copies (d is a multiple of 8 bf16).
+__global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __restrict__ x,
+                                                          const uint32_t* __restrict__ dest_row,
+                                                          long long pairs, int top_k, long long d,
+                                                          uint16_t* __restrict__ x_permuted) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long vecs = d / 8;
+  for (long long q = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; q < pairs; q += warps) {
+    const uint32_t dst = dest_row[q];
+    if (dst == kMoeDropped) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (q / top_k) * d);
+    uint4* out = reinterpret_cast<uint4*>(x_permuted + static_cast<long long>(dst) * d);
+    for (long long v = lane; v < vecs; v += 32) out[v] = src[v];
+  }
+}
+
+// Combine: out[token, :] = residual[token, :] + sum over ranks (in rank order) of
+// gate * y_permuted[dest_row, :], accumulated in fp32 (moe.rs:292-306).  One
+// warp per token; each lane owns 8 consecutive columns at a time.
+template <bool kOutBf16>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __restrict__ y_permuted,
+                                                          const uint32_t* __restrict__ dest_row,
+                                                          const float* __restrict__ gates,
+                                                          const uint16_t* __restrict__ residual,
+                                                          long long tokens, int top_k, long long d,
+                                                          void* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long vecs = d / 8;
+  for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    for (long long v = lane; v < vecs; v += 32) {
+      float acc[8];
+      if (residual) {
+        const uint4 r = reinterpret_cast<const uint4*>(residual + token * d)[v];
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] = __uint_as_float(w[j] << 16);
+          acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      }
+      for (int r = 0; r < top_k; ++r) {
+        const uint32_t src = dest_row[token * top_k + r];
+        if (src == kMoeDropped) continue;
+        const float g = gates[token * top_k + r];
+        const uint4 y = reinterpret_cast<const uint4*>(y_permuted + static_cast<long long>(src) * d)[v];
+        const uint32_t w[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(g, __uint_as_float(w[j] << 16)));
+          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(g, __uint_as_float(w[j] & 0xffff0000u)));
+        }
+      }
+      if (kOutBf16) {
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ow[j]) : "f"(acc[2 * j + 1]), "f"(acc[2 * j]));
+        reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + token * d)[v] = o;
+      } else {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + token * d) + 2 * v;
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+    }
+  }
+}
+
+}  // namespace b200
