@@ -176,6 +176,37 @@ B200GEMM_API int b200gemm_lmhead_ce_forward(b200gemm_handle_t h, void* stream, c
                                             float* loss, void* workspace, size_t workspace_bytes);
 
 /*
+ * b200gemm_lmhead_ce_forward for callers that cannot hand the library a
+ * workspace.  This entry point has no counterpart in the reference.
+ *
+ * Who needs it: a trainer that reserves all of HBM for its own arena at
+ * start-up and therefore has nothing left to cudaMalloc from, or a step loop
+ * that must not call cudaMalloc / cudaFree at all because those calls
+ * synchronise the whole device.  For them the per-row softmax statistics go to
+ * a fixed array that is part of the library image (about 2.1 MiB of every GPU
+ * the library is loaded on, held until the process exits) instead of a
+ * caller-provided workspace.  Same arguments and results as
+ * b200gemm_lmhead_ce_forward otherwise; this call itself never allocates or
+ * frees device or pinned memory.
+ *
+ * Limits and rules:
+ *   - m <= 32768 rows; larger m is refused with B200GEMM_ERR_SHAPE.
+ *   - The first call on a device looks up the array's device address.  Make
+ *     that first call with the handle's device current, and make it before any
+ *     stream capture is begun on that device; later calls only launch kernels.
+ *   - All calls on one device share the one array: two calls whose kernels can
+ *     overlap on the GPU (different streams, no ordering between them) race on
+ *     it and corrupt each other's loss.  Order them on one stream or with events.
+ *   - The array keeps whatever the previous call left in it; the entry point
+ *     re-zeroes the part that must start at zero (the loss accumulator) itself.
+ */
+B200GEMM_API int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream,
+                                                    const void* hidden, const void* weight,
+                                                    int32_t w_layout, const int32_t* targets,
+                                                    int64_t m, int64_t k, int64_t v, int64_t classes,
+                                                    float* lse, float* row_loss, float* loss);
+
+/*
  * Backward of the above (reference: fused_classifier_backward_in_place_bf16 +
  * GpuBf16Head::backward_weight / backward_input, gpu/ops/src/lib.rs:1843-2001,
  * gpu/model/src/lib.rs:3103-3145, 5750-5784).  The logits are recomputed tile

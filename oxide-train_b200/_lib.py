@@ -62,6 +62,9 @@ SIGNATURES = {
     "b200gemm_lmhead_ce_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                              C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                                     C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                                     C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200gemm_lmhead_ce_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                               C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int64,
                                               C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -525,6 +525,49 @@ int moe_check(int64_t tokens, int32_t experts, int32_t top_k) {
   return B200GEMM_OK;
 }
 
+
+// ---------------------------------------------------------------- allocation-free head forward
+
+// Largest row count b200gemm_lmhead_ce_forward_noalloc accepts, and the bytes
+// of scratch that needs (same carving as ce_carve: 256-byte accumulator block,
+// one fp32 target logit per row, kCeMaxChunks (max, sum-exp) pairs per row).
+constexpr int64_t kCeStaticMaxRows = 32768;
+constexpr size_t kCeStaticBytes =
+    256 + static_cast<size_t>(kCeStaticMaxRows) * sizeof(float) +
+    static_cast<size_t>(kCeMaxChunks) * kCeStaticMaxRows * sizeof(float2);
+
+// The scratch itself: part of the library image, so it exists on every GPU the
+// library is loaded on from load until exit, and no call ever allocates it.
+static __device__ __align__(256) unsigned char g_ce_static_scratch[kCeStaticBytes];
+
+constexpr int kCeStaticMaxDevices = 64;
+std::mutex g_ce_static_mu;
+void* g_ce_static_ptr[kCeStaticMaxDevices] = {};
+
+// Device address of the scratch array on `device`.  In host code the array's
+// name is only a handle for the runtime, not an address a kernel can use, so
+// the address is looked up once per device (that device must be current) and
+// remembered.
+int ce_static_scratch(int device, void** out) {
+  if (device < 0 || device >= kCeStaticMaxDevices)
+    return fail(B200GEMM_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks",
+                device, kCeStaticMaxDevices);
+  std::lock_guard<std::mutex> lock(g_ce_static_mu);
+  if (!g_ce_static_ptr[device]) {
+    int current = -1;
+    CUDA_TRY(cudaGetDevice(&current));
+    if (current != device)
+      return fail(B200GEMM_ERR_INVALID, "device %d must be current on the calling thread (device %d is)",
+                  device, current);
+    void* ptr = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&ptr, g_ce_static_scratch));
+    if (!ptr) return fail(B200GEMM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_ce_static_ptr[device] = ptr;
+  }
+  *out = g_ce_static_ptr[device];
+  return B200GEMM_OK;
+}
+
 int check_handle(b200gemm_handle_t h) {
   if (!h) return fail(B200GEMM_ERR_INVALID, "null handle");
   return B200GEMM_OK;
@@ -758,6 +801,26 @@ int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permut
                                                    static_cast<const uint16_t*>(residual), tokens, top_k, d, out);
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
+}
+
+int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream, const void* hidden,
+                                       const void* weight, int32_t w_layout, const int32_t* targets,
+                                       int64_t m, int64_t k, int64_t v, int64_t classes, float* lse,
+                                       float* row_loss, float* loss) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (m > kCeStaticMaxRows)
+    return fail(B200GEMM_ERR_SHAPE,
+                "m = %lld exceeds the %lld rows the built-in scratch holds; use "
+                "b200gemm_lmhead_ce_forward with a caller-provided workspace",
+                static_cast<long long>(m), static_cast<long long>(kCeStaticMaxRows));
+  if (m > 0 && ce_workspace_bytes(m) > kCeStaticBytes)
+    return fail(B200GEMM_ERR_SHAPE, "built-in scratch too small for m = %lld", static_cast<long long>(m));
+  void* scratch = nullptr;
+  rc = ce_static_scratch(h->device, &scratch);
+  if (rc) return rc;
+  return ce_forward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, m, k, v,
+                    classes, lse, row_loss, loss, scratch, kCeStaticBytes);
 }
 
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {
