@@ -176,6 +176,26 @@ B200GEMM_API int b200gemm_lmhead_ce_forward(b200gemm_handle_t h, void* stream, c
                                             float* loss, void* workspace, size_t workspace_bytes);
 
 /*
+ * One vocabulary shard of b200gemm_lmhead_ce_forward (new: the reference is
+ * single-GPU).  `weight_shard` holds `v_local` columns of the vocabulary, of
+ * which the first `classes_local` are real; `local_targets[r]` is the row's
+ * target minus the shard's first column, so a target owned by another shard is
+ * simply out of [0, classes_local).  Outputs per row, device fp32 [m]:
+ *   row_max          max over the shard's real columns
+ *   row_sum          sum of exp(logit - row_max) over them
+ *   row_target_logit the target's logit if this shard owns it, else 0
+ * The caller merges shards: M = max_s row_max; S = sum_s row_sum * exp(row_max - M);
+ * lse = M + ln S; loss = lse - sum_s row_target_logit.  Workspace as above.
+ */
+B200GEMM_API int b200gemm_lmhead_ce_forward_shard(b200gemm_handle_t h, void* stream,
+                                                  const void* hidden, const void* weight_shard,
+                                                  int32_t w_layout, const int32_t* local_targets,
+                                                  int64_t m, int64_t k, int64_t v_local,
+                                                  int64_t classes_local, float* row_max,
+                                                  float* row_sum, float* row_target_logit,
+                                                  void* workspace, size_t workspace_bytes);
+
+/*
  * b200gemm_lmhead_ce_forward for callers that cannot hand the library a
  * workspace.  This entry point has no counterpart in the reference.
  *
@@ -247,6 +267,18 @@ B200GEMM_API int b200gemm_grouped_gemm(b200gemm_handle_t h, void* stream, const 
                                        int64_t batch_stride_b, void* c, int64_t ldc,
                                        const int32_t* offsets, int32_t groups, int64_t total_rows,
                                        int64_t n, int64_t k, int32_t activation);
+
+/* b200gemm_grouped_gemm where group g multiplies B[group_b_index[g]] (device int32
+ * [groups], values in [0, b_count)) instead of B[g]: lets rows that arrive from
+ * several ranks, each run sorted by local expert, be multiplied in place without
+ * re-sorting them (one group per (source rank, local expert)). */
+B200GEMM_API int b200gemm_grouped_gemm_indexed(b200gemm_handle_t h, void* stream, const void* a,
+                                               int64_t lda, const void* b, int32_t b_layout,
+                                               int64_t ldb, int64_t batch_stride_b, int32_t b_count,
+                                               const int32_t* group_b_index, void* c, int64_t ldc,
+                                               const int32_t* offsets, int32_t groups,
+                                               int64_t total_rows, int64_t n, int64_t k,
+                                               int32_t activation);
 
 /*
  * MoE routing integers and gates (crates/nn/src/moe.rs:205-254 `MoeFfn::route`;

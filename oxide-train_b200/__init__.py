@@ -8,6 +8,7 @@ from ._lib import B200GemmError, GemmDesc
 from .gemm import Tcgen05Gemm
 from .lmhead import FusedLmHead
 from . import moe
+from . import parallel
 from .moe import GroupedExpertFfn
 
-__all__ = ["Tcgen05Gemm", "FusedLmHead", "GroupedExpertFfn", "moe", "B200GemmError", "GemmDesc", "_lib"]
+__all__ = ["Tcgen05Gemm", "FusedLmHead", "GroupedExpertFfn", "moe", "parallel", "B200GemmError", "GemmDesc", "_lib"]

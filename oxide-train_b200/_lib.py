@@ -62,6 +62,13 @@ SIGNATURES = {
     "b200gemm_lmhead_ce_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                              C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "b200gemm_lmhead_ce_forward_shard": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                                   C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "b200gemm_grouped_gemm_indexed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                                C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
+                                                C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int64,
+                                                C.c_int64, C.c_int64, C.c_int32]),
     "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                      C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                                      C.c_void_p, C.c_void_p, C.c_void_p]),

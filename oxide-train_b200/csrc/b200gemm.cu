@@ -344,13 +344,23 @@ int ce_encode_operands(b200gemm_context* ctx, GemmParams* params, const void* hi
   return rc;
 }
 
+// With `shard` set the launch is one vocabulary shard's: it hands back the
+// shard's per-row (max, sum-exp, target logit) instead of lse and the loss.
+struct CeShardOut {
+  float* row_max;
+  float* row_sum;
+  float* row_target_logit;
+};
+
 int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, const void* weight,
                int32_t w_layout, const int32_t* targets, int64_t m, int64_t k, int64_t v,
                int64_t classes, float* lse, float* row_loss, float* loss, void* workspace,
-               size_t workspace_bytes) {
+               size_t workspace_bytes, const CeShardOut* shard = nullptr) {
   int rc = ce_check(hidden, weight, w_layout, targets, m, k, v, classes);
   if (rc) return rc;
-  if (!lse) return fail(B200GEMM_ERR_INVALID, "lse output is required");
+  if (!shard && !lse) return fail(B200GEMM_ERR_INVALID, "lse output is required");
+  if (shard && (!shard->row_max || !shard->row_sum || !shard->row_target_logit))
+    return fail(B200GEMM_ERR_INVALID, "null shard output");
   if (!workspace || workspace_bytes < ce_workspace_bytes(m) ||
       (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
     return fail(B200GEMM_ERR_INVALID, "workspace missing, too small (%zu needed) or not 256-byte aligned",
@@ -390,9 +400,18 @@ int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, c
   const int64_t items = static_cast<int64_t>(params.tiles_m) * params.ce_chunks;
   const int grid = static_cast<int>(std::min<int64_t>(items, units)) * 2;
   CUDA_TRY(cudaMemsetAsync(ws.accum, 0, sizeof(CeAccum), stream));
+  // A row whose target lies in another shard gets no target logit from this one.
+  if (shard) CUDA_TRY(cudaMemsetAsync(ws.target_logit, 0, static_cast<size_t>(m) * sizeof(float), stream));
   rc = launch_kernel<2, kEpiCeForward, kSchedCeForward>(ctx, params, grid, stream);
   if (rc) return rc;
   const int blocks = static_cast<int>(std::min<int64_t>((m + 255) / 256, ctx->sm_count * 4));
+  if (shard) {
+    ce_partial_kernel<<<blocks, 256, 0, stream>>>(ws.partials, ws.target_logit, static_cast<int>(m),
+                                                  params.ce_chunks, shard->row_max, shard->row_sum,
+                                                  shard->row_target_logit);
+    CUDA_TRY(cudaGetLastError());
+    return B200GEMM_OK;
+  }
   ce_combine_kernel<<<blocks, 256, 0, stream>>>(ws.partials, ws.target_logit, static_cast<int>(m),
                                                 params.ce_chunks, lse, row_loss, loss, ws.accum);
   CUDA_TRY(cudaGetLastError());
@@ -468,8 +487,11 @@ int ce_backward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, 
 int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int64_t lda,
                  const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b, void* c,
                  int64_t ldc, const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
-                 int64_t k, int32_t activation) {
+                 int64_t k, int32_t activation, const int32_t* group_b_index = nullptr,
+                 int32_t b_count = 0) {
   if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
+  const int32_t b_mats = group_b_index ? b_count : groups;
   if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 1)
     return fail(B200GEMM_ERR_INVALID, "bad layout or activation");
   if (groups < 1 || groups > kMaxGroups) return fail(B200GEMM_ERR_SHAPE, "groups must be in [1, %d]", kMaxGroups);
@@ -487,8 +509,8 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   int rc = encode_map(ctx, &params.map_a, bf16, 2, a, k, total_rows, 1, lda, 0, 64, kTileMCta, "A");
   if (rc) return rc;
-  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, n, groups, ldb, bsb, 64, kTileN / 2, "B");
-  else rc = encode_map(ctx, &params.map_b, bf16, 2, b, n, k, groups, ldb, bsb, 64, 64, "B");
+  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, n, b_mats, ldb, bsb, 64, kTileN / 2, "B");
+  else rc = encode_map(ctx, &params.map_b, bf16, 2, b, n, k, b_mats, ldb, bsb, 64, 64, "B");
   if (rc) return rc;
   rc = encode_map(ctx, &params.map_c, bf16, 2, c, n, total_rows, 1, ldc, 0, 64, 32, "C");
   if (rc) return rc;
@@ -505,6 +527,7 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   params.kb_per_split = params.k_blocks;
   params.b_mn = b_mn;
   params.group_offsets = offsets;
+  params.group_b_index = group_b_index;
   params.groups = groups;
   params.act_silu = activation;
   // The tile count depends on the device-side offsets; bound it from above
@@ -801,6 +824,30 @@ int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permut
                                                    static_cast<const uint16_t*>(residual), tokens, top_k, d, out);
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
+}
+
+int b200gemm_lmhead_ce_forward_shard(b200gemm_handle_t h, void* stream, const void* hidden,
+                                     const void* weight_shard, int32_t w_layout,
+                                     const int32_t* local_targets, int64_t m, int64_t k, int64_t v_local,
+                                     int64_t classes_local, float* row_max, float* row_sum,
+                                     float* row_target_logit, void* workspace, size_t workspace_bytes) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  const CeShardOut out = {row_max, row_sum, row_target_logit};
+  return ce_forward(h, static_cast<cudaStream_t>(stream), hidden, weight_shard, w_layout, local_targets, m,
+                    k, v_local, classes_local, nullptr, nullptr, nullptr, workspace, workspace_bytes, &out);
+}
+
+int b200gemm_grouped_gemm_indexed(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                  const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b,
+                                  int32_t b_count, const int32_t* group_b_index, void* c, int64_t ldc,
+                                  const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
+                                  int64_t k, int32_t activation) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!group_b_index) return fail(B200GEMM_ERR_INVALID, "null group index");
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, c,
+                      ldc, offsets, groups, total_rows, n, k, activation, group_b_index, b_count);
 }
 
 int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream, const void* hidden,

@@ -60,4 +60,26 @@ __global__ void __launch_bounds__(256) ce_combine_kernel(const float2* __restric
   }
 }
 
+// Vocabulary-sharded form: merge the chunks of THIS shard only and hand back the
+// shard's (max, sum-exp relative to that max, target logit) per row; the caller
+// combines shards (max-reduce, rescaled sum-reduce, sum of target logits).
+__global__ void __launch_bounds__(256) ce_partial_kernel(const float2* __restrict__ partials,
+                                                         const float* __restrict__ target_logit,
+                                                         int m, int chunks, float* __restrict__ row_max,
+                                                         float* __restrict__ row_sum,
+                                                         float* __restrict__ row_target_logit) {
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < m; row += gridDim.x * blockDim.x) {
+    float mx = -INFINITY;
+    for (int c = 0; c < chunks; ++c) mx = fmaxf(mx, partials[static_cast<size_t>(c) * m + row].x);
+    float sum = 0.f;
+    for (int c = 0; c < chunks; ++c) {
+      const float2 ps = partials[static_cast<size_t>(c) * m + row];
+      sum += ps.y * expf(ps.x - mx);
+    }
+    row_max[row] = mx;
+    row_sum[row] = sum;
+    row_target_logit[row] = target_logit[row];
+  }
+}
+
 }  // namespace b200

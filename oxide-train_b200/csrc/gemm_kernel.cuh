@@ -120,7 +120,8 @@ struct GemmParams {
   int ce_classes;      // columns at or beyond this index are padding
   int ce_chunks;       // kSchedCeForward: vocabulary chunks per row block
   // ---- grouped (ragged) rows
-  const int* group_offsets;  // [groups + 1] first row of each group; rows of group g use B[g]
+  const int* group_offsets;  // [groups + 1] first row of each group
+  const int* group_b_index;  // [groups] which B matrix group g multiplies; null = g itself
   int groups;
   int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
 #ifdef B200_PROBE
@@ -197,7 +198,7 @@ struct TileWalk {
       int tm = item - tn * total_m;
       int g = 0;
       while (g + 1 < p.groups && group_tile_start[g + 1] <= tm) ++g;
-      t.batch = g;
+      t.batch = p.group_b_index ? p.group_b_index[g] : g;
       t.m0 = p.group_offsets[g] + (tm - group_tile_start[g]) * kTileM;
       t.m_end = p.group_offsets[g + 1];
       t.tile_n = tn;

@@ -1,0 +1,307 @@
+"""The three places the GEMM path shards across the GPUs of one box.
+
+The reference is single-GPU (SPEC.md:15); these are new.  One process per GPU,
+``torch.distributed`` (NCCL over NVLink / NVSwitch) for the exchange steps, the
+kernels of this package for the compute.  Each class keeps its exchange logic
+in plain tensor code that also runs on CPU tensors over the ``gloo`` backend;
+the compute is reached through a small ``ops`` object so that tests can stand
+in a CPU implementation for it.
+
+* :class:`VocabParallelHead` — fused lm-head + cross-entropy with the vocabulary
+  split over ranks; one MAX and one SUM all-reduce of per-row statistics in the
+  forward, a SUM all-reduce of ``d_hidden`` in the backward.
+* :class:`ExpertParallelMoe` — experts split over ranks, tokens split over
+  ranks; counts exchange, all-to-all dispatch, grouped expert GEMMs on the rows
+  received, all-to-all combine.
+* :class:`TensorParallelMlp` — column-parallel up, row-parallel down,
+  reduce-scatter of the partial outputs, chunked so that the collective of one
+  chunk overlaps the GEMMs of the next.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+TILE_N = 256
+
+
+# --------------------------------------------------------------------------- compute back end
+
+class DeviceOps:
+    """The package's kernels, as the parallel classes call them."""
+
+    def __init__(self, gemm):
+        from . import moe as _moe
+        from .lmhead import FusedLmHead
+        self.gemm = gemm
+        self._moe = _moe
+        self._FusedLmHead = FusedLmHead
+
+    # lm-head shard
+    def head_forward_shard(self, hidden, weight_shard, local_targets, classes_local, w_layout):
+        import ctypes as C
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        m, k = hidden.shape
+        v_local = weight_shard.shape[1] if w_layout == "in_out" else weight_shard.shape[0]
+        dev = hidden.device
+        need = self.gemm._lib.b200gemm_lmhead_ce_workspace_bytes(m)
+        if getattr(self, "_ws", None) is None or self._ws.numel() < need:
+            self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
+        out = [torch.empty(m, dtype=torch.float32, device=dev) for _ in range(3)]
+        L.check(self.gemm._lib.b200gemm_lmhead_ce_forward_shard(
+            self.gemm._h, _stream_ptr(), hidden.data_ptr(), weight_shard.data_ptr(),
+            L.MN_MAJOR if w_layout == "in_out" else L.K_MAJOR, local_targets.data_ptr(), m, k, v_local,
+            classes_local, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
+            self._ws.data_ptr(), self._ws.numel()))
+        return tuple(out)
+
+    def head_backward_shard(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy,
+                            d_weight, accumulate_dw):
+        head = self._FusedLmHead(self.gemm, classes_local, w_layout)
+        return head.backward(hidden, weight_shard, local_targets, lse, dy=dy, d_weight=d_weight,
+                             accumulate_dw=accumulate_dw)
+
+    # MoE
+    def route(self, scores, top_k, scores_are_logits):
+        return self._moe.route(self.gemm, scores, top_k, scores_are_logits=scores_are_logits)
+
+    def scatter(self, x, routing):
+        return self._moe.scatter(self.gemm, x, routing)
+
+    def combine(self, y_permuted, routing, residual, out_dtype):
+        return self._moe.combine(self.gemm, y_permuted, routing, residual, out_dtype)
+
+    def grouped_indexed(self, a, b, offsets, group_b_index, silu):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        rows, k = a.shape
+        n = b.shape[2]                                  # b is [experts_local, k, n]
+        out = torch.zeros((rows, n), dtype=torch.bfloat16, device=a.device)
+        if rows == 0:
+            return out
+        L.check(self.gemm._lib.b200gemm_grouped_gemm_indexed(
+            self.gemm._h, _stream_ptr(), a.data_ptr(), a.stride(0), b.data_ptr(), L.MN_MAJOR,
+            b.stride(1), b.stride(0), b.shape[0], group_b_index.data_ptr(), out.data_ptr(),
+            out.stride(0), offsets.data_ptr(), group_b_index.numel(), rows, n, k, int(silu)))
+        return out
+
+    # dense GEMMs (weights are [IN, OUT], read in place)
+    def linear(self, x, w, out_dtype=torch.bfloat16):
+        y = torch.empty((x.shape[0], w.shape[1]), dtype=out_dtype, device=x.device)
+        self.gemm.gemm(x, w, y, transposed_b=True)
+        return y
+
+    def linear_input_grad(self, dy, w, out_dtype=torch.bfloat16):
+        dx = torch.empty((dy.shape[0], w.shape[0]), dtype=out_dtype, device=dy.device)
+        self.gemm.gemm(dy, w, dx)
+        return dx
+
+    def linear_weight_grad(self, x, dy, dw):
+        self.gemm.f32_accumulate_transposed(x, dy, dw)
+
+
+def _world(group):
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+# --------------------------------------------------------------------------- vocabulary-parallel head
+
+def vocab_shards(vocab_padded: int, world: int, tile: int = TILE_N):
+    """Column ranges ``[(c0, c1), ...]`` per rank: whole 256-column tiles, as even as they come.
+
+    50432 columns are 197 tiles; over 8 ranks that is 25, 25, 25, 25, 25, 24, 24, 24."""
+    tiles = (vocab_padded + tile - 1) // tile
+    base, rem = divmod(tiles, world)
+    out, c = [], 0
+    for r in range(world):
+        n = (base + (1 if r < rem else 0)) * tile
+        out.append((min(c, vocab_padded), min(c + n, vocab_padded)))
+        c += n
+    return out
+
+
+def merge_softmax_stats(row_max, row_sum, row_target_logit, group=None):
+    """All-reduce the shards' per-row statistics into ``(lse, row_loss, mean_loss)``.
+
+    One MAX all-reduce of ``row_max`` and one SUM all-reduce of the rescaled sums
+    stacked with the target logits (2 x rows floats)."""
+    gmax = row_max.clone()
+    dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+    packed = torch.stack([row_sum * torch.exp(row_max - gmax), row_target_logit])
+    dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
+    lse = gmax + torch.log(packed[0])
+    row_loss = lse - packed[1]
+    return lse, row_loss, row_loss.double().mean().float()
+
+
+class VocabParallelHead:
+    def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out"):
+        self.ops, self.group, self.w_layout = ops, group, w_layout
+        self.world, self.rank = _world(group)
+        self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
+        self.classes_local = max(0, min(classes, self.c1) - self.c0)
+
+    def shard_weight(self, weight_full):
+        """This rank's columns of a full ``[hidden, vocab_padded]`` weight (a copy)."""
+        if self.w_layout == "in_out":
+            return weight_full[:, self.c0:self.c1].contiguous()
+        return weight_full[self.c0:self.c1].contiguous()
+
+    def local_targets(self, targets):
+        return (targets - self.c0).to(torch.int32)
+
+    def forward(self, hidden, weight_shard, targets):
+        lt = self.local_targets(targets)
+        stats = self.ops.head_forward_shard(hidden, weight_shard, lt, self.classes_local, self.w_layout)
+        lse, row_loss, loss = merge_softmax_stats(*stats, group=self.group)
+        return loss, lse, row_loss
+
+    def backward(self, hidden, weight_shard, targets, lse, dy: float = 1.0, d_weight=None,
+                 accumulate_dw: bool = False):
+        """Returns ``(dlogits shard, d_hidden summed over shards, d_weight shard)``."""
+        lt = self.local_targets(targets)
+        dl, dh, dw = self.ops.head_backward_shard(hidden, weight_shard, lt, lse, self.classes_local,
+                                                  self.w_layout, dy, d_weight, accumulate_dw)
+        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+        return dl, dh, dw
+
+
+# --------------------------------------------------------------------------- expert-parallel MoE
+
+def exchange_counts(counts_by_expert, world, group=None):
+    """``counts_by_expert`` [experts] (rows this rank routes to every expert) ->
+    ``(send_counts [world, local], recv_counts [world, local])``; ``recv_counts[s, e]`` is
+    the number of rows rank ``s`` sends to this rank's local expert ``e``."""
+    local = counts_by_expert.numel() // world
+    send = counts_by_expert.reshape(world, local).to(torch.int64).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return send, recv
+
+
+def received_groups(recv_counts):
+    """Groups of the received rows, one per (source rank, local expert), in arrival order:
+    ``(offsets int32 [groups + 1], group_b_index int32 [groups])``."""
+    world, local = recv_counts.shape
+    flat = recv_counts.reshape(-1)
+    offsets = torch.zeros(flat.numel() + 1, dtype=torch.int32, device=flat.device)
+    offsets[1:] = torch.cumsum(flat, 0).to(torch.int32)
+    index = torch.arange(local, dtype=torch.int32, device=flat.device).repeat(world)
+    return offsets, index
+
+
+class ExpertParallelMoe:
+    """``y = combine(down(silu(up(dispatch(x)))))`` with experts and tokens split over ranks.
+
+    ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
+
+    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None):
+        self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
+        self.world, self.rank = _world(group)
+        if experts % self.world:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.w_up, self.w_down = w_up_local, w_down_local
+        self.last = {}
+
+    def forward(self, x, scores, scores_are_logits=False, residual=None, out_dtype=torch.float32):
+        r = self.ops.route(scores, self.top_k, scores_are_logits)
+        xp = self.ops.scatter(x, r)                       # rows sorted by (global) expert = by owner rank
+        send, recv = exchange_counts(r.accepted_counts, self.world, self.group)
+        send_splits = send.sum(1).tolist()                # the one host sync of the step
+        recv_splits = recv.sum(1).tolist()
+        rows_in = int(sum(recv_splits))
+        recv_x = torch.empty((rows_in, x.shape[1]), dtype=xp.dtype, device=xp.device)
+        dist.all_to_all_single(recv_x, xp, output_split_sizes=recv_splits, input_split_sizes=send_splits,
+                               group=self.group)
+        offsets, index = received_groups(recv)
+        hidden = self.ops.grouped_indexed(recv_x, self.w_up, offsets, index, True)
+        y = self.ops.grouped_indexed(hidden, self.w_down, offsets, index, False)
+        yp = torch.empty((xp.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
+        dist.all_to_all_single(yp, y, output_split_sizes=send_splits, input_split_sizes=recv_splits,
+                               group=self.group)
+        self.last = {"rows_received": rows_in, "rows_sent": int(sum(send_splits)), "routing": r}
+        return self.ops.combine(yp, r, residual, out_dtype)
+
+
+# --------------------------------------------------------------------------- tensor-parallel MLP
+
+class TensorParallelMlp:
+    """Column-parallel ``up`` ([d, ff / world]) and row-parallel ``down`` ([ff / world, d]).
+
+    ``forward`` takes the replicated ``x [m, d]`` and returns this rank's rows of
+    ``y = (x . W_up) . W_down`` after a reduce-scatter.  Rows are processed in
+    ``chunks`` pieces; the reduce-scatter of a piece runs on a side stream while
+    the next piece's GEMMs run, and rank ``r`` ends up owning rows
+    ``[c * m/chunks + r * m/(chunks*world), ...)`` of every piece ``c``."""
+
+    def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks: int = 4,
+                 partial_dtype=torch.bfloat16):
+        self.ops, self.group, self.chunks = ops, group, chunks
+        self.world, self.rank = _world(group)
+        self.w_up, self.w_down = w_up_shard, w_down_shard
+        self.partial_dtype = partial_dtype
+        self._comm_stream = None
+
+    def _side_stream(self, device):
+        if device.type != "cuda":
+            return None
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=device)
+        return self._comm_stream
+
+    def owned_rows(self, m: int):
+        """Global row indices this rank holds after ``forward`` (in output order)."""
+        piece = m // self.chunks
+        share = piece // self.world
+        idx = [torch.arange(c * piece + self.rank * share, c * piece + (self.rank + 1) * share)
+               for c in range(self.chunks)]
+        return torch.cat(idx)
+
+    def forward(self, x):
+        m, d = x.shape[0], self.w_down.shape[1]
+        if m % (self.chunks * self.world):
+            raise ValueError("rows must divide by chunks * world")
+        piece, share = m // self.chunks, m // (self.chunks * self.world)
+        out = torch.empty((self.chunks * share, d), dtype=self.partial_dtype, device=x.device)
+        side = self._side_stream(x.device)
+        self._hidden = []
+        partials = []
+        for c in range(self.chunks):
+            xs = x[c * piece:(c + 1) * piece]
+            h = self.ops.linear(xs, self.w_up, torch.bfloat16)
+            y = self.ops.linear(h, self.w_down, self.partial_dtype)
+            self._hidden.append(h)
+            partials.append(y)
+            dst = out[c * share:(c + 1) * share]
+            if side is None:
+                dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
+                y.record_stream(side)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        return out
+
+    def backward(self, x, dy_local, dw_up, dw_down):
+        """``dy_local`` is this rank's rows of dL/dy (layout of ``forward``'s output).
+
+        Accumulates the weight-gradient shards (fp32) and returns the full
+        ``dx [m, d]`` summed over ranks."""
+        m = x.shape[0]
+        piece, share = m // self.chunks, m // (self.chunks * self.world)
+        dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)
+        for c in range(self.chunks):
+            dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
+            dist.all_gather_into_tensor(dy, dy_local[c * share:(c + 1) * share].contiguous(), group=self.group)
+            h = self._hidden[c]
+            self.ops.linear_weight_grad(h, dy, dw_down)                   # dW_down += h^T dy
+            dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16)   # dh = dy W_down^T
+            xs = x[c * piece:(c + 1) * piece]
+            self.ops.linear_weight_grad(xs, dh, dw_up)                    # dW_up += x^T dh
+            dxs = self.ops.linear_input_grad(dh, self.w_up, self.partial_dtype)
+            dx[c * piece:(c + 1) * piece] = dxs
+        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=self.group)
+        return dx
