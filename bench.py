@@ -7,7 +7,8 @@ Workload (one "step"): every GEMM of one training step of the dense model
 B=32, T=1024 (M=32768 tokens), D=1536, FF=4096, 12 layers, lm-head 1536->50432:
 per layer the four forward projections (QKV, attention-out, MLP up, MLP down),
 their four input gradients and their four weight gradients (K = 32768 tokens,
-split-K), plus the lm-head trio.  Inputs are seeded synthetic tensors with the
+split-K), plus the lm-head fused with the softmax cross-entropy classifier (forward, and a
+backward that recomputes the logits; the recompute is not credited as FLOPs).  Inputs are seeded synthetic tensors with the
 shapes and value distributions the model has (activations ~N(0,1), weights
 ~N(0,0.02), upstream gradients ~N(0,1e-2)), bf16 operands, fp32 accumulation.
 
@@ -188,23 +189,25 @@ class StepBuffers:
                   for o in (D_MODEL, 3 * D_MODEL, D_FF)}
         self.head_w = rnd((D_MODEL, VOCAB_PAD), 0.02)
         self.head_dw = torch.zeros((D_MODEL, VOCAB_PAD), device=device, dtype=f32)
-        self.logits = torch.empty((M_TOKENS, VOCAB_PAD), device=device, dtype=bf)
+        self.dlogits = torch.empty((M_TOKENS, VOCAB_PAD), device=device, dtype=bf)
         self.dh = torch.empty((M_TOKENS, D_MODEL), device=device, dtype=f32)
+        self.targets = torch.randint(0, VOCAB, (M_TOKENS,), generator=g, device=device, dtype=torch.int32)
+        self.loss = None
 
 
-def run_step(gemm, buf):
-    """One pass over the step's GEMMs.  Returns the number of GEMM launches."""
+def run_step(gemm, head, buf):
+    """One pass over the step's GEMMs.  Returns the number of kernel launches of this library."""
     n = 0
     for layer in buf.layers:                       # forward
         for name, i, o in PROJECTIONS:
             gemm.f32_store(buf.x[i], layer[name]["w"], buf.y[o], transposed_b=True)   # y = x W
             n += 1
-    # lm-head forward: logits = h W
-    gemm.store(buf.x[D_MODEL], buf.head_w, buf.logits, transposed_b=True)
-    # lm-head backward: dW += h^T dlogits ; dh = dlogits W^T
-    gemm.f32_accumulate_transposed(buf.x[D_MODEL], buf.logits, buf.head_dw)
-    gemm.f32_store(buf.logits, buf.head_w, buf.dh)
-    n += 3
+    # lm-head fused with the classifier: the [tokens, vocab] logits never reach HBM.
+    buf.loss, lse, _ = head.forward(buf.x[D_MODEL], buf.head_w, buf.targets)          # GEMM + merge kernel
+    # backward: logits recomputed into bf16 dlogits, then dh = dlogits W^T and dW += h^T dlogits
+    head.backward(buf.x[D_MODEL], buf.head_w, buf.targets, lse, dlogits=buf.dlogits, d_hidden=buf.dh,
+                  d_weight=buf.head_dw, accumulate_dw=True)
+    n += 5
     for layer in reversed(buf.layers):             # backward
         for name, i, o in reversed(PROJECTIONS):
             gemm.f32_accumulate_transposed(buf.x[i], buf.dy[o], layer[name]["dw"])   # dW += x^T dy
@@ -213,7 +216,7 @@ def run_step(gemm, buf):
     return n
 
 
-def per_shape_table(torch, gemm, buf, iters=3):
+def per_shape_table(torch, gemm, head, buf, iters=3):
     """TFLOP/s of every distinct GEMM of the step, timed alone (reported, not the headline)."""
     rows = []
     layer = buf.layers[0]
@@ -241,12 +244,15 @@ def per_shape_table(torch, gemm, buf, iters=3):
             ms, tf = timed(fn, fl)
             rows.append({"gemm": f"{name}.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
     fl = 2.0 * M_TOKENS * D_MODEL * VOCAB_PAD
-    for kind, fn in (
-        ("forward", lambda: gemm.store(buf.x[D_MODEL], buf.head_w, buf.logits, transposed_b=True)),
-        ("weight_grad", lambda: gemm.f32_accumulate_transposed(buf.x[D_MODEL], buf.logits, buf.head_dw)),
-        ("input_grad", lambda: gemm.f32_store(buf.logits, buf.head_w, buf.dh)),
+    lse = head.forward(buf.x[D_MODEL], buf.head_w, buf.targets)[1]
+    for kind, fn, credit in (
+        ("fused_forward", lambda: head.forward(buf.x[D_MODEL], buf.head_w, buf.targets), fl),
+        # recompute + two gradient products; only the two products are credited
+        ("fused_backward", lambda: head.backward(buf.x[D_MODEL], buf.head_w, buf.targets, lse,
+                                                 dlogits=buf.dlogits, d_hidden=buf.dh,
+                                                 d_weight=buf.head_dw, accumulate_dw=True), 2 * fl),
     ):
-        ms, tf = timed(fn, fl)
+        ms, tf = timed(fn, credit)
         rows.append({"gemm": f"lm_head.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
     return rows
 
@@ -312,6 +318,7 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
     pkg = entry.load_package()
     gemm = pkg.Tcgen05Gemm(local)
+    head = pkg.FusedLmHead(gemm, VOCAB, "in_out")
     buf = StepBuffers(torch, device, seed=rank)
 
     def barrier():
@@ -321,7 +328,7 @@ def run_gpu(args):
 
     # ---- device-resident timing -------------------------------------------------
     for _ in range(max(args.warmup, 3)):
-        launches = run_step(gemm, buf)
+        launches = run_step(gemm, head, buf)
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
@@ -329,7 +336,7 @@ def run_gpu(args):
     barrier()
     start.record()
     for _ in range(args.steps):
-        run_step(gemm, buf)
+        run_step(gemm, head, buf)
     stop.record()
     barrier()
     clocks = sampler.stop()
@@ -344,8 +351,8 @@ def run_gpu(args):
 
     def e2e_step():
         buf.x[D_MODEL].copy_(host_x, non_blocking=True)         # this step's token activations
-        run_step(gemm, buf)
-        host_out.copy_(buf.dh.view(-1)[:1], non_blocking=True)  # one word of the step's last result
+        run_step(gemm, head, buf)
+        host_out.copy_(buf.loss, non_blocking=True)             # the step's loss
         torch.cuda.current_stream().synchronize()
 
     e2e_step()
@@ -386,7 +393,7 @@ def run_gpu(args):
     }
     if rank == 0:
         if not args.no_table:
-            line["per_shape"] = per_shape_table(torch, gemm, buf)
+            line["per_shape"] = per_shape_table(torch, gemm, head, buf)
         if world == 1 and not args.no_cpu:
             secs, fl, text = cpu_sample(1)
             line["cpu_baseline"] = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",

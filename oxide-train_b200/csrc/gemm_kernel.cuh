@@ -465,7 +465,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         int target = -1;
         if constexpr (kEpi == kEpiCeBackward) {
           if (row < p.m) {
-            neg_lse2 = -p.ce_lse[row] * kLog2e;
+            neg_lse2 = log2f(fabsf(p.ce_scale)) - p.ce_lse[row] * kLog2e;   // sign applied below
             target = p.targets[row];
           }
         }
@@ -482,14 +482,27 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
             tmem_ld_32x32(t_acc + c * 64 + h * 32, r);
             tmem_ld_wait();
             if constexpr (kEpi == kEpiCeBackward) {
+              // scale * exp(logit - lse) = exp2(logit*log2e + (log2(scale) - lse*log2e)): one
+              // FMA and one ex2 per element; the target and the padding mask are
+              // handled only in the 32-column chunk they fall into.
               const int cbase = col0 + c * 64 + h * 32;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int col = cbase + j;
-                float g = p.ce_scale * fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, neg_lse2));
-                if (col == target) g -= p.ce_scale;
-                if (col >= p.ce_classes) g = 0.f;
-                r[j] = __float_as_uint(g);
+              for (int j = 0; j < 32; ++j)
+                r[j] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, neg_lse2)));
+              if (p.ce_scale < 0.f) {               // uniform: a negative upstream gradient
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] ^= 0x80000000u;
+              }
+              const unsigned target_off = static_cast<unsigned>(target - cbase);
+              if (target_off < 32u) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (static_cast<unsigned>(j) == target_off) r[j] = __float_as_uint(__uint_as_float(r[j]) - p.ce_scale);
+              }
+              if (cbase + 32 > p.ce_classes) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (cbase + j >= p.ce_classes) r[j] = 0u;
               }
             }
             if constexpr (kEpi == kEpiBf16Grouped) {
@@ -553,21 +566,34 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           tmem_ld_32x32(t_acc + c * 32, r);
           tmem_ld_wait();
           if (c == kChunks - 1) release_accumulator();
-          float cmax = -INFINITY;
+          // Padding can only start inside the last real chunk; everywhere else the
+          // mask is skipped.  The target column is looked for only in its own chunk.
+          if (cbase + 32 > p.ce_classes) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (cbase + j >= p.ce_classes) v = -INFINITY;
-            if (cbase + j == target) { target_logit = v; have_target = true; }
-            r[j] = __float_as_uint(v);
-            cmax = fmaxf(cmax, v);
+            for (int j = 0; j < 32; ++j)
+              if (cbase + j >= p.ce_classes) r[j] = __float_as_uint(-INFINITY);
           }
+          const unsigned target_off = static_cast<unsigned>(target - cbase);
+          if (target_off < 32u) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (static_cast<unsigned>(j) == target_off) target_logit = __uint_as_float(r[j]);
+            have_target = true;
+          }
+          // Four independent chains each for the max and for the sum: one warp per
+          // scheduler has no other warp to hide a 32-long dependent chain behind.
+          float mx[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) mx[q] = __uint_as_float(r[q]);
+#pragma unroll
+          for (int j = 4; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r[j]));
+          const float cmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           const float new_max = fmaxf(run_max, cmax);
           const float m2 = new_max * kLog2e;
-          float s = 0.f;
+          float sm[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int j = 0; j < 32; ++j) s += fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, -m2));
-          run_sum = run_sum * fast_exp2((run_max - new_max) * kLog2e) + s;
+          for (int j = 0; j < 32; ++j) sm[j & 3] += fast_exp2(fmaf(__uint_as_float(r[j]), kLog2e, -m2));
+          run_sum = run_sum * fast_exp2((run_max - new_max) * kLog2e) + ((sm[0] + sm[1]) + (sm[2] + sm[3]));
           run_max = new_max;
         }
         if (t.last && row < p.m) {

@@ -1,0 +1,115 @@
+"""The sharded paths on real GPUs: 2 ranks over NCCL, compared with the same
+computation done by the single-GPU kernels on each rank.  Needs two GPUs; skips
+itself otherwise.  Child processes, NVLS off, ranks leave only between steps."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORLD = 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, port, failures):
+    try:
+        import torch
+        import torch.distributed as dist
+        sys.path.insert(0, ROOT)
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
+        import __graft_entry__ as entry
+        pkg = entry.load_package()
+        par = pkg.parallel
+        gemm = pkg.Tcgen05Gemm(rank)
+        ops = par.DeviceOps(gemm)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(5)                                   # same data on every rank
+        bf = torch.bfloat16
+
+        # ---- vocabulary-parallel head vs the single-GPU fused head
+        m, k, v, classes = 1024, 256, 2048, 2000
+        h = torch.randn((m, k), generator=gen, device=dev).to(bf)
+        w = (torch.randn((k, v), generator=gen, device=dev) * 0.2).to(bf)
+        t = torch.randint(0, classes, (m,), generator=gen, device=dev, dtype=torch.int32)
+        single = pkg.FusedLmHead(gemm, classes, "in_out")
+        loss1, lse1, row1 = single.forward(h, w, t)
+        _, dh1, dw1 = single.backward(h, w, t, lse1)
+        head = par.VocabParallelHead(ops, classes, v)
+        ws = head.shard_weight(w)
+        loss2, lse2, row2 = head.forward(h, ws, t)
+        assert abs(float(loss1.item()) - float(loss2.item())) < 5e-5
+        assert torch.allclose(lse1, lse2, atol=2e-4, rtol=1e-5)
+        _, dh2, dw2 = head.backward(h, ws, t, lse2)
+        assert torch.allclose(dh1, dh2, atol=2e-5, rtol=2e-2), float((dh1 - dh2).abs().max())
+        assert torch.allclose(dw1[:, head.c0:head.c1], dw2, atol=2e-5, rtol=2e-2)
+
+        # ---- expert-parallel MoE vs the single-GPU grouped path on this rank's tokens
+        n_local, d, ff, experts, top_k = 512, 256, 384, 8, 2
+        x = torch.randn((WORLD, n_local, d), generator=gen, device=dev).to(bf)
+        up = (torch.randn((experts, d, ff), generator=gen, device=dev) * 0.1).to(bf)
+        dn = (torch.randn((experts, ff, d), generator=gen, device=dev) * 0.1).to(bf)
+        logits = torch.randn((WORLD, n_local, experts), generator=gen, device=dev)
+        ref, _ = pkg.GroupedExpertFfn(gemm, up, dn).forward(x[rank].contiguous(), logits[rank].contiguous(),
+                                                             top_k, scores_are_logits=True)
+        local = experts // WORLD
+        ep = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                   dn[rank * local:(rank + 1) * local].contiguous())
+        out = ep.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+        assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5), float((out - ref).abs().max())
+
+        # ---- tensor-parallel MLP vs the unsharded product of the same bf16 operands
+        m, d, ff = 2048, 512, 1024
+        x2 = torch.randn((m, d), generator=gen, device=dev).to(bf)
+        w1 = (torch.randn((d, ff), generator=gen, device=dev) * 0.05).to(bf)
+        w2 = (torch.randn((ff, d), generator=gen, device=dev) * 0.05).to(bf)
+        cols = slice(rank * ff // WORLD, (rank + 1) * ff // WORLD)
+        mlp = par.TensorParallelMlp(ops, w1[:, cols].contiguous(), w2[cols].contiguous(), chunks=2,
+                                    partial_dtype=torch.float32)
+        y = mlp.forward(x2)
+        hid = ops.linear(x2, w1)                               # bf16 hidden, as each shard rounds it
+        full = hid.float() @ w2.float()
+        rows = mlp.owned_rows(m).to(dev)
+        assert torch.allclose(y, full[rows], atol=2e-3, rtol=2e-2), float((y - full[rows]).abs().max())
+        assert gemm.device_status() == 0
+        dist.barrier()
+        torch.cuda.synchronize()
+        gemm.close()
+        dist.destroy_process_group()
+    except Exception:
+        failures.put(f"rank {rank}:\n{traceback.format_exc()}")
+        raise
+
+
+def test_sharded_paths_on_two_gpus():
+    import torch
+    if torch.cuda.device_count() < WORLD:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, port, failures)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            msgs.append("a rank did not finish in time")
+    assert not msgs, "\n".join(msgs)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
