@@ -257,6 +257,173 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
     return rows
 
 
+
+# ---- the sharded workloads (BASELINE configs[2], [3], [4]) ------------------------
+
+def run_sharded(args):
+    """`--workload lmhead | moe | tp_mlp`: the paths that shard over the GPUs of one box.
+
+    Strong scaling: the problem is the BASELINE configuration whatever N is; each
+    rank holds its shard.  Prints one JSON line (rank 0)."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        if world == 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29517")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    pkg = entry.load_package()
+    par = pkg.parallel
+    gemm = pkg.Tcgen05Gemm(local)
+    ops = par.DeviceOps(gemm)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1)                                    # replicated operands: same seed on every rank
+    bf, f32 = torch.bfloat16, torch.float32
+
+    def rnd(shape, std, g=gen):
+        return (torch.randn(shape, generator=g, device=dev, dtype=f32) * std).to(bf)
+
+    if args.workload == "lmhead":
+        m, k, v, classes = M_TOKENS, D_MODEL, VOCAB_PAD, VOCAB
+        head = par.VocabParallelHead(ops, classes, v)
+        hidden = rnd((m, k), 1.0)
+        w_shard = rnd((k, head.c1 - head.c0), 0.02)
+        targets = torch.randint(0, classes, (m,), generator=gen, device=dev, dtype=torch.int32)
+        dw = torch.zeros((k, head.c1 - head.c0), device=dev, dtype=f32)
+        result = {}
+
+        def step():
+            loss, lse, _ = head.forward(hidden, w_shard, targets)
+            head.backward(hidden, w_shard, targets, lse, d_weight=dw, accumulate_dw=True)
+            result["loss"] = loss
+            return 5
+
+        flops = 3 * 2.0 * m * k * v
+        name = ("fused lm-head + softmax cross-entropy (BASELINE configs[2]): M=32768 K=1536 V=50432 "
+                "(50257 classes), forward + backward; the backward's logit recompute is not credited")
+        par_text = f"vocabulary split over {world} GPU(s); all-reduce of row max / sum-exp and of d_hidden"
+        host_in = (hidden, None)
+    elif args.workload == "moe":
+        n_tok, d, ff, experts, top_k = 32768, 1536, 768, 64, 8
+        n_local, e_local = n_tok // world, experts // world
+        grank = torch.Generator(device=dev)
+        grank.manual_seed(100 + rank)                     # each rank has its own tokens
+        x = rnd((n_local, d), 1.0, grank)
+        bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
+        logits = (torch.randn((n_local, experts), generator=grank, device=dev) + bias).contiguous()
+        w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
+        w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
+        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn)
+        result = {}
+
+        def step():
+            result["out"] = ep.forward(x, logits, scores_are_logits=True)
+            return 9
+
+        flops = 2.0 * n_tok * top_k * d * ff * 2
+        name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens, D=1536, E=64, top-8, expert FF=768, "
+                "up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
+        par_text = f"experts and tokens split over {world} GPU(s); all-to-all dispatch and combine"
+        host_in = (x, None)
+    else:
+        m, d, ff = 65536, 4096, 16384
+        cols = ff // world
+        x = rnd((m, d), 1.0)
+        w1 = rnd((d, cols), 0.015)
+        w2 = rnd((cols, d), 0.015)
+        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=4, partial_dtype=bf)
+        dy_local = rnd((m // world, d), 0.01)
+        dw1 = torch.zeros((d, cols), device=dev, dtype=f32)
+        dw2 = torch.zeros((cols, d), device=dev, dtype=f32)
+        result = {}
+
+        def step():
+            result["out"] = mlp.forward(x)
+            result["dx"] = mlp.backward(x, dy_local, dw1, dw2)
+            return 6 * 4
+
+        flops = 6 * 2.0 * m * d * ff
+        name = ("tensor-parallel MLP block (BASELINE configs[4]): M=65536 D=4096 FF=16384, column-parallel up, "
+                "row-parallel down, forward + input and weight gradients (K=65536 split-K)")
+        par_text = f"FF split over {world} GPU(s); reduce-scatter of the partial outputs, all-reduce of dx"
+        host_in = (x, None)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        launches = step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s0.record()
+    for _ in range(args.steps):
+        step()
+    e0.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = s0.elapsed_time(e0) / args.steps
+    # end to end: this step's activations from pinned host memory, one result word back
+    src = host_in[0]
+    host_x = torch.empty(src.shape, dtype=src.dtype).pin_memory()
+    host_x.copy_(src.cpu())
+    host_out = torch.empty(1, dtype=f32).pin_memory()
+
+    def e2e_step():
+        src.copy_(host_x, non_blocking=True)
+        step()
+        word = result.get("loss")
+        if word is None:
+            word = next(iter(result.values())).reshape(-1)[:1].float()
+        host_out.copy_(word, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_step()
+    barrier()
+    s1, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s1.record()
+    n_e2e = max(1, min(args.steps, 5))
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = s1.elapsed_time(e1) / n_e2e
+    tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = tt.tolist()
+    status = gemm.device_status()
+    peaks = measured_peaks()
+    value = flops / (ms * 1e-3) / 1e12
+    line = {
+        "metric": f"bf16_gemm_tflops_{args.workload}", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": name, "parallelism": par_text,
+                   "l2": "operands exceed the 126 MB L2"},
+        "pct_of_nominal_dense_peak": 100.0 * value / world / 2250.0,
+        "gpu_launches": launches * args.steps, "device_status": status, "clocks": clocks,
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": host_x.numel() * host_x.element_size(), "d2h_bytes_per_step": 4},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": value / world / peaks["tflops"], "traffic": None,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
+                     "algorithmic_flops_per_step": flops},
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    gemm.close()
+    dist.destroy_process_group()
+
 def run_only(args):
     """Profiling aid: launch ONE named GEMM of the step (e.g. qkv.forward) a few times.
 
@@ -415,11 +582,15 @@ def main():
     ap.add_argument("--only", default=None,
                     help="profiling aid: run one GEMM, e.g. qkv.forward, mlp_up.weight_grad, lm_head.input_grad")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
+    ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
+                    help="dense_step (default) is the headline; the others are the sharded configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.only:
         run_only(args)
+    elif args.workload != "dense_step":
+        run_sharded(args)
     else:
         run_gpu(args)
 

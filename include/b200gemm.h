@@ -260,7 +260,7 @@ B200GEMM_API int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, 
  *   offsets  DEVICE int32 [groups + 1], non-decreasing, offsets[groups] <= total_rows
  *            (the expert offsets the router produces; never read on the host)
  *   activation 0 = none, 1 = SiLU x*sigmoid(x) (crates/nn/src/swiglu.rs:22-28)
- * Rows of C outside every group are left untouched.  groups <= 256.
+ * Rows of C outside every group are left untouched.  groups <= 192.
  */
 B200GEMM_API int b200gemm_grouped_gemm(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
                                        const void* b, int32_t b_layout, int64_t ldb,

@@ -59,6 +59,8 @@ struct b200gemm_context {
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
   bool smem_opt_in[2][8] = {};   // [cta_group - 1][epilogue kind]
+  void* moe_scratch = nullptr;   // per-segment expert counts of b200gemm_moe_route
+  size_t moe_scratch_bytes = 0;
   std::mutex mu;
 };
 
@@ -653,6 +655,7 @@ int b200gemm_destroy(b200gemm_handle_t h) {
   cudaSetDevice(h->device);
   for (void* p : h->stage)
     if (p) cudaFree(p);
+  if (h->moe_scratch) cudaFree(h->moe_scratch);
   if (h->status) cudaFree(h->status);
   delete h;
   return B200GEMM_OK;
@@ -781,8 +784,29 @@ int b200gemm_moe_route(b200gemm_handle_t h, void* stream_, const float* scores,
   moe_topk_kernel<<<topk_blocks, 256, 0, stream>>>(scores, scores_are_logits, tokens, experts, top_k,
                                                    selected, gates);
   CUDA_TRY(cudaGetLastError());
-  moe_slot_kernel<<<experts, 256, 0, stream>>>(selected, pairs, capacity, slots, assignment_counts,
+  // Slot assignment in three passes over 256-pair segments.  The per-segment
+  // count table (segments x experts words) lives in scratch owned by the handle,
+  // grown on first use and whenever a larger problem arrives.
+  const long long segments = (pairs + kMoeSegment - 1) / kMoeSegment;
+  const size_t table_bytes = static_cast<size_t>(segments) * experts * sizeof(uint32_t);
+  {
+    std::lock_guard<std::mutex> lock(h->mu);
+    if (h->moe_scratch_bytes < table_bytes) {
+      if (h->moe_scratch) CUDA_TRY(cudaFree(h->moe_scratch));   // waits for kernels still using it
+      h->moe_scratch = nullptr;
+      h->moe_scratch_bytes = 0;
+      CUDA_TRY(cudaMalloc(&h->moe_scratch, table_bytes));
+      h->moe_scratch_bytes = table_bytes;
+    }
+  }
+  uint32_t* seg_table = static_cast<uint32_t*>(h->moe_scratch);
+  const int seg_blocks = static_cast<int>((segments + 7) / 8);
+  moe_hist_kernel<<<seg_blocks, 256, 0, stream>>>(selected, pairs, experts, seg_table);
+  CUDA_TRY(cudaGetLastError());
+  moe_scan_kernel<<<experts, 256, 0, stream>>>(seg_table, segments, experts, capacity, assignment_counts,
                                                accepted_counts);
+  CUDA_TRY(cudaGetLastError());
+  moe_assign_kernel<<<seg_blocks, 256, 0, stream>>>(selected, seg_table, pairs, experts, capacity, slots);
   CUDA_TRY(cudaGetLastError());
   moe_offsets_kernel<<<1, 32, 0, stream>>>(accepted_counts, experts, offsets);
   CUDA_TRY(cudaGetLastError());

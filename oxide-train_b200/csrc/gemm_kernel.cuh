@@ -69,7 +69,7 @@ constexpr int kTmemCols = 512;    // two 256-column fp32 accumulators
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 B, one per epilogue warp per buffer
 constexpr int kRasterGroupM = 8;  // tile rows walked together so B panels stay in L2
 constexpr int kSubtileBytes = 64 * kBlockK * 2;  // one 64(mn) x 64(k) MN-major box
-constexpr int kMaxGroups = 256;   // experts a grouped launch can address
+constexpr int kMaxGroups = 192;   // groups a grouped launch can address (its tables share the SM with a 225 KiB ring)
 
 enum EpilogueKind : int {
   kEpiF32Tma = 0,       // fp32 C through TMA: store, or reduce-add when p.reduce != 0
@@ -196,11 +196,18 @@ struct TileWalk {
       int total_m = group_tile_start[p.groups];
       int tn = item / total_m;
       int tm = item - tn * total_m;
-      int g = 0;
-      while (g + 1 < p.groups && group_tile_start[g + 1] <= tm) ++g;
+      // largest g with group_tile_start[g] <= tm (empty groups share a start and are skipped)
+      int lo = 0, hi = p.groups - 1;
+      while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (group_tile_start[mid] <= tm) lo = mid; else hi = mid - 1;
+      }
+      while (lo + 1 < p.groups && group_tile_start[lo + 1] <= tm) ++lo;
+      const int g = lo;
+      const int* group_row_start = group_tile_start + kMaxGroups + 1;   // offsets, staged in shared memory
       t.batch = p.group_b_index ? p.group_b_index[g] : g;
-      t.m0 = p.group_offsets[g] + (tm - group_tile_start[g]) * kTileM;
-      t.m_end = p.group_offsets[g + 1];
+      t.m0 = group_row_start[g] + (tm - group_tile_start[g]) * kTileM;
+      t.m_end = group_row_start[g + 1];
       t.tile_n = tn;
     }
     return true;
@@ -227,7 +234,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<kCtaGroup>;
   using Walk = TileWalk<kSched, Cfg::kTileM>;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ int group_tile_start[kSched == kSchedGrouped ? kMaxGroups + 1 : 1];
+  // kSchedGrouped: [0, groups]: first m-tile of each group; [kMaxGroups + 1, ...]: first row of each group
+  __shared__ int group_tile_start[kSched == kSchedGrouped ? 2 * (kMaxGroups + 1) : 1];
 
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
@@ -267,14 +275,18 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   }
   if constexpr (kSched == kSchedGrouped) {
     // Every CTA derives the same tile table from the offsets array.
-    if (warp == 3 && lane == 0) {
-      int run = 0;
-      for (int g = 0; g < p.groups; ++g) {
-        group_tile_start[g] = run;
-        int rows = p.group_offsets[g + 1] - p.group_offsets[g];
-        run += (max(rows, 0) + Cfg::kTileM - 1) / Cfg::kTileM;
+    if (warp == 3) {
+      for (int g = lane; g <= p.groups; g += 32) group_tile_start[kMaxGroups + 1 + g] = p.group_offsets[g];
+      __syncwarp();
+      if (lane == 0) {
+        int run = 0;
+        for (int g = 0; g < p.groups; ++g) {
+          group_tile_start[g] = run;
+          int rows = group_tile_start[kMaxGroups + 2 + g] - group_tile_start[kMaxGroups + 1 + g];
+          run += (max(rows, 0) + Cfg::kTileM - 1) / Cfg::kTileM;
+        }
+        group_tile_start[p.groups] = run;
       }
-      group_tile_start[p.groups] = run;
     }
   }
   if (warp == 2) {

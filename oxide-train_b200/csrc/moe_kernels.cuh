@@ -101,26 +101,43 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__
   }
 }
 
-// One block per expert walks every (token, rank) pair in order and hands out
-// slots by arrival (moe.rs:228-236): slot = number of earlier pairs routed to
-// the same expert; pairs beyond `capacity` are dropped.  Deterministic by
-// construction: no atomics decide an order.
-__global__ void __launch_bounds__(256) moe_slot_kernel(const uint32_t* __restrict__ selected,
-                                                       long long pairs, long long capacity,
-                                                       uint32_t* __restrict__ slots,
+// Slot assignment (moe.rs:228-236): slot = number of earlier (token, rank) pairs,
+// in flattened order, routed to the same expert; pairs beyond `capacity` are
+// dropped.  Three passes over segments of kMoeSegment consecutive pairs, one warp
+// per segment; no atomic ever decides an order, so the result is deterministic.
+constexpr int kMoeSegment = 256;   // pairs per warp
+
+// Pass 1: per-segment histogram over experts -> seg_counts[segment][experts].
+__global__ void __launch_bounds__(256) moe_hist_kernel(const uint32_t* __restrict__ selected,
+                                                       long long pairs, int experts,
+                                                       uint32_t* __restrict__ seg_counts) {
+  __shared__ unsigned hist[8][kMoeMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long seg = static_cast<long long>(blockIdx.x) * 8 + warp;
+  for (int e = lane; e < experts; e += 32) hist[warp][e] = 0;
+  __syncwarp();
+  const long long base = seg * kMoeSegment;
+  for (int i = lane; i < kMoeSegment; i += 32)
+    if (base + i < pairs) atomicAdd(&hist[warp][selected[base + i]], 1u);
+  __syncwarp();
+  if (base < pairs)
+    for (int e = lane; e < experts; e += 32) seg_counts[seg * experts + e] = hist[warp][e];
+}
+
+// Pass 2: one block per expert turns its column of seg_counts into exclusive
+// prefix sums (in place) and writes the expert's totals.
+__global__ void __launch_bounds__(256) moe_scan_kernel(uint32_t* __restrict__ seg_counts,
+                                                       long long segments, int experts,
+                                                       long long capacity,
                                                        uint32_t* __restrict__ assignment_counts,
                                                        uint32_t* __restrict__ accepted_counts) {
   __shared__ unsigned warp_totals[8];
-  const uint32_t expert = blockIdx.x;
+  const int expert = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned long long running = 0;
-  for (long long base = 0; base < pairs; base += 256 * 4) {
-    const long long q0 = base + static_cast<long long>(threadIdx.x) * 4;
-    unsigned flags = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (q0 + j < pairs && selected[q0 + j] == expert) flags |= 1u << j;
-    const unsigned mine = __popc(flags);
+  for (long long base = 0; base < segments; base += 256) {
+    const long long i = base + threadIdx.x;
+    const unsigned mine = i < segments ? seg_counts[i * experts + expert] : 0u;
     unsigned incl = mine;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -135,15 +152,7 @@ __global__ void __launch_bounds__(256) moe_slot_kernel(const uint32_t* __restric
       if (w < warp) warp_base += warp_totals[w];
       tile_total += warp_totals[w];
     }
-    unsigned long long slot = running + warp_base + (incl - mine);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if ((flags >> j) & 1u) {
-        slots[q0 + j] = slot < static_cast<unsigned long long>(capacity) ? static_cast<uint32_t>(slot)
-                                                                        : kMoeDropped;
-        ++slot;
-      }
-    }
+    if (i < segments) seg_counts[i * experts + expert] = static_cast<uint32_t>(running + warp_base + incl - mine);
     running += tile_total;
     __syncthreads();
   }
@@ -151,6 +160,36 @@ __global__ void __launch_bounds__(256) moe_slot_kernel(const uint32_t* __restric
     assignment_counts[expert] = static_cast<uint32_t>(running);
     accepted_counts[expert] = static_cast<uint32_t>(
         running < static_cast<unsigned long long>(capacity) ? running : capacity);
+  }
+}
+
+// Pass 3: each warp walks its segment in order, 32 pairs at a time; lanes routed
+// to the same expert rank themselves by lane index (match.any), on top of the
+// expert's running count for this segment.
+__global__ void __launch_bounds__(256) moe_assign_kernel(const uint32_t* __restrict__ selected,
+                                                         const uint32_t* __restrict__ seg_base,
+                                                         long long pairs, int experts,
+                                                         long long capacity,
+                                                         uint32_t* __restrict__ slots) {
+  __shared__ unsigned counter[8][kMoeMaxExperts];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long seg = static_cast<long long>(blockIdx.x) * 8 + warp;
+  const long long base = seg * kMoeSegment;
+  if (base >= pairs) return;
+  for (int e = lane; e < experts; e += 32) counter[warp][e] = seg_base[seg * experts + e];
+  __syncwarp();
+  for (int i = 0; i < kMoeSegment; i += 32) {
+    const long long q = base + i + lane;
+    const bool live = q < pairs;
+    const uint32_t e = live ? selected[q] : 0xFFFFFFFFu;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const unsigned rank = __popc(peers & ((1u << lane) - 1u));
+    unsigned slot = 0;
+    if (live) slot = counter[warp][e] + rank;
+    __syncwarp();
+    if (live && rank == 0) counter[warp][e] += __popc(peers);
+    __syncwarp();
+    if (live) slots[q] = slot < static_cast<unsigned long long>(capacity) ? slot : kMoeDropped;
   }
 }
 

@@ -53,7 +53,9 @@ def scatter(gemm: Tcgen05Gemm, x, routing: MoeRouting, rows: int | None = None):
     """Dispatch: permuted[dest_row] = x[token].  ``rows`` defaults to tokens * top_k."""
     tokens, d = x.shape
     rows = tokens * routing.top_k if rows is None else rows
-    out = torch.zeros((rows, d), dtype=torch.bfloat16, device=x.device)
+    # every routed row is written; rows of dropped assignments (none when capacity is
+    # tokens * top_k) are never read back by combine
+    out = torch.empty((rows, d), dtype=torch.bfloat16, device=x.device)
     L.check(gemm._lib.b200gemm_moe_scatter(gemm._h, _stream_ptr(), x.data_ptr(),
                                            routing.dest_row.data_ptr(), tokens, routing.top_k, d,
                                            out.data_ptr()))
@@ -85,7 +87,7 @@ def grouped_gemm(gemm: Tcgen05Gemm, a, b, offsets, out=None, transposed_b: bool 
     if offsets.dtype != torch.int32 or offsets.numel() != groups + 1:
         raise TypeError("offsets must be int32 [groups + 1] on the device")
     if out is None:
-        out = torch.zeros((rows, n), dtype=torch.bfloat16, device=a.device)
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=a.device)
     L.check(gemm._lib.b200gemm_grouped_gemm(
         gemm._h, _stream_ptr(), a.data_ptr(), a.stride(0), b.data_ptr(),
         L.MN_MAJOR if transposed_b else L.K_MAJOR, b.stride(1), b.stride(0), out.data_ptr(),

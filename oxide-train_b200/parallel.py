@@ -77,7 +77,7 @@ class DeviceOps:
         from .gemm import _stream_ptr
         rows, k = a.shape
         n = b.shape[2]                                  # b is [experts_local, k, n]
-        out = torch.zeros((rows, n), dtype=torch.bfloat16, device=a.device)
+        out = torch.empty((rows, n), dtype=torch.bfloat16, device=a.device)
         if rows == 0:
             return out
         L.check(self.gemm._lib.b200gemm_grouped_gemm_indexed(
@@ -207,6 +207,13 @@ class ExpertParallelMoe:
     def forward(self, x, scores, scores_are_logits=False, residual=None, out_dtype=torch.float32):
         r = self.ops.route(scores, self.top_k, scores_are_logits)
         xp = self.ops.scatter(x, r)                       # rows sorted by (global) expert = by owner rank
+        if self.world == 1:
+            # one rank owns every expert: the routed rows are already where they are multiplied
+            index = torch.arange(self.experts, dtype=torch.int32, device=x.device)
+            hidden = self.ops.grouped_indexed(xp, self.w_up, r.offsets, index, True)
+            yp = self.ops.grouped_indexed(hidden, self.w_down, r.offsets, index, False)
+            self.last = {"rows_received": xp.shape[0], "rows_sent": xp.shape[0], "routing": r}
+            return self.ops.combine(yp, r, residual, out_dtype)
         send, recv = exchange_counts(r.accepted_counts, self.world, self.group)
         send_splits = send.sum(1).tolist()                # the one host sync of the step
         recv_splits = recv.sum(1).tolist()
