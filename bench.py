@@ -311,7 +311,9 @@ def run_sharded(args):
         par_text = f"vocabulary split over {world} GPU(s); all-reduce of row max / sum-exp and of d_hidden"
         host_in = (hidden, None)
     elif args.workload == "moe":
-        n_tok, d, ff, experts, top_k = 32768, 1536, 768, 64, 8
+        # 32768 tokens PER GPU (weak scaling): expert parallelism serves data-parallel
+        # token batches; the experts, not the tokens, are what is divided.
+        n_tok, d, ff, experts, top_k = 32768 * world, 1536, 768, 64, 8
         n_local, e_local = n_tok // world, experts // world
         grank = torch.Generator(device=dev)
         grank.manual_seed(100 + rank)                     # each rank has its own tokens
@@ -328,8 +330,8 @@ def run_sharded(args):
             return 9
 
         flops = 2.0 * n_tok * top_k * d * ff * 2
-        name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens, D=1536, E=64, top-8, expert FF=768, "
-                "up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
+        name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens per GPU, D=1536, E=64, top-8, "
+                "expert FF=768, up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
         par_text = f"experts and tokens split over {world} GPU(s); all-to-all dispatch and combine"
         host_in = (x, None)
     else:
@@ -407,7 +409,8 @@ def run_sharded(args):
     line = {
         "metric": f"bf16_gemm_tflops_{args.workload}", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "weak" if args.workload == "moe" else "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
         "config": {"workload": name, "parallelism": par_text,
                    "l2": "operands exceed the 126 MB L2"},
         "pct_of_nominal_dense_peak": 100.0 * value / world / 2250.0,

@@ -62,6 +62,23 @@ class DeviceOps:
         return head.backward(hidden, weight_shard, local_targets, lse, dy=dy, d_weight=d_weight,
                              accumulate_dw=accumulate_dw)
 
+    def head_dlogits_and_dhidden(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy):
+        """First half of the shard's backward: dlogits (bf16) and this shard's part of d_hidden."""
+        head = self._FusedLmHead(self.gemm, classes_local, w_layout)
+        dl, dh, _ = head.backward(hidden, weight_shard, local_targets, lse, dy=dy, want_d_weight=False)
+        return dl, dh
+
+    def head_dweight(self, hidden, dlogits, w_layout, d_weight, accumulate_dw):
+        """Second half: d_weight (=|+=) hidden^T . dlogits in the weight's orientation."""
+        k, v = hidden.shape[1], dlogits.shape[1]
+        if d_weight is None:
+            shape = (k, v) if w_layout == "in_out" else (v, k)
+            d_weight = torch.zeros(shape, dtype=torch.float32, device=hidden.device)
+            accumulate_dw = True
+        a, b = (hidden, dlogits) if w_layout == "in_out" else (dlogits, hidden)
+        self.gemm.gemm(a, b, d_weight, transposed_a=True, transposed_b=True, accumulate=accumulate_dw)
+        return d_weight
+
     # MoE
     def route(self, scores, top_k, scores_are_logits):
         return self._moe.route(self.gemm, scores, top_k, scores_are_logits=scores_are_logits)
@@ -96,6 +113,9 @@ class DeviceOps:
         dx = torch.empty((dy.shape[0], w.shape[0]), dtype=out_dtype, device=dy.device)
         self.gemm.gemm(dy, w, dx)
         return dx
+
+    def linear_input_grad_into(self, dy, w, dx):
+        self.gemm.gemm(dy, w, dx)
 
     def linear_weight_grad(self, x, dy, dw):
         self.gemm.f32_accumulate_transposed(x, dy, dw)
@@ -141,6 +161,7 @@ class VocabParallelHead:
         self.world, self.rank = _world(group)
         self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
+        self._side = None
 
     def shard_weight(self, weight_full):
         """This rank's columns of a full ``[hidden, vocab_padded]`` weight (a copy)."""
@@ -161,9 +182,23 @@ class VocabParallelHead:
                  accumulate_dw: bool = False):
         """Returns ``(dlogits shard, d_hidden summed over shards, d_weight shard)``."""
         lt = self.local_targets(targets)
-        dl, dh, dw = self.ops.head_backward_shard(hidden, weight_shard, lt, lse, self.classes_local,
-                                                  self.w_layout, dy, d_weight, accumulate_dw)
-        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+        if not hasattr(self.ops, "head_dweight") or hidden.device.type != "cuda":
+            dl, dh, dw = self.ops.head_backward_shard(hidden, weight_shard, lt, lse, self.classes_local,
+                                                      self.w_layout, dy, d_weight, accumulate_dw)
+            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+            return dl, dh, dw
+        # d_hidden's all-reduce (rows x hidden fp32, the one large message of this path)
+        # runs on a side stream underneath the weight-gradient GEMM.
+        dl, dh = self.ops.head_dlogits_and_dhidden(hidden, weight_shard, lt, lse, self.classes_local,
+                                                   self.w_layout, dy)
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=hidden.device)
+        self._side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._side):
+            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+        dh.record_stream(self._side)
+        dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
+        torch.cuda.current_stream().wait_stream(self._side)
         return dl, dh, dw
 
 
@@ -196,8 +231,9 @@ class ExpertParallelMoe:
 
     ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
 
-    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None):
+    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces: int = 4):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
+        self.pieces, self._side = pieces, None
         self.world, self.rank = _world(group)
         if experts % self.world:
             raise ValueError("experts must divide evenly over the ranks")
@@ -205,30 +241,83 @@ class ExpertParallelMoe:
         self.last = {}
 
     def forward(self, x, scores, scores_are_logits=False, residual=None, out_dtype=torch.float32):
-        r = self.ops.route(scores, self.top_k, scores_are_logits)
-        xp = self.ops.scatter(x, r)                       # rows sorted by (global) expert = by owner rank
         if self.world == 1:
             # one rank owns every expert: the routed rows are already where they are multiplied
+            r = self.ops.route(scores, self.top_k, scores_are_logits)
+            xp = self.ops.scatter(x, r)                   # rows sorted by expert
             index = torch.arange(self.experts, dtype=torch.int32, device=x.device)
             hidden = self.ops.grouped_indexed(xp, self.w_up, r.offsets, index, True)
             yp = self.ops.grouped_indexed(hidden, self.w_down, r.offsets, index, False)
             self.last = {"rows_received": xp.shape[0], "rows_sent": xp.shape[0], "routing": r}
             return self.ops.combine(yp, r, residual, out_dtype)
-        send, recv = exchange_counts(r.accepted_counts, self.world, self.group)
-        send_splits = send.sum(1).tolist()                # the one host sync of the step
-        recv_splits = recv.sum(1).tolist()
-        rows_in = int(sum(recv_splits))
-        recv_x = torch.empty((rows_in, x.shape[1]), dtype=xp.dtype, device=xp.device)
-        dist.all_to_all_single(recv_x, xp, output_split_sizes=recv_splits, input_split_sizes=send_splits,
-                               group=self.group)
-        offsets, index = received_groups(recv)
-        hidden = self.ops.grouped_indexed(recv_x, self.w_up, offsets, index, True)
-        y = self.ops.grouped_indexed(hidden, self.w_down, offsets, index, False)
-        yp = torch.empty((xp.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
-        dist.all_to_all_single(yp, y, output_split_sizes=send_splits, input_split_sizes=recv_splits,
-                               group=self.group)
-        self.last = {"rows_received": rows_in, "rows_sent": int(sum(send_splits)), "routing": r}
-        return self.ops.combine(yp, r, residual, out_dtype)
+        return self._forward_pipelined(x, scores, scores_are_logits, residual, out_dtype)
+
+    def _forward_pipelined(self, x, scores, scores_are_logits, residual, out_dtype):
+        """Several ranks: the tokens go through in ``pieces`` slices.  Routing and the
+        counts exchange of every slice come first (one host sync for all the split
+        sizes); then slice i's dispatch / expert GEMMs / combine run on one of two
+        streams, so that the all-to-alls of a slice overlap the GEMMs of its
+        neighbour."""
+        n = x.shape[0]
+        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+        step = n // pieces
+        on_gpu = x.device.type == "cuda"
+        plan = []
+        for p in range(pieces):
+            sl = slice(p * step, (p + 1) * step)
+            r = self.ops.route(scores[sl].contiguous(), self.top_k, scores_are_logits)
+            xp = self.ops.scatter(x[sl], r)               # rows sorted by (global) expert = by owner rank
+            send, recv = exchange_counts(r.accepted_counts, self.world, self.group)
+            plan.append((sl, r, xp, send, recv))
+        # the one host sync of the step: every slice's split sizes at once
+        sizes = torch.stack([torch.stack([s.sum(1), rv.sum(1)]) for _, _, _, s, rv in plan]).cpu().tolist()
+        out = torch.empty((n, self.w_down.shape[2]), dtype=out_dtype, device=x.device)
+        streams = self._streams(x.device) if on_gpu and pieces > 1 else [None]
+        main = torch.cuda.current_stream() if on_gpu else None
+        rows_in = rows_out = 0
+        for p, (sl, r, xp, send, recv) in enumerate(plan):
+            send_splits = [int(v) for v in sizes[p][0]]
+            recv_splits = [int(v) for v in sizes[p][1]]
+            stream = streams[p % len(streams)]
+            ctx = torch.cuda.stream(stream) if stream is not None else _NullCtx()
+            if stream is not None:
+                stream.wait_stream(main)
+            with ctx:
+                got = int(sum(recv_splits))
+                recv_x = torch.empty((got, x.shape[1]), dtype=xp.dtype, device=xp.device)
+                dist.all_to_all_single(recv_x, xp, output_split_sizes=recv_splits,
+                                       input_split_sizes=send_splits, group=self.group)
+                offsets, index = received_groups(recv)
+                hidden = self.ops.grouped_indexed(recv_x, self.w_up, offsets, index, True)
+                y = self.ops.grouped_indexed(hidden, self.w_down, offsets, index, False)
+                yp = torch.empty((xp.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
+                dist.all_to_all_single(yp, y, output_split_sizes=send_splits, input_split_sizes=recv_splits,
+                                       group=self.group)
+                res = residual[sl] if residual is not None else None
+                out[sl] = self.ops.combine(yp, r, res, out_dtype)
+                if stream is not None:
+                    for tns in (xp, out):
+                        tns.record_stream(stream)
+            rows_in += got
+            rows_out += int(sum(send_splits))
+        if streams[0] is not None:
+            for st in streams:
+                main.wait_stream(st)
+        self.last = {"rows_received": rows_in, "rows_sent": rows_out, "routing": plan[0][1], "pieces": pieces}
+        return out
+
+    def _streams(self, device):
+        if self._side is None:
+            self._side = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
+        return self._side
+
+
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
 
 
 # --------------------------------------------------------------------------- tensor-parallel MLP
@@ -296,19 +385,54 @@ class TensorParallelMlp:
         """``dy_local`` is this rank's rows of dL/dy (layout of ``forward``'s output).
 
         Accumulates the weight-gradient shards (fp32) and returns the full
-        ``dx [m, d]`` summed over ranks."""
+        ``dx [m, d]`` summed over ranks.  Piece by piece: the all-gather of the
+        next piece's ``dy`` and the all-reduce of the previous piece's ``dx`` run
+        on a side stream underneath the current piece's four GEMMs."""
         m = x.shape[0]
         piece, share = m // self.chunks, m // (self.chunks * self.world)
         dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)
-        for c in range(self.chunks):
+        side = self._side_stream(x.device)
+        main = torch.cuda.current_stream() if side is not None else None
+        if side is not None:
+            dx.record_stream(side)
+
+        def gather(c):
             dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
-            dist.all_gather_into_tensor(dy, dy_local[c * share:(c + 1) * share].contiguous(), group=self.group)
+            src = dy_local[c * share:(c + 1) * share].contiguous()
+            if side is None:
+                dist.all_gather_into_tensor(dy, src, group=self.group)
+                return dy, None
+            with torch.cuda.stream(side):
+                dist.all_gather_into_tensor(dy, src, group=self.group)
+                done = torch.cuda.Event()
+                done.record(side)
+            dy.record_stream(side)
+            return dy, done
+
+        if side is not None:
+            side.wait_stream(main)
+        nxt = gather(0)
+        for c in range(self.chunks):
+            dy, ready = nxt
+            if c + 1 < self.chunks:
+                nxt = gather(c + 1)                                       # prefetch under this piece's GEMMs
+            if ready is not None:
+                main.wait_event(ready)
             h = self._hidden[c]
             self.ops.linear_weight_grad(h, dy, dw_down)                   # dW_down += h^T dy
             dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16)   # dh = dy W_down^T
             xs = x[c * piece:(c + 1) * piece]
             self.ops.linear_weight_grad(xs, dh, dw_up)                    # dW_up += x^T dh
-            dxs = self.ops.linear_input_grad(dh, self.w_up, self.partial_dtype)
-            dx[c * piece:(c + 1) * piece] = dxs
-        dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=self.group)
+            dxs = dx[c * piece:(c + 1) * piece]
+            self.ops.linear_input_grad_into(dh, self.w_up, dxs)           # dx piece (partial sum)
+            if side is None:
+                dist.all_reduce(dxs, op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                produced = torch.cuda.Event()
+                produced.record(main)
+                with torch.cuda.stream(side):
+                    side.wait_event(produced)
+                    dist.all_reduce(dxs, op=dist.ReduceOp.SUM, group=self.group)
+        if side is not None:
+            main.wait_stream(side)
         return dx

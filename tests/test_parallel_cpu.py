@@ -102,6 +102,9 @@ class CpuOps:
     def linear_input_grad(self, dy, w, out_dtype=None):
         return dy.float() @ w.float().t()
 
+    def linear_input_grad_into(self, dy, w, dx):
+        dx.copy_(dy.float() @ w.float().t())
+
     def linear_weight_grad(self, x, dy, dw):
         dw += x.float().t() @ dy.float()
 
