@@ -100,6 +100,12 @@ typedef struct {
 B200GEMM_API int b200gemm_create(int device, b200gemm_handle_t* out);
 B200GEMM_API int b200gemm_destroy(b200gemm_handle_t h);
 
+/* Caps the number of SMs the persistent kernels of later launches occupy
+ * (0 or a value above the device's SM count restores all of them).  New: lets a
+ * caller keep a few SMs free for a collective's kernels that must run at the
+ * same time, since a persistent grid would otherwise hold every SM until it ends. */
+B200GEMM_API int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms);
+
 /* The tcgen05 GEMM (host.rs:616-1098, kernels gpu/gemm/src/optimized.rs:1138-1268). */
 B200GEMM_API int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
 

@@ -25,6 +25,7 @@ using namespace b200;
 thread_local char g_error[512] = "";
 #ifdef B200_PROBE
 long long* g_probe = nullptr;   // diagnostic builds only: device buffer of phase counters
+int g_probe_skip_loads = 0;
 #endif
 
 int fail(int code, const char* fmt, ...) {
@@ -52,7 +53,8 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 struct b200gemm_context {
   int device = 0;
-  int sm_count = 0;
+  int sm_count = 0;          // SMs the persistent kernels spread over (b200gemm_set_sm_limit)
+  int sm_total = 0;          // SMs of the device
   int* status = nullptr;        // device status word
   EncodeTiledFn encode = nullptr;
   // staging for b200gemm_gemm_host
@@ -268,6 +270,7 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
   params.reduce = plan.reduce;
 #ifdef B200_PROBE
   params.probe = g_probe;
+  params.probe_skip_loads = g_probe_skip_loads;
 #endif
 
   if (plan.epi == kEpiF32Tma && d->mode == B200GEMM_STORE && plan.split_k > 1) {
@@ -606,9 +609,19 @@ extern "C" {
 
 int b200gemm_version(void) { return 100; }
 
+int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms) {
+  if (!h) return fail(B200GEMM_ERR_INVALID, "null handle");
+  if (sms <= 0 || sms > h->sm_total) sms = h->sm_total;
+  h->sm_count = sms < 2 ? 2 : sms;
+  return B200GEMM_OK;
+}
+
 #ifdef B200_PROBE
 __attribute__((visibility("default"))) void b200gemm_set_probe(long long* device_buffer) {
   g_probe = device_buffer;
+}
+__attribute__((visibility("default"))) void b200gemm_set_probe_skip_loads(int on) {
+  g_probe_skip_loads = on;
 }
 #endif
 
@@ -632,6 +645,7 @@ int b200gemm_create(int device, b200gemm_handle_t* out) {
   if (!ctx) return fail(B200GEMM_ERR_INVALID, "out of host memory");
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
+  ctx->sm_total = prop.multiProcessorCount;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);

@@ -126,6 +126,7 @@ struct GemmParams {
   int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
 #ifdef B200_PROBE
   long long* probe;
+  int probe_skip_loads;   // timing experiment: producers signal "full" without copying anything
 #endif
 };
 
@@ -303,11 +304,14 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // Two producer threads (in different warps) take alternate K blocks: one
     // thread cannot issue the 2-5 bulk-tensor copies of a K block as fast as
     // the tensor cores consume one.
-    if (lane == 0) {
+    // The whole warp walks the loop (so that addresses, coordinates and barrier
+    // phases stay warp-uniform and live in uniform registers); one elected lane
+    // issues the copies.
+    {
       const uint32_t which = warp == 0 ? 0u : 1u;
       uint32_t g = 0;   // K blocks seen so far, over all of this CTA's tiles
       bool ok = true;
-      PROBE_DECL_IF(which == 0)
+      PROBE_DECL_IF(which == 0 && lane == 0)
       Walk walk(p, group_tile_start, cluster_id, num_clusters);
       Tile t;
       for (; ok && walk.get(t); walk.next(t)) {
@@ -318,31 +322,39 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           if ((g & 1u) != which) continue;
           const uint32_t stage = g % Cfg::kStages;
           const uint32_t phase = (g / Cfg::kStages) & 1u;
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kDevTimeoutProducer, abort_flag)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kDevTimeoutProducer, abort_flag));
+          if (!ok) break;
           PROBE_ADD(0);
           // Both CTAs of a pair complete their bytes on the leader's barrier.
           const uint32_t fb = kCtaGroup == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
-          if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
           const uint32_t a_dst = ring + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kABytes;
           const int k0 = kb * kBlockK;
-          if (!p.a_mn) {
-            tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, a_batch);
-          } else {
+          if (elect_one()) {
+#ifdef B200_PROBE
+            if (p.probe_skip_loads) {
+              if (cta_rank == 0) mbar_arrive(full_bar(stage));
+            } else
+#endif
+            {
+              if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
+              if (!p.a_mn) {
+                tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, a_batch);
+              } else {
 #pragma unroll
-            for (int i = 0; i < kTileMCta / 64; ++i)
-              tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
-          }
-          if (!p.b_mn) {
-            tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, t.batch);
-          } else {
+                for (int i = 0; i < kTileMCta / 64; ++i)
+                  tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
+              }
+              if (!p.b_mn) {
+                tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, t.batch);
+              } else {
 #pragma unroll
-            for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
-              tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, t.batch);
+                for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
+                  tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, t.batch);
+              }
+            }
           }
+          __syncwarp();
           PROBE_ADD(1);
         }
       }
@@ -350,48 +362,54 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && cta_rank == 0) {
+    // Only the leader CTA of a pair issues.  As in the producers, the whole warp
+    // runs the loop and one elected lane issues: the descriptors then live in
+    // uniform registers, which is what tcgen05.mma takes its operands from, and
+    // the issuing path from one MMA to the next stays short.
+    if (cta_rank == 0) {
       const uint32_t idesc = make_idesc_bf16(Cfg::kTileM, kTileN, p.a_mn != 0, p.b_mn != 0);
       // K-major: LBO unused (encoded 1), next K=16 slice is 32 bytes along the swizzled row.
       // MN-major: LBO = one 64x64 subtile, next K=16 slice is 16 rows of 128 bytes.
-      const uint32_t a_lbo = p.a_mn ? kSubtileBytes : 16, a_kstep = p.a_mn ? 2048 : 32;
-      const uint32_t b_lbo = p.b_mn ? kSubtileBytes : 16, b_kstep = p.b_mn ? 2048 : 32;
+      // The descriptors of stage 0 / slice 0 are built once; every other one differs
+      // only in the start-address field (address >> 4, below bit 14).
+      const uint64_t a_desc0 = make_smem_desc(ring, p.a_mn ? kSubtileBytes : 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc(ring + Cfg::kABytes, p.b_mn ? kSubtileBytes : 16, 1024);
+      const uint64_t a_kadd = (p.a_mn ? 2048u : 32u) >> 4, b_kadd = (p.b_mn ? 2048u : 32u) >> 4;
+      constexpr uint64_t kStageAdd = Cfg::kStageBytes >> 4;
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
-      PROBE_DECL
+      PROBE_DECL_IF(lane == 0)
       Walk walk(p, group_tile_start, cluster_id, num_clusters);
       Tile t;
       for (; ok && walk.get(t); walk.next(t), ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag)) {
-          ok = false;
-          break;
-        }
+        ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag));
+        if (!ok) break;
         PROBE_ADD(2);
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
         for (int kb = 0; kb < t.kb_count; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag)) {
-            ok = false;
-            break;
-          }
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag));
+          if (!ok) break;
           PROBE_ADD(3);
           tcgen05_fence_after_sync();
-          const uint32_t a_addr = ring + stage * Cfg::kStageBytes;
-          const uint32_t b_addr = a_addr + Cfg::kABytes;
+          const uint64_t da = a_desc0 + stage * kStageAdd;
+          const uint64_t db = b_desc0 + stage * kStageAdd;
+          if (elect_one()) {
+            umma_bf16<kCtaGroup>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint64_t da = make_smem_desc(a_addr + k * a_kstep, a_lbo, 1024);
-            const uint64_t db = make_smem_desc(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_bf16<kCtaGroup>(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 1; k < kBlockK / kUmmaK; ++k)
+              umma_bf16<kCtaGroup>(d_tmem, da + k * a_kadd, db + k * b_kadd, idesc, 1u);
+            umma_commit<kCtaGroup>(empty_bar(stage));   // stage reusable once these MMAs retire
           }
-          umma_commit<kCtaGroup>(empty_bar(stage));   // stage reusable once these MMAs retire
+          __syncwarp();
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
           PROBE_ADD(4);
         }
-        if (ok) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
+        if (ok && elect_one()) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
+        __syncwarp();
       }
     }
     __syncwarp();

@@ -104,6 +104,10 @@ class Tcgen05Gemm:
         L.check(self._lib.b200gemm_launch_config(self._h, C.byref(d), *[C.byref(v) for v in vals]))
         return dict(zip(("grid", "cluster", "smem_bytes", "split_k"), (v.value for v in vals)))
 
+    def set_sm_limit(self, sms: int = 0) -> None:
+        """Keep the persistent kernels on at most ``sms`` SMs (0 = all of them)."""
+        L.check(self._lib.b200gemm_set_sm_limit(self._h, int(sms)))
+
     def device_status(self) -> int:
         """Synchronise and return the device status word (0 = ok); raises on a timeout."""
         code = C.c_int32()
