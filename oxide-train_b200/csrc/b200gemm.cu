@@ -837,9 +837,9 @@ int b200gemm_moe_scatter(b200gemm_handle_t h, void* stream, const void* x, const
   if (tokens <= 0 || top_k < 1 || d <= 0 || (d % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "need tokens, top_k > 0 and d a multiple of 8");
   if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(x_permuted)) & 15u) != 0)
     return fail(B200GEMM_ERR_SHAPE, "buffers must be 16-byte aligned");
-  const long long pairs = tokens * top_k;
-  moe_scatter_kernel<<<stream_grid(pairs * 32, h->sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint16_t*>(x), dest_row, pairs, top_k, d, static_cast<uint16_t*>(x_permuted));
+  if (top_k > 32) return fail(B200GEMM_ERR_SHAPE, "top_k must be at most 32");
+  moe_scatter_kernel<<<stream_grid(tokens * 32, h->sm_count), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), dest_row, tokens, top_k, d, static_cast<uint16_t*>(x_permuted));
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
 }

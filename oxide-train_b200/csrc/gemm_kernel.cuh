@@ -192,11 +192,12 @@ struct TileWalk {
       t.first = inner == 0;
       t.last = inner == count - 1;
     } else {
-      // item -> (m-tile over all groups, n-tile); n varies slowest so that the
-      // clusters running together share few B panels.
-      int total_m = group_tile_start[p.groups];
-      int tn = item / total_m;
-      int tm = item - tn * total_m;
+      // item -> (m-tile over all groups, n-tile) with n fastest: the clusters running
+      // side by side then cover a couple of dozen consecutive m-tiles (one to three
+      // experts) times all n-tiles, so every A tile is fetched from HBM once and the
+      // few expert matrices in use stay in L2.
+      int tm = item / p.tiles_n;
+      int tn = item - tm * p.tiles_n;
       // largest g with group_tile_start[g] <= tm (empty groups share a start and are skipped)
       int lo = 0, hi = p.groups - 1;
       while (lo < hi) {
@@ -222,6 +223,12 @@ struct TileWalk {
     item += step;
   }
 };
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -539,8 +546,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               if (p.act_silu) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                  const float x = __uint_as_float(r[j]);
-                  r[j] = __float_as_uint(x / (1.f + fast_exp2(-x * kLog2e)));
+                  // x * sigmoid(x) = hx + hx * tanh(hx), hx = x / 2: one MUFU op per element
+                  const float hx = 0.5f * __uint_as_float(r[j]);
+                  r[j] = __float_as_uint(fmaf(hx, fast_tanh(hx), hx));
                 }
               }
             }

@@ -220,26 +220,44 @@ __global__ void __launch_bounds__(256) moe_dest_kernel(const uint32_t* __restric
 }
 
 // Dispatch: x_permuted[dest_row[token * top_k + rank], :] = x[token, :].  One warp
-// per pair, 16-byte copies (d is a multiple of 8 bf16).
+// per token: the row is read once, 16 bytes per lane per step, and written to
+// each of its top_k destinations (d is a multiple of 8 bf16).
 __global__ void __launch_bounds__(256) moe_scatter_kernel(const uint16_t* __restrict__ x,
                                                           const uint32_t* __restrict__ dest_row,
-                                                          long long pairs, int top_k, long long d,
+                                                          long long tokens, int top_k, long long d,
                                                           uint16_t* __restrict__ x_permuted) {
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long vecs = d / 8;
-  for (long long q = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; q < pairs; q += warps) {
-    const uint32_t dst = dest_row[q];
-    if (dst == kMoeDropped) continue;
-    const uint4* src = reinterpret_cast<const uint4*>(x + (q / top_k) * d);
-    uint4* out = reinterpret_cast<uint4*>(x_permuted + static_cast<long long>(dst) * d);
-    for (long long v = lane; v < vecs; v += 32) out[v] = src[v];
+  for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + token * d);
+    uint32_t dst = lane < top_k ? dest_row[token * top_k + lane] : kMoeDropped;
+    for (long long v0 = 0; v0 < vecs; v0 += 128) {          // four 16-byte loads in flight per lane
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long v = v0 + u * 32 + lane;
+        if (v < vecs) val[u] = src[v];
+      }
+      for (int r = 0; r < top_k; ++r) {
+        const uint32_t row = __shfl_sync(0xffffffffu, dst, r);
+        if (row == kMoeDropped) continue;
+        uint4* out = reinterpret_cast<uint4*>(x_permuted + static_cast<long long>(row) * d);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long v = v0 + u * 32 + lane;
+          if (v < vecs) out[v] = val[u];
+        }
+      }
+    }
   }
 }
 
 // Combine: out[token, :] = residual[token, :] + sum over ranks (in rank order) of
 // gate * y_permuted[dest_row, :], accumulated in fp32 (moe.rs:292-306).  One
-// warp per token; each lane owns 8 consecutive columns at a time.
+// warp per token; each lane owns 8 consecutive columns at a time.  The (row,
+// gate) pairs of the token are read once and broadcast; the gathered rows of
+// four ranks are loaded together before they are added.
 template <bool kOutBf16>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __restrict__ y_permuted,
                                                           const uint32_t* __restrict__ dest_row,
@@ -251,6 +269,15 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long vecs = d / 8;
   for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    const uint32_t my_row = lane < top_k ? dest_row[token * top_k + lane] : kMoeDropped;
+    const float my_gate = lane < top_k ? gates[token * top_k + lane] : 0.f;
+    uint32_t rows[kMoeMaxTopK];
+    float gs[kMoeMaxTopK];
+#pragma unroll
+    for (int r = 0; r < kMoeMaxTopK; ++r) {     // lanes at or beyond top_k hold "dropped"
+      rows[r] = __shfl_sync(0xffffffffu, my_row, r);
+      gs[r] = __shfl_sync(0xffffffffu, my_gate, r);
+    }
     for (long long v = lane; v < vecs; v += 32) {
       float acc[8];
       if (residual) {
@@ -265,16 +292,24 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       }
-      for (int r = 0; r < top_k; ++r) {
-        const uint32_t src = dest_row[token * top_k + r];
-        if (src == kMoeDropped) continue;
-        const float g = gates[token * top_k + r];
-        const uint4 y = reinterpret_cast<const uint4*>(y_permuted + static_cast<long long>(src) * d)[v];
-        const uint32_t w[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(g, __uint_as_float(w[j] << 16)));
-          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(g, __uint_as_float(w[j] & 0xffff0000u)));
+      for (int r0 = 0; r0 < kMoeMaxTopK; r0 += 4) {
+        if (r0 >= top_k) break;
+        uint4 y[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (rows[r0 + u] != kMoeDropped)
+            y[u] = reinterpret_cast<const uint4*>(y_permuted + static_cast<long long>(rows[r0 + u]) * d)[v];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (rows[r0 + u] == kMoeDropped) continue;
+          const float g = gs[r0 + u];
+          const uint32_t w[4] = {y[u].x, y[u].y, y[u].z, y[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(g, __uint_as_float(w[j] << 16)));
+            acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(g, __uint_as_float(w[j] & 0xffff0000u)));
+          }
         }
       }
       if (kOutBf16) {
