@@ -440,6 +440,58 @@ def run_only(args):
     gemm = pkg.Tcgen05Gemm(0)
     name, kind = args.only.split(".")
     bf, f32 = torch.bfloat16, torch.float32
+    if name == "lm_head" and kind.startswith("fused"):
+        m = args.only_tokens
+        head = pkg.FusedLmHead(gemm, VOCAB, "in_out")
+        hid = torch.randn((m, D_MODEL), device=dev).to(bf)
+        w = (torch.randn((D_MODEL, VOCAB_PAD), device=dev) * 0.02).to(bf)
+        tg = torch.randint(0, VOCAB, (m,), device=dev, dtype=torch.int32)
+        lse = head.forward(hid, w, tg)[1]
+        if kind == "fused_forward":
+            fn, fl = (lambda: head.forward(hid, w, tg)), 2.0 * m * D_MODEL * VOCAB_PAD
+        else:
+            dl = torch.empty((m, VOCAB_PAD), device=dev, dtype=bf)
+            dh = torch.empty((m, D_MODEL), device=dev, dtype=f32)
+            dw = torch.zeros((D_MODEL, VOCAB_PAD), device=dev, dtype=f32)
+            fn = lambda: head.backward(hid, w, tg, lse, dlogits=dl, d_hidden=dh, d_weight=dw, accumulate_dw=True)
+            fl = 4.0 * m * D_MODEL * VOCAB_PAD
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            fn()
+        e0.record()
+        torch.cuda.synchronize()
+        ms = s0.elapsed_time(e0) / args.steps
+        print(json.dumps({"only": args.only, "tokens": m, "ms": ms, "tflops": fl / ms / 1e9,
+                          "device_status": gemm.device_status()}), flush=True)
+        gemm.close()
+        return
+    if name == "moe":
+        n_tok, d, ff, experts, top_k = args.only_tokens, 1536, 768, 64, 8
+        x = torch.randn((n_tok, d), device=dev).to(bf)
+        bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
+        logits = (torch.randn((n_tok, experts), device=dev) + bias).contiguous()
+        ffn = pkg.GroupedExpertFfn(gemm, (torch.randn((experts, d, ff), device=dev) * 0.02).to(bf),
+                                   (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
+        fn = lambda: ffn.forward(x, logits, top_k, scores_are_logits=True)
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            fn()
+        e0.record()
+        torch.cuda.synchronize()
+        ms = s0.elapsed_time(e0) / args.steps
+        print(json.dumps({"only": args.only, "tokens": n_tok, "ms": ms,
+                          "tflops": 2.0 * n_tok * top_k * d * ff * 2 / ms / 1e9,
+                          "device_status": gemm.device_status()}), flush=True)
+        gemm.close()
+        return
     if name == "lm_head":
         i, o = D_MODEL, VOCAB_PAD
     else:
@@ -583,7 +635,8 @@ def main():
     ap.add_argument("--no-table", action="store_true", help="skip the per-shape table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default=None,
-                    help="profiling aid: run one GEMM, e.g. qkv.forward, mlp_up.weight_grad, lm_head.input_grad")
+                    help="profiling aid: run one piece, e.g. qkv.forward, mlp_up.weight_grad, lm_head.fused_forward, "
+                         "lm_head.fused_backward, moe.forward")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
                     help="dense_step (default) is the headline; the others are the sharded configurations")
