@@ -329,6 +329,15 @@ B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const v
  * failures only (gpu/gemm/src/host.rs:616-626 `Result<(), DriverError>`). */
 B200GEMM_API int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_code);
 
+/* Self-test of the bounded waits every kernel here uses: launches a one-block
+ * kernel that waits on a barrier nothing completes, gives up after `limit_ms`
+ * (1..5000) and records a timeout code, so that the next
+ * b200gemm_device_status returns B200GEMM_ERR_DEVICE with code 104.  The
+ * kernel returns normally; the context stays usable.  No counterpart in the
+ * reference, whose kernels spin without a limit (SPEC.md:725-741 describes the
+ * deadlock that cost). */
+B200GEMM_API int b200gemm_wait_selftest(b200gemm_handle_t h, void* stream, int64_t limit_ms);
+
 /* Text of the last failure on the calling thread ("" if none). */
 B200GEMM_API const char* b200gemm_last_error_string(void);
 

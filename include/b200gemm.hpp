@@ -101,6 +101,53 @@ class Tcgen05Gemm {
     return run(stream, a, b, out, B200GEMM_OUT_F32, B200GEMM_ACCUMULATE, experts);
   }
 
+  // ---- lm-head fused with softmax cross-entropy ------------------------------
+  // Replaces GpuBf16Head::forward_into + cross_entropy_into and their backward
+  // (gpu/model/src/lib.rs:3076-3145, 6977-7040).  `weight` is the [k, v] master
+  // when w_layout is MN-major, [v, k] when K-major.
+  static size_t lmhead_ce_workspace_bytes(int64_t m) { return b200gemm_lmhead_ce_workspace_bytes(m); }
+  int lmhead_ce_forward(void* stream, const void* hidden, const void* weight, b200gemm_layout_t w_layout,
+                        const int32_t* targets, int64_t m, int64_t k, int64_t v, int64_t classes,
+                        float* lse, float* row_loss, float* loss, void* workspace,
+                        size_t workspace_bytes) const {
+    return b200gemm_lmhead_ce_forward(h_, stream, hidden, weight, w_layout, targets, m, k, v, classes,
+                                      lse, row_loss, loss, workspace, workspace_bytes);
+  }
+  int lmhead_ce_backward(void* stream, const void* hidden, const void* weight, b200gemm_layout_t w_layout,
+                         const int32_t* targets, const float* lse, float dy, int64_t m, int64_t k,
+                         int64_t v, int64_t classes, void* dlogits_bf16, float* d_hidden,
+                         float* d_weight, bool accumulate_dw) const {
+    return b200gemm_lmhead_ce_backward(h_, stream, hidden, weight, w_layout, targets, lse, dy, m, k, v,
+                                       classes, dlogits_bf16, d_hidden, d_weight, accumulate_dw ? 1 : 0);
+  }
+
+  // ---- MoE: routing integers, dispatch, grouped expert GEMM, combine -----------
+  // (crates/nn/src/moe.rs:205-352; gpu/model/src/lib.rs:4971-5130)
+  int moe_route(void* stream, const float* scores, bool scores_are_logits, int64_t tokens,
+                int32_t experts, int32_t top_k, int64_t capacity, uint32_t* selected, float* gates,
+                uint32_t* slots, uint32_t* assignment_counts, uint32_t* accepted_counts,
+                int32_t* offsets, uint32_t* dest_row) const {
+    return b200gemm_moe_route(h_, stream, scores, scores_are_logits ? 1 : 0, tokens, experts, top_k,
+                              capacity, selected, gates, slots, assignment_counts, accepted_counts,
+                              offsets, dest_row);
+  }
+  int moe_scatter(void* stream, const void* x, const uint32_t* dest_row, int64_t tokens, int32_t top_k,
+                  int64_t d, void* x_permuted) const {
+    return b200gemm_moe_scatter(h_, stream, x, dest_row, tokens, top_k, d, x_permuted);
+  }
+  int moe_combine(void* stream, const void* y_permuted, const uint32_t* dest_row, const float* gates,
+                  const void* residual, int64_t tokens, int32_t top_k, int64_t d, void* out,
+                  b200gemm_out_t out_type) const {
+    return b200gemm_moe_combine(h_, stream, y_permuted, dest_row, gates, residual, tokens, top_k, d, out,
+                                out_type);
+  }
+  /// Rows offsets[g]..offsets[g+1] of `a` times expert g's matrix, bf16 out, optional SiLU.
+  int grouped_gemm(void* stream, const Operand& a, const Operand& b, void* c, int64_t ldc,
+                   const int32_t* offsets, int32_t groups, bool silu) const {
+    return b200gemm_grouped_gemm(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, c, ldc,
+                                 offsets, groups, a.rows, b.rows, a.k, silu ? 1 : 0);
+  }
+
   /// Output row stride (elements) for the next calls; 0 = dense.  Lets a GEMM
   /// write one column block of a wider matrix (the grouped QKV projections,
   /// gpu/model/src/lib.rs:1379-1562).

@@ -49,6 +49,7 @@ SIGNATURES = {
     "b200gemm_convert_f32_to_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "b200gemm_convert_bf16_to_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "b200gemm_transpose_bf16": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
+    "b200gemm_wait_selftest": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
     "b200gemm_device_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "b200gemm_grouped_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,
                                         C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,

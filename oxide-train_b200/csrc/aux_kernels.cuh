@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
+
 namespace b200 {
 
 // ------------------------------------------------------------------ fp32 GEMM
@@ -196,6 +198,23 @@ inline cudaError_t launch_transpose_bf16(cudaStream_t stream, const uint16_t* sr
   if (grid.y > 65535) return cudaErrorInvalidValue;
   transpose_bf16_kernel<<<grid, 256, 0, stream>>>(src, dst, rows, cols);
   return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ wait self-test
+// Waits, with the same bounded-wait helper the GEMM kernels use, on a barrier
+// that nothing will ever complete; the wait gives up after `limit_ns`, records
+// kDevTimeoutDrain in the status word and the kernel returns normally.
+__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, status, kDevTimeoutDrain, &abort_flag, limit_ns);
+  __syncthreads();
 }
 
 }  // namespace b200

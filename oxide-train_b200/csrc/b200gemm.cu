@@ -944,6 +944,16 @@ int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t
   return B200GEMM_OK;
 }
 
+int b200gemm_wait_selftest(b200gemm_handle_t h, void* stream, int64_t limit_ms) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (limit_ms < 1 || limit_ms > 5000) return fail(B200GEMM_ERR_INVALID, "limit must be 1..5000 ms");
+  wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      h->status, static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
 int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_code) {
   int rc = check_handle(h);
   if (rc) return rc;

@@ -114,7 +114,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait.  Returns false on timeout (after recording `code` in *status)
 // or when another role of this CTA has already raised `abort_flag`.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t start = 0;
   for (uint32_t spin = 1;; ++spin) {
@@ -124,7 +125,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
       uint64_t now = global_timer_ns();
       if (start == 0) {
         start = now;
-      } else if (now - start > kWaitLimitNs) {
+      } else if (now - start > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

@@ -208,3 +208,22 @@ def test_contract_violations_return_status_codes(pkg, gemm):
     with pytest.raises(pkg.B200GemmError) as e:
         gemm.gemm(a[:, 1:], a[:, 1:], c)                             # base not 16-byte aligned
     assert e.value.code == L.ERR_SHAPE
+
+
+def test_bounded_wait_reports_a_status_code_and_the_context_survives(pkg, oracle, gemm):
+    """A wait that can never be satisfied gives up after its limit, the kernel
+    returns, the host reads the code, and the next GEMM on the same handle is correct."""
+    import torch
+    from oxide_train_b200._lib import check
+    stream = torch.cuda.current_stream().cuda_stream
+    check(gemm._lib.b200gemm_wait_selftest(gemm._h, stream, 50))
+    with pytest.raises(pkg.B200GemmError) as e:
+        gemm.device_status()
+    assert e.value.code == pkg._lib.ERR_DEVICE and "104" in str(e.value)
+    assert gemm.device_status() == 0                      # reading the code cleared it
+    a, av = bf16_operand(oracle, (256, 64), 61, kind="uniform")
+    b, bv = bf16_operand(oracle, (256, 64), 62, kind="uniform")
+    c = torch.zeros((256, 256), dtype=torch.float32, device="cuda")
+    gemm.f32_store(a, b, c)
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), oracle.matmul_nt(av, bv, THREADS), "after timeout", rel_fro=2e-5, elem=2e-4)
