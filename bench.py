@@ -318,21 +318,34 @@ def run_sharded(args):
         grank = torch.Generator(device=dev)
         grank.manual_seed(100 + rank)                     # each rank has its own tokens
         x = rnd((n_local, d), 1.0, grank)
-        bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
+        # Popularity rank r (Zipf bias 0.5*ln(1/r)) is dealt to the ranks in snake order, the
+        # placement a deployment would choose: expert ids are arbitrary labels, and a
+        # contiguous block of the hottest experts on one rank would triple its load.
+        pop = torch.arange(experts)
+        rnd_i, pos = pop // world, pop % world
+        owner = torch.where(rnd_i % 2 == 0, pos, world - 1 - pos)
+        expert_id = owner * e_local + rnd_i
+        bias = torch.empty(experts, dtype=f32)
+        bias[expert_id] = 0.5 * torch.log(1.0 / (pop.float() + 1.0))
+        bias = bias.to(dev)
         logits = (torch.randn((n_local, experts), generator=grank, device=dev) + bias).contiguous()
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
-        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn)
+        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=2, use_peer_copies=True)
         result = {}
 
         def step():
             result["out"] = ep.forward(x, logits, scores_are_logits=True)
             return 9
 
+        extra_fn = lambda: {"rows_received_this_rank": ep.last.get("rows_received"),
+                            "rows_sent_this_rank": ep.last.get("rows_sent")}
+
         flops = 2.0 * n_tok * top_k * d * ff * 2
         name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens per GPU, D=1536, E=64, top-8, "
                 "expert FF=768, up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
-        par_text = f"experts and tokens split over {world} GPU(s); all-to-all dispatch and combine"
+        par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch and combine by copy-engine "
+                    "pushes into peer memory (symmetric memory), NCCL for counts and barriers")
         host_in = (x, None)
     else:
         m, d, ff = 65536, 4096, 16384
@@ -422,6 +435,13 @@ def run_sharded(args):
                      "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
                      "algorithmic_flops_per_step": flops},
     }
+    if args.workload == "moe":
+        recv = torch.tensor([float(ep.last.get("rows_received", 0))], device=dev)
+        allr = [torch.zeros_like(recv) for _ in range(world)]
+        dist.all_gather(allr, recv)
+        rows = [float(t.item()) for t in allr]
+        line["moe_rows_received_per_rank"] = rows
+        line["moe_load_imbalance_max_over_mean"] = max(rows) / (sum(rows) / len(rows))
     if rank == 0:
         print(json.dumps(line), flush=True)
     gemm.close()

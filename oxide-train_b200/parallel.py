@@ -62,11 +62,22 @@ class DeviceOps:
         return head.backward(hidden, weight_shard, local_targets, lse, dy=dy, d_weight=d_weight,
                              accumulate_dw=accumulate_dw)
 
-    def head_dlogits_and_dhidden(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy):
-        """First half of the shard's backward: dlogits (bf16) and this shard's part of d_hidden."""
+    def head_dlogits(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy):
+        """First step of the shard's backward: the logits recomputed into bf16 dlogits."""
         head = self._FusedLmHead(self.gemm, classes_local, w_layout)
-        dl, dh, _ = head.backward(hidden, weight_shard, local_targets, lse, dy=dy, want_d_weight=False)
-        return dl, dh
+        dl, _, _ = head.backward(hidden, weight_shard, local_targets, lse, dy=dy, want_d_hidden=False,
+                                 want_d_weight=False)
+        return dl
+
+    def head_dhidden_partial(self, dlogits, weight_shard, w_layout, dtype):
+        """This shard's part of d_hidden = dlogits . W_shard^T, in `dtype`."""
+        k = weight_shard.shape[0] if w_layout == "in_out" else weight_shard.shape[1]
+        dh = torch.empty((dlogits.shape[0], k), dtype=dtype, device=dlogits.device)
+        self.gemm.gemm(dlogits, weight_shard, dh, transposed_b=(w_layout != "in_out"))
+        return dh
+
+    def widen(self, t):
+        return self.gemm.convert_bf16_to_f32(t)
 
     def head_dweight(self, hidden, dlogits, w_layout, d_weight, accumulate_dw):
         """Second half: d_weight (=|+=) hidden^T . dlogits in the weight's orientation."""
@@ -156,8 +167,9 @@ def merge_softmax_stats(row_max, row_sum, row_target_logit, group=None):
 
 
 class VocabParallelHead:
-    def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out"):
-        self.ops, self.group, self.w_layout = ops, group, w_layout
+    def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out",
+                 reduce_dtype=torch.bfloat16):
+        self.ops, self.group, self.w_layout, self.reduce_dtype = ops, group, w_layout, reduce_dtype
         self.world, self.rank = _world(group)
         self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
@@ -187,10 +199,13 @@ class VocabParallelHead:
                                                       self.w_layout, dy, d_weight, accumulate_dw)
             dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
             return dl, dh, dw
-        # d_hidden's all-reduce (rows x hidden fp32, the one large message of this path)
-        # runs on a side stream underneath the weight-gradient GEMM.
-        dl, dh = self.ops.head_dlogits_and_dhidden(hidden, weight_shard, lt, lse, self.classes_local,
-                                                   self.w_layout, dy)
+        # d_hidden's all-reduce (rows x hidden, the one large message of this path) runs on
+        # a side stream underneath the weight-gradient GEMM.  The shards' partial sums
+        # travel as bf16 -- the reference's own d_hidden is a bf16 GEMM output that is
+        # widened afterwards (gpu/model/src/lib.rs:3125-3145, 5777-5784) -- which halves
+        # the message; `reduce_dtype=torch.float32` keeps fp32 partials instead.
+        dl = self.ops.head_dlogits(hidden, weight_shard, lt, lse, self.classes_local, self.w_layout, dy)
+        dh = self.ops.head_dhidden_partial(dl, weight_shard, self.w_layout, self.reduce_dtype)
         if self._side is None:
             self._side = torch.cuda.Stream(device=hidden.device)
         self._side.wait_stream(torch.cuda.current_stream())
@@ -199,6 +214,8 @@ class VocabParallelHead:
         dh.record_stream(self._side)
         dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
         torch.cuda.current_stream().wait_stream(self._side)
+        if dh.dtype != torch.float32:
+            dh = self.ops.widen(dh)
         return dl, dh, dw
 
 
@@ -231,9 +248,11 @@ class ExpertParallelMoe:
 
     ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
 
-    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces: int = 4):
+    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces: int = 1,
+                 use_peer_copies: bool = False):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
         self.pieces, self._side = pieces, None
+        self.use_peer_copies, self._peer, self._peer_shape, self._index = use_peer_copies, None, None, None
         self.world, self.rank = _world(group)
         if experts % self.world:
             raise ValueError("experts must divide evenly over the ranks")
@@ -250,7 +269,96 @@ class ExpertParallelMoe:
             yp = self.ops.grouped_indexed(hidden, self.w_down, r.offsets, index, False)
             self.last = {"rows_received": xp.shape[0], "rows_sent": xp.shape[0], "routing": r}
             return self.ops.combine(yp, r, residual, out_dtype)
+        if self.use_peer_copies and x.device.type == "cuda":
+            return self._forward_peer(x, scores, scores_are_logits, residual, out_dtype)
         return self._forward_pipelined(x, scores, scores_are_logits, residual, out_dtype)
+
+    def _forward_peer(self, x, scores, scores_are_logits, residual, out_dtype):
+        """Several GPUs, copy-engine exchange.  The tokens go through in ``pieces`` slices:
+        first every slice is routed and its rows are pushed into the owners' inboxes;
+        then, slice by slice on two streams, the expert GEMMs run on what arrived and the
+        results are pushed back, so the pushes of one slice ride under the GEMMs of another."""
+        n, d = x.shape
+        d_out = self.w_down.shape[2]
+        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+        step = n // pieces
+        pairs = step * self.top_k
+        cap = pairs * min(self.world, 3)                      # inbox rows per slice (3x the even share)
+        if self._peer is None or self._peer_shape != (pieces, cap, pairs, d, d_out):
+            self._peer = PeerExchange(self.group, x.device, pieces * cap, pieces * pairs, d, d_out)
+            self._peer_shape = (pieces, cap, pairs, d, d_out)
+        px = self._peer
+        local = self.experts // self.world
+        main = torch.cuda.current_stream()
+        plan = []
+        gathered = []
+        for p in range(pieces):
+            sl = slice(p * step, (p + 1) * step)
+            r = self.ops.route(scores[sl].contiguous(), self.top_k, scores_are_logits)
+            xp = self.ops.scatter(x[sl], r)
+            allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
+            plan.append((sl, r, xp, allc))
+            gathered.append(allc)
+        counts_host = torch.stack(gathered).cpu().to(torch.int64)     # the one host sync of the step
+        out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
+        streams = self._streams(x.device)
+        work = []
+        rows_in = rows_out = 0
+        # stage 1: push every slice's rows to their owners (copy engines), then a barrier per slice
+        for p, (sl, r, xp, allc) in enumerate(plan):
+            send_off, send_rows, inbox_off, back_off, per_dest = exchange_plan(counts_host[p], self.rank, self.world)
+            got = int(per_dest[:, self.rank].sum())
+            if got > cap:
+                raise RuntimeError(f"slice {p}: {got} rows routed to rank {self.rank} exceed the inbox capacity {cap}")
+            st = streams[p % 2]
+            st.wait_stream(main)
+            with torch.cuda.stream(st):
+                # destinations in ring order starting after this rank, so that at any moment
+                # every GPU is receiving from one sender instead of all senders hitting GPU 0
+                for hop in range(self.world):
+                    j = (self.rank + 1 + hop) % self.world
+                    if send_rows[j]:
+                        dst = px.peer_inbox[j][p * cap + inbox_off[j]: p * cap + inbox_off[j] + send_rows[j]]
+                        dst.copy_(xp[send_off[j]: send_off[j] + send_rows[j]], non_blocking=True)
+                px.barrier()
+                xp.record_stream(st)
+            work.append((send_off, send_rows, back_off, per_dest, got))
+            rows_in += got
+            rows_out += int(sum(send_rows))
+        # stage 2: expert GEMMs on the rows that arrived, results pushed back, combine
+        for p, (sl, r, xp, allc) in enumerate(plan):
+            send_off, send_rows, back_off, per_dest, got = work[p]
+            st = streams[p % 2]
+            with torch.cuda.stream(st):
+                # group table of what arrived, built on the host from the counts already there
+                flat = counts_host[p][:, self.rank * local:(self.rank + 1) * local].reshape(-1)
+                off_host = torch.zeros(flat.numel() + 1, dtype=torch.int32).pin_memory()
+                off_host[1:] = torch.cumsum(flat, 0).to(torch.int32)
+                offsets = off_host.to(x.device, non_blocking=True)
+                index = self._group_index(x.device)
+                inbox = px.inbox[p * cap: p * cap + max(got, 1)]
+                hidden = self.ops.grouped_indexed(inbox[:got], self.w_up, offsets, index, True)
+                y = self.ops.grouped_indexed(hidden, self.w_down, offsets, index, False)
+                for hop in range(self.world):
+                    s_rank = (self.rank + 1 + hop) % self.world
+                    rows = int(per_dest[s_rank, self.rank])
+                    if rows:
+                        # where my block starts in the sender's permuted order = its send offset for me
+                        their_off = int(per_dest[s_rank, :self.rank].sum())
+                        dst = px.peer_outbox[s_rank][p * pairs + their_off: p * pairs + their_off + rows]
+                        dst.copy_(y[back_off[s_rank]: back_off[s_rank] + rows], non_blocking=True)
+                px.barrier()
+                yp = px.outbox[p * pairs: (p + 1) * pairs]
+                res = residual[sl] if residual is not None else None
+                out[sl] = self.ops.combine(yp, r, res, out_dtype)
+                for tns in (y, out):
+                    tns.record_stream(st)
+        for st in streams:
+            main.wait_stream(st)
+        self.last = {"rows_received": rows_in, "rows_sent": rows_out, "routing": plan[0][1], "pieces": pieces,
+                     "exchange": "peer copies"}
+        return out
 
     def _forward_pipelined(self, x, scores, scores_are_logits, residual, out_dtype):
         """Several ranks: the tokens go through in ``pieces`` slices.  Routing and the
@@ -306,6 +414,12 @@ class ExpertParallelMoe:
         self.last = {"rows_received": rows_in, "rows_sent": rows_out, "routing": plan[0][1], "pieces": pieces}
         return out
 
+    def _group_index(self, device):
+        if self._index is None:
+            local = self.experts // self.world
+            self._index = torch.arange(local, dtype=torch.int32, device=device).repeat(self.world)
+        return self._index
+
     def _streams(self, device):
         if self._side is None:
             self._side = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
@@ -318,6 +432,54 @@ class _NullCtx:
 
     def __exit__(self, *a):
         return False
+
+
+class PeerExchange:
+    """Row exchange between the GPUs of one box by copy-engine pushes into peer memory.
+
+    Each rank owns two buffers that every peer can write (``torch.distributed``
+    symmetric memory: ordinary device memory mapped into the peers' address
+    spaces).  A dispatch is a handful of ``cudaMemcpyAsync`` calls per rank: the
+    copy engines move the rows over NVLink while the SMs keep multiplying, which
+    an all-to-all made of NCCL kernels cannot do next to a persistent GEMM that
+    occupies every SM.  Ordering between ranks comes from one-element NCCL
+    all-reduces used as stream-ordered barriers; no kernel here spins on a
+    peer's flag and no kernel reads peer memory."""
+
+    def __init__(self, group, device, rows_in, rows_back, d_in, d_back, dtype=torch.bfloat16):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.rows_in, self.rows_back = rows_in, rows_back
+        self.inbox = symm_mem.empty((rows_in, d_in), dtype=dtype, device=device)        # rows dispatched to me
+        self.outbox = symm_mem.empty((rows_back, d_back), dtype=dtype, device=device)   # results returned to me
+        name = self.group.group_name
+        self._in = symm_mem.rendezvous(self.inbox, name)
+        self._back = symm_mem.rendezvous(self.outbox, name)
+        self.peer_inbox = [self._in.get_buffer(r, (rows_in, d_in), dtype) for r in range(self.world)]
+        self.peer_outbox = [self._back.get_buffer(r, (rows_back, d_back), dtype) for r in range(self.world)]
+        self._token = torch.zeros(1, device=device)
+
+    def barrier(self):
+        """Stream-ordered: later work on this stream starts after every rank got here."""
+        dist.all_reduce(self._token, group=self.group)
+
+
+def exchange_plan(counts_all, rank, world):
+    """Offsets of a dispatch from the full counts matrix ``counts_all[src, expert]`` (host ints).
+
+    Returns ``(send_off, send_rows, inbox_off, back_off)``: my rows for rank j start at
+    ``send_off[j]`` of my permuted buffer and land at ``inbox_off[j]`` of j's inbox (after
+    the rows of lower-ranked sources); rank s's rows sit at ``back_off[s]`` of my inbox."""
+    experts = counts_all.shape[1]
+    local = experts // world
+    per_dest = counts_all.reshape(world, world, local).sum(2)          # [src, dest]
+    send_rows = per_dest[rank].tolist()
+    send_off = [int(v) for v in (per_dest[rank].cumsum(0) - per_dest[rank]).tolist()]
+    before = per_dest.cumsum(0) - per_dest                              # rows of lower-ranked sources, per dest
+    inbox_off = [int(before[rank, j]) for j in range(world)]
+    back_off = [int(before[s, rank]) for s in range(world)]
+    return send_off, [int(v) for v in send_rows], inbox_off, back_off, per_dest
 
 
 # --------------------------------------------------------------------------- tensor-parallel MLP
@@ -384,17 +546,21 @@ class TensorParallelMlp:
     def backward(self, x, dy_local, dw_up, dw_down):
         """``dy_local`` is this rank's rows of dL/dy (layout of ``forward``'s output).
 
-        Accumulates the weight-gradient shards (fp32) and returns the full
-        ``dx [m, d]`` summed over ranks.  Piece by piece: the all-gather of the
-        next piece's ``dy`` and the all-reduce of the previous piece's ``dx`` run
-        on a side stream underneath the current piece's four GEMMs."""
+        Accumulates the weight-gradient shards (fp32) and returns this rank's rows
+        of ``dx`` (same row ownership as ``forward``'s output) after a
+        reduce-scatter -- the mirror image of the all-gather that hands the MLP its
+        replicated ``x``.  Piece by piece: the all-gather of the next piece's ``dy``
+        and the reduce-scatter of the previous piece's ``dx`` run on a side stream
+        underneath the current piece's four GEMMs."""
         m = x.shape[0]
         piece, share = m // self.chunks, m // (self.chunks * self.world)
         dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)
+        dx_local = torch.empty((self.chunks * share, x.shape[1]), dtype=self.partial_dtype, device=x.device)
         side = self._side_stream(x.device)
         main = torch.cuda.current_stream() if side is not None else None
         if side is not None:
             dx.record_stream(side)
+            dx_local.record_stream(side)
 
         def gather(c):
             dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
@@ -425,14 +591,15 @@ class TensorParallelMlp:
             self.ops.linear_weight_grad(xs, dh, dw_up)                    # dW_up += x^T dh
             dxs = dx[c * piece:(c + 1) * piece]
             self.ops.linear_input_grad_into(dh, self.w_up, dxs)           # dx piece (partial sum)
+            mine = dx_local[c * share:(c + 1) * share]
             if side is None:
-                dist.all_reduce(dxs, op=dist.ReduceOp.SUM, group=self.group)
+                dist.reduce_scatter_tensor(mine, dxs, op=dist.ReduceOp.SUM, group=self.group)
             else:
                 produced = torch.cuda.Event()
                 produced.record(main)
                 with torch.cuda.stream(side):
                     side.wait_event(produced)
-                    dist.all_reduce(dxs, op=dist.ReduceOp.SUM, group=self.group)
+                    dist.reduce_scatter_tensor(mine, dxs, op=dist.ReduceOp.SUM, group=self.group)
         if side is not None:
             main.wait_stream(side)
-        return dx
+        return dx_local

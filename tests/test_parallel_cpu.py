@@ -214,7 +214,7 @@ def case_tp_mlp(rank, par, ops, orc):
     dw1 = torch.zeros(d, ff // WORLD)
     dw2 = torch.zeros(ff // WORLD, d)
     dx = mlp.backward(torch.from_numpy(x), torch.from_numpy(dy_full[rows].copy()), dw1, dw2)
-    assert np.allclose(dx.numpy(), (dy_full @ w2.T) @ w1.T, atol=1e-3)
+    assert np.allclose(dx.numpy(), ((dy_full @ w2.T) @ w1.T)[rows], atol=1e-3)     # this rank's rows
     assert np.allclose(dw2.numpy(), ((x @ w1).T @ dy_full)[cols], atol=1e-3)
     assert np.allclose(dw1.numpy(), (x.T @ (dy_full @ w2.T))[:, cols], atol=1e-3)
 
@@ -234,6 +234,30 @@ def test_vocab_shards_cover_the_vocabulary_in_whole_tiles():
     assert all(a[1] == b[0] for a, b in zip(shards, shards[1:]))
     assert par.vocab_shards(50432, 1) == [(0, 50432)]
     assert par.vocab_shards(1000, 2) == [(0, 512), (512, 1000)]
+
+
+def test_exchange_plan_offsets_are_consistent_between_ranks():
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    par = entry.load_package().parallel
+    world, experts = 4, 8
+    rng = np.random.default_rng(3)
+    counts = torch.from_numpy(rng.integers(0, 50, size=(world, experts)))
+    plans = [par.exchange_plan(counts, r, world) for r in range(world)]
+    per_dest = plans[0][4]
+    for i in range(world):
+        send_off, send_rows, inbox_off, back_off, _ = plans[i]
+        assert send_rows == per_dest[i].tolist()
+        assert send_off == [int(per_dest[i, :j].sum()) for j in range(world)]
+        for j in range(world):
+            # my block in j's inbox starts after the blocks of lower-ranked sources ...
+            assert inbox_off[j] == int(per_dest[:i, j].sum())
+            # ... which is exactly where j expects source i's rows
+            assert plans[j][3][i] == inbox_off[j]
+    # inbox blocks tile [0, total) without gaps
+    for j in range(world):
+        ends = [plans[i][2][j] + plans[i][1][j] for i in range(world)]
+        assert ends[-1] == int(per_dest[:, j].sum())
 
 
 @pytest.mark.parametrize("case", sorted(CASES))

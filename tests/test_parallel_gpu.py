@@ -51,7 +51,11 @@ def _worker(rank, port, failures):
         assert abs(float(loss1.item()) - float(loss2.item())) < 5e-5
         assert torch.allclose(lse1, lse2, atol=2e-4, rtol=1e-5)
         _, dh2, dw2 = head.backward(h, ws, t, lse2)
-        assert torch.allclose(dh1, dh2, atol=2e-5, rtol=2e-2), float((dh1 - dh2).abs().max())
+        # partial sums cross the link as bf16: the GEMM contract's relative Frobenius bound
+        assert float((dh1 - dh2).norm() / dh1.norm()) < 1e-2
+        head32 = par.VocabParallelHead(ops, classes, v, reduce_dtype=torch.float32)
+        _, dh3, _ = head32.backward(h, ws, t, lse2)
+        assert torch.allclose(dh1, dh3, atol=2e-5, rtol=2e-2), float((dh1 - dh3).abs().max())
         assert torch.allclose(dw1[:, head.c0:head.c1], dw2, atol=2e-5, rtol=2e-2)
 
         # ---- expert-parallel MoE vs the single-GPU grouped path on this rank's tokens
@@ -67,6 +71,14 @@ def _worker(rank, port, failures):
                                    dn[rank * local:(rank + 1) * local].contiguous())
         out = ep.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
         assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5), float((out - ref).abs().max())
+        # the same exchange by copy-engine pushes into peer memory, in two slices, twice in a row
+        ep2 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=2,
+                                    use_peer_copies=True)
+        for _ in range(2):
+            out2 = ep2.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert ep2.last["exchange"] == "peer copies" and ep2.last["pieces"] == 2
+            assert torch.allclose(out2, ref, atol=1e-5, rtol=1e-5), float((out2 - ref).abs().max())
 
         # ---- tensor-parallel MLP vs the unsharded product of the same bf16 operands
         m, d, ff = 2048, 512, 1024
