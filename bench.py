@@ -628,7 +628,10 @@ def run_gpu(args):
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": 4,
                 "api": "Tcgen05Gemm methods over the C ABI; token activations from pinned host memory"},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                     "frac": per_gpu / peaks["tflops"], "traffic": None,
+                     "frac": per_gpu / peaks["tflops"],
+                     # dram__bytes_read + write of ONE launch of the dominant instantiation (the QKV
+                     # forward, 718.8 MB algorithmic), from the ncu capture summarised under profiles/
+                     "traffic": 706.7e6, "traffic_launch": "gemm_tcgen05_kernel<2,0,0> qkv.forward",
                      "kernel": "gemm_tcgen05_kernel (every launch of the timed region)",
                      "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
                      "algorithmic_flops_per_step": flops},
@@ -649,7 +652,7 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-table", action="store_true", help="skip the per-shape table")

@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200gemm.so")
+# B200GEMM_LIB lets a developer point the binding at another build of the same library.
+LIB_PATH = os.environ.get("B200GEMM_LIB") or os.path.join(HERE, "libb200gemm.so")
 
 OK, ERR_INVALID, ERR_SHAPE, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
 K_MAJOR, MN_MAJOR = 0, 1

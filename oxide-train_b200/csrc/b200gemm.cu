@@ -18,6 +18,10 @@
 #include "gemm_kernel.cuh"
 #include "moe_kernels.cuh"
 
+#ifndef B200_L2_PROMOTION
+#define B200_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+
 namespace {
 
 using namespace b200;
@@ -89,7 +93,7 @@ int encode_map(const b200gemm_context* ctx, CUtensorMap* map, CUtensorMapDataTyp
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = ctx->encode(map, dtype, 3, const_cast<void*>(base), dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                           B200_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(B200GEMM_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what,
                 static_cast<int>(r));

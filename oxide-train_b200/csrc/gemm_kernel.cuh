@@ -67,7 +67,10 @@ constexpr int kGemmThreads = 224;
 constexpr int kProducerWarp1 = 6;  // second TMA producer (warp 0 is the first)
 constexpr int kTmemCols = 512;    // two 256-column fp32 accumulators
 constexpr int kEpiBufBytes = 4096;  // 32 rows x 128 B, one per epilogue warp per buffer
-constexpr int kRasterGroupM = 8;  // tile rows walked together so B panels stay in L2
+#ifndef B200_RASTER_GROUP_M
+#define B200_RASTER_GROUP_M 8
+#endif
+constexpr int kRasterGroupM = B200_RASTER_GROUP_M;  // tile rows walked together so B panels stay in L2
 constexpr int kSubtileBytes = 64 * kBlockK * 2;  // one 64(mn) x 64(k) MN-major box
 constexpr int kMaxGroups = 192;   // groups a grouped launch can address (its tables share the SM with a 225 KiB ring)
 

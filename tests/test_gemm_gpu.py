@@ -227,3 +227,26 @@ def test_bounded_wait_reports_a_status_code_and_the_context_survives(pkg, oracle
     gemm.f32_store(a, b, c)
     assert gemm.device_status() == 0
     assert_gemm_close(c.cpu().numpy(), oracle.matmul_nt(av, bv, THREADS), "after timeout", rel_fro=2e-5, elem=2e-4)
+
+
+def test_host_buffer_form_copies_in_and_out(pkg, oracle, gemm):
+    """b200gemm_gemm_host: A, B (and C when accumulating) live in host memory."""
+    import ctypes as C
+    L = pkg._lib
+    M, N, K = 384, 256, 128
+    av = oracle.bf16_round(oracle.uniform(M * K, 71)).reshape(M, K)
+    bv = oracle.bf16_round(oracle.uniform(N * K, 72)).reshape(N, K)
+    a_bits = np.ascontiguousarray(oracle.bf16_bits(av))
+    b_bits = np.ascontiguousarray(oracle.bf16_bits(bv))
+    c = np.full((M, N), 2.0, np.float32)
+    d = L.GemmDesc()
+    d.a, d.b, d.c = a_bits.ctypes.data, b_bits.ctypes.data, c.ctypes.data
+    d.m, d.n, d.k = M, N, K
+    d.out_type, d.mode, d.batch = L.OUT_F32, L.STORE, 1
+    L.check(gemm._lib.b200gemm_gemm_host(gemm._h, None, C.byref(d)))
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    assert_gemm_close(c, ref, "host store", rel_fro=2e-5, elem=2e-4)
+    d.mode = L.ACCUMULATE
+    L.check(gemm._lib.b200gemm_gemm_host(gemm._h, None, C.byref(d)))
+    assert_gemm_close(c, 2 * ref, "host accumulate", rel_fro=2e-5, elem=2e-4)
+    assert gemm.device_status() == 0
