@@ -322,6 +322,48 @@ B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const v
                                       const void* residual, int64_t tokens, int32_t top_k, int64_t d,
                                       void* out, int32_t out_type);
 
+/*
+ * Expert parallelism over peer-mapped memory (new: the reference is single-GPU).
+ * Experts are split in contiguous blocks over `world` GPUs of one box (expert e
+ * lives on rank e / (experts / world)); every rank keeps its own tokens.  Each rank
+ * owns an inbox and a result buffer that its peers can address (memory mapped into
+ * every process, e.g. torch symmetric memory or CUDA IPC; `peer_*[r]` is rank r's
+ * buffer as seen from the calling process).  Row layout of rank j's inbox: blocks by
+ * source rank, inside a block by local expert, inside an expert by slot.  All three
+ * calls take their sizes from device memory: nothing is read back to the host.
+ *
+ *   plan          from all_counts[world][experts] (every rank's accepted_counts,
+ *                 all-gathered; device int32) computes, on the device,
+ *                 dst_base[experts]: where MY rows for expert e begin in owner(e)'s inbox;
+ *                 group_offsets[experts + 1], group_b_index[experts]: the (source rank,
+ *                 local expert) groups of MY inbox, for b200gemm_grouped_gemm_indexed.
+ *   push          writes x[token] into owner(e)'s inbox at dst_base[e] + slot for every
+ *                 selected expert of every token (peer stores over NVLink).  A row that
+ *                 would land at or beyond `inbox_rows` is not written and device status
+ *                 105 is recorded (b200gemm_device_status).
+ *   pull_combine  out[token] = residual + sum_r gate_r * results_of_owner[dst_base[e_r] + slot_r]
+ *                 (peer loads), ranks added in order in fp32; a row at or beyond
+ *                 `result_rows` is skipped and device status 105 recorded.
+ * The caller orders the phases between ranks (a barrier after every rank's push and
+ * after every rank's expert GEMMs); the kernels themselves never wait on a peer.
+ * world <= 8, experts a multiple of world and <= 192, top_k <= 16, d % 8 == 0.
+ */
+B200GEMM_API int b200gemm_moe_ep_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts,
+                                      int32_t world, int32_t rank, int32_t experts, int32_t* dst_base,
+                                      int32_t* group_offsets, int32_t* group_b_index);
+B200GEMM_API int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x,
+                                      const uint32_t* selected, const uint32_t* slots,
+                                      const int32_t* dst_base, void* const* peer_inbox,
+                                      int64_t inbox_rows, int32_t world, int32_t experts,
+                                      int64_t tokens, int32_t top_k, int64_t d);
+B200GEMM_API int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream,
+                                              void* const* peer_results, const uint32_t* selected,
+                                              const uint32_t* slots, const int32_t* dst_base,
+                                              const float* gates, const void* residual,
+                                              int64_t result_rows, int32_t world, int32_t experts,
+                                              int64_t tokens, int32_t top_k, int64_t d, void* out,
+                                              int32_t out_type);
+
 /* Synchronises `stream`, reads and clears the device status word; returns
  * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
  * *device_code (may be NULL).  The reference has no counterpart: its kernels

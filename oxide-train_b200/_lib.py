@@ -57,6 +57,15 @@ SIGNATURES = {
                                         C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
     "b200gemm_moe_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32,
                                      C.c_int32, C.c_int64] + [C.c_void_p] * 7),
+    "b200gemm_moe_ep_plan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200gemm_moe_ep_push": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.POINTER(C.c_void_p), C.c_int64, C.c_int32, C.c_int32, C.c_int64,
+                                       C.c_int32, C.c_int64]),
+    "b200gemm_moe_ep_pull_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                               C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int64,
+                                               C.c_void_p, C.c_int32]),
     "b200gemm_moe_scatter": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                        C.c_int64, C.c_void_p]),
     "b200gemm_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -9,6 +9,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <new>
 
@@ -65,8 +66,13 @@ struct b200gemm_context {
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
   bool smem_opt_in[2][8] = {};   // [cta_group - 1][epilogue kind]
-  void* moe_scratch = nullptr;   // per-segment expert counts of b200gemm_moe_route
-  size_t moe_scratch_bytes = 0;
+  // per-segment expert counts of b200gemm_moe_route: one buffer per stream, so that routing
+  // calls issued on different streams can overlap on the GPU without sharing scratch
+  struct Scratch {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+  };
+  std::map<cudaStream_t, Scratch> moe_scratch;
   std::mutex mu;
 };
 
@@ -673,7 +679,8 @@ int b200gemm_destroy(b200gemm_handle_t h) {
   cudaSetDevice(h->device);
   for (void* p : h->stage)
     if (p) cudaFree(p);
-  if (h->moe_scratch) cudaFree(h->moe_scratch);
+  for (auto& kv : h->moe_scratch)
+    if (kv.second.ptr) cudaFree(kv.second.ptr);
   if (h->status) cudaFree(h->status);
   delete h;
   return B200GEMM_OK;
@@ -807,17 +814,19 @@ int b200gemm_moe_route(b200gemm_handle_t h, void* stream_, const float* scores,
   // grown on first use and whenever a larger problem arrives.
   const long long segments = (pairs + kMoeSegment - 1) / kMoeSegment;
   const size_t table_bytes = static_cast<size_t>(segments) * experts * sizeof(uint32_t);
+  uint32_t* seg_table = nullptr;
   {
     std::lock_guard<std::mutex> lock(h->mu);
-    if (h->moe_scratch_bytes < table_bytes) {
-      if (h->moe_scratch) CUDA_TRY(cudaFree(h->moe_scratch));   // waits for kernels still using it
-      h->moe_scratch = nullptr;
-      h->moe_scratch_bytes = 0;
-      CUDA_TRY(cudaMalloc(&h->moe_scratch, table_bytes));
-      h->moe_scratch_bytes = table_bytes;
+    b200gemm_context::Scratch& sc = h->moe_scratch[stream];
+    if (sc.bytes < table_bytes) {
+      if (sc.ptr) CUDA_TRY(cudaFree(sc.ptr));   // waits for kernels still using it
+      sc.ptr = nullptr;
+      sc.bytes = 0;
+      CUDA_TRY(cudaMalloc(&sc.ptr, table_bytes));
+      sc.bytes = table_bytes;
     }
+    seg_table = static_cast<uint32_t*>(sc.ptr);
   }
-  uint32_t* seg_table = static_cast<uint32_t*>(h->moe_scratch);
   const int seg_blocks = static_cast<int>((segments + 7) / 8);
   moe_hist_kernel<<<seg_blocks, 256, 0, stream>>>(selected, pairs, experts, seg_table);
   CUDA_TRY(cudaGetLastError());
@@ -910,6 +919,79 @@ int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream, const 
   if (rc) return rc;
   return ce_forward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, m, k, v,
                     classes, lse, row_loss, loss, scratch, kCeStaticBytes);
+}
+
+int b200gemm_moe_ep_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts, int32_t world,
+                         int32_t rank, int32_t experts, int32_t* dst_base, int32_t* group_offsets,
+                         int32_t* group_b_index) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!all_counts || !dst_base || !group_offsets || !group_b_index) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (world < 1 || world > kMoeMaxPeers || rank < 0 || rank >= world)
+    return fail(B200GEMM_ERR_SHAPE, "world must be in [1, %d] and rank inside it", kMoeMaxPeers);
+  if (experts < world || experts > kMaxGroups || experts % world)
+    return fail(B200GEMM_ERR_SHAPE, "experts must be a multiple of world and at most %d", kMaxGroups);
+  moe_ep_plan_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(all_counts, world, rank, experts, dst_base,
+                                                                      group_offsets, group_b_index);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const uint32_t* selected,
+                         const uint32_t* slots, const int32_t* dst_base, void* const* peer_inbox,
+                         int64_t inbox_rows, int32_t world, int32_t experts, int64_t tokens,
+                         int32_t top_k, int64_t d) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!x || !selected || !slots || !dst_base || !peer_inbox) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (inbox_rows <= 0) return fail(B200GEMM_ERR_SHAPE, "inbox_rows must be positive");
+  if (world < 1 || world > kMoeMaxPeers || experts % world) return fail(B200GEMM_ERR_SHAPE, "bad world / experts");
+  if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
+  PeerPointers pp = {};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_inbox[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
+    pp.ptr[r] = static_cast<uint16_t*>(peer_inbox[r]);
+  }
+  // Two 256-thread CTAs per SM at most: the link, not the SMs, bounds this kernel, and a
+  // persistent GEMM CTA (224 threads, nearly all shared memory) must still fit beside them.
+  const int push_grid = std::min(stream_grid(tokens * 32, h->sm_total), 2 * h->sm_total);
+  moe_ep_push_kernel<<<push_grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), selected, slots, dst_base, pp, experts / world, tokens, top_k, d,
+      inbox_rows, h->status);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const* peer_results,
+                                 const uint32_t* selected, const uint32_t* slots,
+                                 const int32_t* dst_base, const float* gates, const void* residual,
+                                 int64_t result_rows, int32_t world, int32_t experts, int64_t tokens,
+                                 int32_t top_k, int64_t d, void* out, int32_t out_type) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!peer_results || !selected || !slots || !dst_base || !gates || !out) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (world < 1 || world > kMoeMaxPeers || experts % world) return fail(B200GEMM_ERR_SHAPE, "bad world / experts");
+  if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
+  if (out_type < 0 || out_type > 1) return fail(B200GEMM_ERR_INVALID, "bad output type");
+  PeerPointers pp = {};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_results[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
+    pp.ptr[r] = static_cast<uint16_t*>(peer_results[r]);
+  }
+  const int grid = std::min(stream_grid(tokens * 32, h->sm_total), 2 * h->sm_total);   // see b200gemm_moe_ep_push
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_type == B200GEMM_OUT_BF16)
+    moe_ep_pull_combine_kernel<true><<<grid, 256, 0, s>>>(pp, selected, slots, dst_base, gates,
+                                                          static_cast<const uint16_t*>(residual), experts / world,
+                                                          tokens, top_k, d, result_rows, h->status, out);
+  else
+    moe_ep_pull_combine_kernel<false><<<grid, 256, 0, s>>>(pp, selected, slots, dst_base, gates,
+                                                           static_cast<const uint16_t*>(residual), experts / world,
+                                                           tokens, top_k, d, result_rows, h->status, out);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
 }
 
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {

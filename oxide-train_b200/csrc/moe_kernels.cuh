@@ -328,4 +328,190 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
   }
 }
 
+// ------------------------------------------------------------------ expert parallelism over peer memory
+// Device-driven dispatch for experts spread over the GPUs of one box (contiguous
+// blocks: expert e lives on rank e / (experts / world)).  Every rank owns an
+// "inbox" that its peers can address (peer-mapped device memory); a routed row is
+// written straight into the owner's inbox by the rank that holds the token, and
+// read back from the owner's result buffer by the same rank.  Row layout of an
+// inbox: blocks by source rank, inside a block sorted by local expert, inside an
+// expert by slot -- so the owner multiplies what arrived as (source, expert)
+// groups without moving it.  All offsets come from the all-gathered per-expert
+// counts on the device; the host never sees a count.
+constexpr int kMoeMaxPeers = 8;
+
+struct PeerPointers {
+  uint16_t* ptr[kMoeMaxPeers];
+};
+
+// One block.  all_counts[src * experts + e] = rows rank `src` routes to expert e.
+//   dst_base[e]      row of owner(e)'s inbox where MY rows for expert e begin
+//   group_offsets[g] first inbox row of group g = (src, local expert) of MY inbox; g in [0, experts]
+//   group_b_index[g] local expert of group g
+__global__ void moe_ep_plan_kernel(const int* __restrict__ all_counts, int world, int rank,
+                                   int experts, int* __restrict__ dst_base,
+                                   int* __restrict__ group_offsets, int* __restrict__ group_b_index) {
+  const int local = experts / world;
+  if (threadIdx.x == 0) {
+    // my rows in each owner's inbox
+    for (int owner = 0; owner < world; ++owner) {
+      int base = 0;
+      for (int s = 0; s < rank; ++s)
+        for (int e = 0; e < local; ++e) base += all_counts[s * experts + owner * local + e];
+      for (int e = 0; e < local; ++e) {
+        dst_base[owner * local + e] = base;
+        base += all_counts[rank * experts + owner * local + e];
+      }
+    }
+    // groups of my own inbox
+    int run = 0;
+    for (int s = 0; s < world; ++s)
+      for (int e = 0; e < local; ++e) {
+        group_offsets[s * local + e] = run;
+        group_b_index[s * local + e] = e;
+        run += all_counts[s * experts + rank * local + e];
+      }
+    group_offsets[experts] = run;
+  }
+}
+
+// Dispatch: one warp per token reads the token's row once and stores it into the
+// inbox of each selected expert's owner (a plain peer store over NVLink, or a
+// local store when this rank owns the expert).
+__global__ void __launch_bounds__(256) moe_ep_push_kernel(const uint16_t* __restrict__ x,
+                                                          const uint32_t* __restrict__ selected,
+                                                          const uint32_t* __restrict__ slots,
+                                                          const int* __restrict__ dst_base,
+                                                          PeerPointers inbox, int experts_per_rank,
+                                                          long long tokens, int top_k, long long d,
+                                                          long long inbox_rows, int* status) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long vecs = d / 8;
+  for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + token * d);
+    int my_owner = -1;
+    long long my_row = 0;
+    if (lane < top_k) {
+      const uint32_t e = selected[token * top_k + lane];
+      const uint32_t s = slots[token * top_k + lane];
+      if (s != kMoeDropped) {
+        my_owner = static_cast<int>(e) / experts_per_rank;
+        my_row = static_cast<long long>(dst_base[e]) + s;
+        if (my_row >= inbox_rows) {          // the owner's inbox is too small: drop the row, report it
+          my_owner = -1;
+          atomicCAS(status, 0, 105);
+        }
+      }
+    }
+    for (long long v0 = 0; v0 < vecs; v0 += 128) {
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long v = v0 + u * 32 + lane;
+        if (v < vecs) val[u] = src[v];
+      }
+      for (int r = 0; r < top_k; ++r) {
+        const int owner = __shfl_sync(0xffffffffu, my_owner, r);
+        const long long row = __shfl_sync(0xffffffffu, my_row, r);
+        if (owner < 0) continue;
+        uint4* out = reinterpret_cast<uint4*>(inbox.ptr[owner] + row * d);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const long long v = v0 + u * 32 + lane;
+          if (v < vecs) out[v] = val[u];
+        }
+      }
+    }
+  }
+}
+
+// Combine: out[token, :] = residual + sum over ranks (in order) of gate * result row,
+// each result row read from its expert owner's result buffer (plain peer loads).
+template <bool kOutBf16>
+__global__ void __launch_bounds__(256) moe_ep_pull_combine_kernel(PeerPointers results,
+                                                                  const uint32_t* __restrict__ selected,
+                                                                  const uint32_t* __restrict__ slots,
+                                                                  const int* __restrict__ dst_base,
+                                                                  const float* __restrict__ gates,
+                                                                  const uint16_t* __restrict__ residual,
+                                                                  int experts_per_rank, long long tokens,
+                                                                  int top_k, long long d,
+                                                                  long long result_rows, int* status,
+                                                                  void* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long vecs = d / 8;
+  for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    const uint16_t* my_ptr = nullptr;
+    float my_gate = 0.f;
+    if (lane < top_k) {
+      const uint32_t e = selected[token * top_k + lane];
+      const uint32_t s = slots[token * top_k + lane];
+      if (s != kMoeDropped) {
+        const long long row = static_cast<long long>(dst_base[e]) + s;
+        if (row < result_rows) {
+          my_ptr = results.ptr[static_cast<int>(e) / experts_per_rank] + row * d;
+          my_gate = gates[token * top_k + lane];
+        } else {
+          atomicCAS(status, 0, 105);       // outside the owner's buffer: skip the row, report it
+        }
+      }
+    }
+    const uint16_t* rows[kMoeMaxTopK];
+    float gs[kMoeMaxTopK];
+#pragma unroll
+    for (int r = 0; r < kMoeMaxTopK; ++r) {
+      rows[r] = reinterpret_cast<const uint16_t*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_ptr), r));
+      gs[r] = __shfl_sync(0xffffffffu, my_gate, r);
+    }
+    for (long long v = lane; v < vecs; v += 32) {
+      float acc[8];
+      if (residual) {
+        const uint4 r = reinterpret_cast<const uint4*>(residual + token * d)[v];
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] = __uint_as_float(w[j] << 16);
+          acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      }
+#pragma unroll
+      for (int r0 = 0; r0 < kMoeMaxTopK; r0 += 4) {
+        if (r0 >= top_k) break;
+        uint4 y[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (rows[r0 + u]) y[u] = reinterpret_cast<const uint4*>(rows[r0 + u])[v];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (!rows[r0 + u]) continue;
+          const float g = gs[r0 + u];
+          const uint32_t w[4] = {y[u].x, y[u].y, y[u].z, y[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(g, __uint_as_float(w[j] << 16)));
+            acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(g, __uint_as_float(w[j] & 0xffff0000u)));
+          }
+        }
+      }
+      if (kOutBf16) {
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ow[j]) : "f"(acc[2 * j + 1]), "f"(acc[2 * j]));
+        reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + token * d)[v] = o;
+      } else {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + token * d) + 2 * v;
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+    }
+  }
+}
+
 }  // namespace b200

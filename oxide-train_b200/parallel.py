@@ -114,6 +114,49 @@ class DeviceOps:
             out.stride(0), offsets.data_ptr(), group_b_index.numel(), rows, n, k, int(silu)))
         return out
 
+    def grouped_indexed_into(self, a, b, offsets, group_b_index, silu, out):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        rows, k = a.shape
+        n = b.shape[2]
+        L.check(self.gemm._lib.b200gemm_grouped_gemm_indexed(
+            self.gemm._h, _stream_ptr(), a.data_ptr(), a.stride(0), b.data_ptr(), L.MN_MAJOR,
+            b.stride(1), b.stride(0), b.shape[0], group_b_index.data_ptr(), out.data_ptr(),
+            out.stride(0), offsets.data_ptr(), group_b_index.numel(), rows, n, k, int(silu)))
+        return out
+
+    def ep_plan(self, all_counts, world, rank, experts):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        dev = all_counts.device
+        dst_base = torch.empty(experts, dtype=torch.int32, device=dev)
+        offsets = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+        index = torch.empty(experts, dtype=torch.int32, device=dev)
+        L.check(self.gemm._lib.b200gemm_moe_ep_plan(self.gemm._h, _stream_ptr(), all_counts.data_ptr(), world,
+                                                    rank, experts, dst_base.data_ptr(), offsets.data_ptr(),
+                                                    index.data_ptr()))
+        return dst_base, offsets, index
+
+    def ep_push(self, x, routing, dst_base, peer_ptrs, inbox_rows, world, experts):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        tokens, d = x.shape
+        L.check(self.gemm._lib.b200gemm_moe_ep_push(
+            self.gemm._h, _stream_ptr(), x.data_ptr(), routing.selected_experts.data_ptr(),
+            routing.slots.data_ptr(), dst_base.data_ptr(), peer_ptrs, inbox_rows, world, experts, tokens,
+            routing.top_k, d))
+
+    def ep_pull_combine(self, peer_ptrs, routing, dst_base, residual, result_rows, world, experts, d, out):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        L.check(self.gemm._lib.b200gemm_moe_ep_pull_combine(
+            self.gemm._h, _stream_ptr(), peer_ptrs, routing.selected_experts.data_ptr(),
+            routing.slots.data_ptr(), dst_base.data_ptr(), routing.gate_weights.data_ptr(),
+            residual.data_ptr() if residual is not None else None, result_rows, world, experts,
+            routing.tokens, routing.top_k, d, out.data_ptr(),
+            L.OUT_F32 if out.dtype == torch.float32 else L.OUT_BF16))
+        return out
+
     # dense GEMMs (weights are [IN, OUT], read in place)
     def linear(self, x, w, out_dtype=torch.bfloat16):
         y = torch.empty((x.shape[0], w.shape[1]), dtype=out_dtype, device=x.device)
@@ -249,10 +292,12 @@ class ExpertParallelMoe:
     ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
 
     def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces: int = 1,
-                 use_peer_copies: bool = False):
+                 use_peer_copies: bool = False, exchange: str = "nccl"):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
         self.pieces, self._side = pieces, None
         self.use_peer_copies, self._peer, self._peer_shape, self._index = use_peer_copies, None, None, None
+        self.exchange, self._dev = exchange, None       # "nccl" | "device" (peer stores / loads)
+        self.reserve_sms = 4                            # SMs kept free of GEMM CTAs in the device path
         self.world, self.rank = _world(group)
         if experts % self.world:
             raise ValueError("experts must divide evenly over the ranks")
@@ -269,9 +314,110 @@ class ExpertParallelMoe:
             yp = self.ops.grouped_indexed(hidden, self.w_down, r.offsets, index, False)
             self.last = {"rows_received": xp.shape[0], "rows_sent": xp.shape[0], "routing": r}
             return self.ops.combine(yp, r, residual, out_dtype)
+        if self.exchange == "device" and x.device.type == "cuda":
+            return self._forward_device(x, scores, scores_are_logits, residual, out_dtype)
         if self.use_peer_copies and x.device.type == "cuda":
             return self._forward_peer(x, scores, scores_are_logits, residual, out_dtype)
         return self._forward_pipelined(x, scores, scores_are_logits, residual, out_dtype)
+
+    def _forward_device(self, x, scores, scores_are_logits, residual, out_dtype):
+        """Several GPUs, device-driven exchange: nothing is read back to the host.
+
+        Per slice of tokens: route; all-gather the per-expert counts; a plan kernel turns
+        them into inbox offsets; a push kernel writes every routed row straight into its
+        expert owner's inbox (peer stores); barrier; the two grouped GEMMs run on what
+        arrived; barrier; a combine kernel reads each result row from its owner's result
+        buffer (peer loads).  Slices alternate between two streams, so the NVLink traffic
+        of one slice runs beside the tensor-core work of the other; the whole step is
+        enqueued without a host round trip."""
+        import ctypes as C
+        n, d = x.shape
+        ff, d_out = self.w_up.shape[2], self.w_down.shape[2]
+        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+        step = n // pieces
+        cap = step * self.top_k * self.world                # worst case: every row of every rank lands here
+        key = (pieces, cap, d, ff, d_out)
+        if self._dev is None or self._dev["key"] != key:
+            import torch.distributed._symmetric_memory as symm_mem
+            grp = self.group if self.group is not None else dist.group.WORLD
+            inbox = symm_mem.empty((pieces * cap, d), dtype=torch.bfloat16, device=x.device)
+            results = symm_mem.empty((pieces * cap, d_out), dtype=torch.bfloat16, device=x.device)
+            h_in = symm_mem.rendezvous(inbox, grp.group_name)
+            h_res = symm_mem.rendezvous(results, grp.group_name)
+            ptrs_in, ptrs_res = [], []
+            for p in range(pieces):
+                a_in = (C.c_void_p * self.world)()
+                a_res = (C.c_void_p * self.world)()
+                for r in range(self.world):
+                    a_in[r] = h_in.get_buffer(r, (pieces * cap, d), torch.bfloat16).data_ptr() + p * cap * d * 2
+                    a_res[r] = h_res.get_buffer(r, (pieces * cap, d_out), torch.bfloat16).data_ptr() + p * cap * d_out * 2
+                ptrs_in.append(a_in)
+                ptrs_res.append(a_res)
+            self._dev = {"key": key, "inbox": inbox, "results": results, "handles": (h_in, h_res),
+                         "ptrs_in": ptrs_in, "ptrs_res": ptrs_res,
+                         "hidden": torch.empty((pieces * cap, ff), dtype=torch.bfloat16, device=x.device),
+                         "token": torch.zeros(1, device=x.device)}
+        dv = self._dev
+        out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
+        # The expert GEMMs leave a few SMs free: a persistent GEMM CTA takes all of an SM's
+        # shared memory, and the one-element all-reduces used as barriers (and the other
+        # slice's small kernels) would otherwise wait for a whole GEMM to drain.
+        if hasattr(self.ops, "gemm") and self.reserve_sms:
+            self.ops.gemm.set_sm_limit(self._sm_total(x.device) - self.reserve_sms)
+        try:
+            return self._forward_device_body(x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out)
+        finally:
+            if hasattr(self.ops, "gemm") and self.reserve_sms:
+                self.ops.gemm.set_sm_limit(0)
+
+    def _sm_total(self, device):
+        return torch.cuda.get_device_properties(device).multi_processor_count
+
+    def _forward_device_body(self, x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out):
+        n = x.shape[0]
+        streams = self._streams(x.device) if pieces > 1 else [torch.cuda.current_stream()]
+        main = torch.cuda.current_stream()
+        routed = []
+        # Stage 1, every slice: route, plan, push, barrier.  Issued for all slices before
+        # any GEMM so that the collectives (which NCCL runs in issue order) of a later
+        # slice are not queued behind an earlier slice's post-GEMM barrier.
+        for p in range(pieces):
+            sl = slice(p * step, (p + 1) * step)
+            st = streams[p % len(streams)]
+            if st is not main:
+                st.wait_stream(main)
+            with torch.cuda.stream(st):
+                r = self.ops.route(scores[sl].contiguous(), self.top_k, scores_are_logits)
+                allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
+                dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
+                dst_base, offsets, index = self.ops.ep_plan(allc, self.world, self.rank, self.experts)
+                self.ops.ep_push(x[sl], r, dst_base, dv["ptrs_in"][p], cap, self.world, self.experts)
+                dist.all_reduce(dv["token"], group=self.group)        # every rank's rows have landed
+                if st is not main:
+                    for tns in (allc, dst_base, offsets, index):
+                        tns.record_stream(st)
+            routed.append((sl, r, dst_base, offsets, index))
+        # Stage 2, every slice: expert GEMMs on what arrived, barrier, pull + combine.
+        for p, (sl, r, dst_base, offsets, index) in enumerate(routed):
+            st = streams[p % len(streams)]
+            with torch.cuda.stream(st):
+                inbox = dv["inbox"][p * cap:(p + 1) * cap]
+                hidden = dv["hidden"][p * cap:(p + 1) * cap]
+                res = dv["results"][p * cap:(p + 1) * cap]
+                self.ops.grouped_indexed_into(inbox, self.w_up, offsets, index, True, hidden)
+                self.ops.grouped_indexed_into(hidden, self.w_down, offsets, index, False, res)
+                dist.all_reduce(dv["token"], group=self.group)        # every rank's results are complete
+                self.ops.ep_pull_combine(dv["ptrs_res"][p], r, dst_base, residual[sl] if residual is not None else None,
+                                         cap, self.world, self.experts, d_out, out[sl])
+                if st is not main:
+                    out.record_stream(st)
+        for st in streams:
+            if st is not main:
+                main.wait_stream(st)
+        routed = [t[1] for t in routed]
+        self.last = {"routing": routed[0], "pieces": pieces, "exchange": "device",
+                     "rows_received": None, "rows_sent": n * self.top_k, "offsets": offsets}
+        return out
 
     def _forward_peer(self, x, scores, scores_are_logits, residual, out_dtype):
         """Several GPUs, copy-engine exchange.  The tokens go through in ``pieces`` slices:

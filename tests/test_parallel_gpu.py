@@ -80,6 +80,15 @@ def _worker(rank, port, failures):
             assert ep2.last["exchange"] == "peer copies" and ep2.last["pieces"] == 2
             assert torch.allclose(out2, ref, atol=1e-5, rtol=1e-5), float((out2 - ref).abs().max())
 
+        # the device-driven exchange (peer stores / peer loads, no host round trip), twice in a row
+        ep3 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=2, exchange="device")
+        for _ in range(2):
+            out3 = ep3.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert ep3.last["exchange"] == "device"
+            assert torch.allclose(out3, ref, atol=1e-5, rtol=1e-5), float((out3 - ref).abs().max())
+        assert gemm.device_status() == 0
+
         # ---- tensor-parallel MLP vs the unsharded product of the same bf16 operands
         m, d, ff = 2048, 512, 1024
         x2 = torch.randn((m, d), generator=gen, device=dev).to(bf)
