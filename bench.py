@@ -233,27 +233,53 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
         ms = s.elapsed_time(e) / iters
         return ms, flops / ms / 1e9
 
+    # Comparator column: the same products through cuBLASLt (torch.mm, fp32 output like the
+    # rows they stand beside), timed the same way.  Reported only; not on the product path.
+    f32 = torch.float32
+
+    def cublas(fn, flops):
+        try:
+            return round(timed(fn, flops)[1], 1)
+        except Exception:                                   # a torch build without out_dtype
+            return None
+
     for name, i, o in PROJECTIONS:
         fl = 2.0 * M_TOKENS * i * o
         w, dw = layer[name]["w"], layer[name]["dw"]
-        for kind, fn in (
-            ("forward", lambda: gemm.f32_store(buf.x[i], w, buf.y[o], transposed_b=True)),
-            ("input_grad", lambda: gemm.f32_store(buf.dy[o], w, buf.y[i])),
-            ("weight_grad", lambda: gemm.f32_accumulate_transposed(buf.x[i], buf.dy[o], dw)),
+        x, dy = buf.x[i], buf.dy[o]
+        for kind, fn, ref in (
+            ("forward", lambda: gemm.f32_store(x, w, buf.y[o], transposed_b=True),
+             lambda: torch.mm(x, w, out_dtype=f32)),
+            ("input_grad", lambda: gemm.f32_store(dy, w, buf.y[i]),
+             lambda: torch.mm(dy, w.t(), out_dtype=f32)),
+            ("weight_grad", lambda: gemm.f32_accumulate_transposed(x, dy, dw),
+             lambda: torch.mm(x.t(), dy, out_dtype=f32)),     # overwrite: cuBLASLt's cheaper case
         ):
             ms, tf = timed(fn, fl)
-            rows.append({"gemm": f"{name}.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
+            rows.append({"gemm": f"{name}.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1),
+                         "cublaslt_tflops": cublas(ref, fl)})
     fl = 2.0 * M_TOKENS * D_MODEL * VOCAB_PAD
     lse = head.forward(buf.x[D_MODEL], buf.head_w, buf.targets)[1]
-    for kind, fn, credit in (
-        ("fused_forward", lambda: head.forward(buf.x[D_MODEL], buf.head_w, buf.targets), fl),
-        # recompute + two gradient products; only the two products are credited
-        ("fused_backward", lambda: head.backward(buf.x[D_MODEL], buf.head_w, buf.targets, lse,
+    h = buf.x[D_MODEL]
+
+    def two_products():
+        torch.mm(buf.dlogits, buf.head_w.t(), out_dtype=f32)
+        torch.mm(h.t(), buf.dlogits, out_dtype=f32)
+
+    for kind, fn, credit, ref in (
+        # comparator: the logits product alone (bf16 logits written to HBM, no classifier)
+        ("fused_forward", lambda: head.forward(h, buf.head_w, buf.targets), fl,
+         lambda: torch.mm(h, buf.head_w)),
+        # recompute + two gradient products; only the two products are credited.
+        # comparator: the two products alone, on dlogits already in HBM
+        ("fused_backward", lambda: head.backward(h, buf.head_w, buf.targets, lse,
                                                  dlogits=buf.dlogits, d_hidden=buf.dh,
-                                                 d_weight=buf.head_dw, accumulate_dw=True), 2 * fl),
+                                                 d_weight=buf.head_dw, accumulate_dw=True), 2 * fl,
+         two_products),
     ):
         ms, tf = timed(fn, credit)
-        rows.append({"gemm": f"lm_head.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1)})
+        rows.append({"gemm": f"lm_head.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1),
+                     "cublaslt_tflops": cublas(ref, credit)})
     return rows
 
 
@@ -494,8 +520,14 @@ def run_only(args):
         x = torch.randn((n_tok, d), device=dev).to(bf)
         bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
         logits = (torch.randn((n_tok, experts), device=dev) + bias).contiguous()
-        ffn = pkg.GroupedExpertFfn(gemm, (torch.randn((experts, d, ff), device=dev) * 0.02).to(bf),
-                                   (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
+        if kind == "gated_forward":        # the reference's own expert: SwiGLU over a fused gate/up projection
+            ffn = pkg.GatedExpertFfn(gemm, (torch.randn((experts, d, 2, ff), device=dev) * 0.02).to(bf),
+                                     (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
+            flops = 2.0 * n_tok * top_k * d * ff * 3
+        else:
+            ffn = pkg.GroupedExpertFfn(gemm, (torch.randn((experts, d, ff), device=dev) * 0.02).to(bf),
+                                       (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
+            flops = 2.0 * n_tok * top_k * d * ff * 2
         fn = lambda: ffn.forward(x, logits, top_k, scores_are_logits=True)
         for _ in range(args.warmup):
             fn()
@@ -508,7 +540,43 @@ def run_only(args):
         torch.cuda.synchronize()
         ms = s0.elapsed_time(e0) / args.steps
         print(json.dumps({"only": args.only, "tokens": n_tok, "ms": ms,
-                          "tflops": 2.0 * n_tok * top_k * d * ff * 2 / ms / 1e9,
+                          "tflops": flops / ms / 1e9,
+                          "device_status": gemm.device_status()}), flush=True)
+        gemm.close()
+        return
+    if name == "mlp_gate_up":
+        # Dense gated MLP, x [m, D] . W [D, 2, FF]: the fused launch (activation in the
+        # epilogue, panel kept for the backward) against the same product as a plain
+        # bf16 GEMM followed by a separate activation pass over the panel.
+        m = args.only_tokens
+        x = torch.randn((m, D_MODEL), device=dev).to(bf)
+        w = (torch.randn((1, D_MODEL, 2, D_FF), device=dev) * 0.02).to(bf)
+        offs = torch.tensor([0, m], dtype=torch.int32, device=dev)
+        y = torch.empty((m, D_FF), device=dev, dtype=bf)
+        panel = torch.empty((m, 2, D_FF), device=dev, dtype=bf)
+        w2 = w.reshape(D_MODEL, 2 * D_FF)
+
+        def unfused():
+            gemm.gemm(x, w2, panel.view(m, 2 * D_FF), transposed_b=True)
+            torch.mul(torch.nn.functional.silu(panel[:, 0].float()), panel[:, 1].float()).to(bf)
+
+        variants = {"swiglu": lambda: pkg.moe.grouped_gemm_swiglu(gemm, x, w, offs, out=y, gate_up=panel),
+                    "swiglu_no_panel": lambda: pkg.moe.grouped_gemm_swiglu(gemm, x, w, offs, out=y),
+                    "plain_gemm_only": lambda: gemm.gemm(x, w2, panel.view(m, 2 * D_FF), transposed_b=True),
+                    "unfused": unfused}
+        fn = variants[kind]
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            fn()
+        e0.record()
+        torch.cuda.synchronize()
+        ms = s0.elapsed_time(e0) / args.steps
+        print(json.dumps({"only": args.only, "tokens": m, "ms": ms,
+                          "tflops": 2.0 * m * D_MODEL * 2 * D_FF / ms / 1e9,
                           "device_status": gemm.device_status()}), flush=True)
         gemm.close()
         return
@@ -659,7 +727,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default=None,
                     help="profiling aid: run one piece, e.g. qkv.forward, mlp_up.weight_grad, lm_head.fused_forward, "
-                         "lm_head.fused_backward, moe.forward")
+                         "lm_head.fused_backward, moe.forward, moe.gated_forward, "
+                         "mlp_gate_up.{swiglu,swiglu_no_panel,plain_gemm_only,unfused}")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
                     help="dense_step (default) is the headline; the others are the sharded configurations")

@@ -265,7 +265,9 @@ B200GEMM_API int b200gemm_lmhead_ce_backward(b200gemm_handle_t h, void* stream, 
  *   c        device bf16 [total_rows, n], row stride ldc (0 = n; multiple of 8)
  *   offsets  DEVICE int32 [groups + 1], non-decreasing, offsets[groups] <= total_rows
  *            (the expert offsets the router produces; never read on the host)
- *   activation 0 = none, 1 = SiLU x*sigmoid(x) (crates/nn/src/swiglu.rs:22-28)
+ *   activation 0 = none, 1 = SiLU x*sigmoid(x) (crates/nn/src/swiglu.rs:22-28),
+ *              2 = SwiGLU: every B matrix holds 2*n columns, [gate(n) | up(n)], and
+ *                  C[rows, n] = silu(gate) * up (see b200gemm_grouped_gemm_swiglu)
  * Rows of C outside every group are left untouched.  groups <= 192.
  */
 B200GEMM_API int b200gemm_grouped_gemm(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
@@ -285,6 +287,30 @@ B200GEMM_API int b200gemm_grouped_gemm_indexed(b200gemm_handle_t h, void* stream
                                                const int32_t* offsets, int32_t groups,
                                                int64_t total_rows, int64_t n, int64_t k,
                                                int32_t activation);
+
+/*
+ * The gate/up product of a gated MLP fused with its activation.  Replaces the pair
+ * "fused gate/up GEMM into a [rows, 2, ff] panel" + `swiglu_forward_interleaved_packed`
+ * (gpu/model/src/lib.rs:1913-2154 expert_linear_forward over `[E,D,2,FF]` weights;
+ * gpu/ops/src/lib.rs:1149-1222): every B matrix is [k, 2*ff] (MN-major, the
+ * reference's `[D, 2, FF]`) or [2*ff, k] (K-major), gate block first, and
+ *   y[rows, ff] = silu(gate) * up            (bf16; the activation is applied to the
+ *                                             fp32 accumulators, so the panel's bf16
+ *                                             rounding is not in y)
+ *   gate_up[rows, 2*ff] = [gate | up]        (bf16, optional: NULL skips it; it is what
+ *                                             the backward of the activation reads)
+ * in ONE launch: the panel is never read back.  Groups and `group_b_index` (NULL =
+ * group g uses B[g], then b_count is ignored) as in b200gemm_grouped_gemm_indexed;
+ * one group with offsets {0, rows} is the dense gated MLP.  ff % 8 == 0, and
+ * ff % 64 == 0 when the panel is written; ldy, ld_gate_up in elements (0 = packed).
+ */
+B200GEMM_API int b200gemm_grouped_gemm_swiglu(b200gemm_handle_t h, void* stream, const void* a,
+                                              int64_t lda, const void* b, int32_t b_layout,
+                                              int64_t ldb, int64_t batch_stride_b, int32_t b_count,
+                                              const int32_t* group_b_index, void* y, int64_t ldy,
+                                              void* gate_up, int64_t ld_gate_up,
+                                              const int32_t* offsets, int32_t groups,
+                                              int64_t total_rows, int64_t ff, int64_t k);
 
 /*
  * MoE routing integers and gates (crates/nn/src/moe.rs:205-254 `MoeFfn::route`;

@@ -141,11 +141,43 @@ class Tcgen05Gemm {
     return b200gemm_moe_combine(h_, stream, y_permuted, dest_row, gates, residual, tokens, top_k, d, out,
                                 out_type);
   }
+  // Expert-parallel exchange over peer memory (no counterpart in the reference, which
+  // trains on one GPU): plan -> push (peer stores) -> expert GEMMs -> pull_combine (peer loads).
+  int moe_ep_plan(void* stream, const int32_t* all_counts, int32_t world, int32_t rank, int32_t experts,
+                  int32_t* dst_base, int32_t* group_offsets, int32_t* group_b_index) const {
+    return b200gemm_moe_ep_plan(h_, stream, all_counts, world, rank, experts, dst_base, group_offsets,
+                                group_b_index);
+  }
+  int moe_ep_push(void* stream, const void* x, const uint32_t* selected, const uint32_t* slots,
+                  const int32_t* dst_base, void* const* peer_inbox, int64_t inbox_rows, int32_t world,
+                  int32_t experts, int64_t tokens, int32_t top_k, int64_t d) const {
+    return b200gemm_moe_ep_push(h_, stream, x, selected, slots, dst_base, peer_inbox, inbox_rows, world,
+                                experts, tokens, top_k, d);
+  }
+  int moe_ep_pull_combine(void* stream, void* const* peer_results, const uint32_t* selected,
+                          const uint32_t* slots, const int32_t* dst_base, const float* gates,
+                          const void* residual, int64_t result_rows, int32_t world, int32_t experts,
+                          int64_t tokens, int32_t top_k, int64_t d, void* out, b200gemm_out_t out_type) const {
+    return b200gemm_moe_ep_pull_combine(h_, stream, peer_results, selected, slots, dst_base, gates, residual,
+                                        result_rows, world, experts, tokens, top_k, d, out, out_type);
+  }
   /// Rows offsets[g]..offsets[g+1] of `a` times expert g's matrix, bf16 out, optional SiLU.
   int grouped_gemm(void* stream, const Operand& a, const Operand& b, void* c, int64_t ldc,
                    const int32_t* offsets, int32_t groups, bool silu) const {
     return b200gemm_grouped_gemm(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, c, ldc,
                                  offsets, groups, a.rows, b.rows, a.k, silu ? 1 : 0);
+  }
+
+  /// y = silu(a . W_gate) * (a . W_up) per row group in one launch, `b` holding [gate | up]
+  /// (2 * ff columns); `gate_up` (may be null) receives the bf16 [rows, 2, ff] panel.
+  /// Replaces the fused gate/up GEMM + swiglu_forward_interleaved_packed pair
+  /// (gpu/ops/src/lib.rs:1174-1222).
+  int grouped_gemm_swiglu(void* stream, const Operand& a, const Operand& b, int32_t b_count,
+                          const int32_t* group_b_index, void* y, int64_t ldy, void* gate_up,
+                          int64_t ld_gate_up, const int32_t* offsets, int32_t groups, int64_t ff) const {
+    return b200gemm_grouped_gemm_swiglu(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride,
+                                        b_count, group_b_index, y, ldy, gate_up, ld_gate_up, offsets, groups,
+                                        a.rows, ff, a.k);
   }
 
   /// Output row stride (elements) for the next calls; 0 = dense.  Lets a GEMM

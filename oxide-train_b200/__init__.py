@@ -9,6 +9,6 @@ from .gemm import Tcgen05Gemm
 from .lmhead import FusedLmHead
 from . import moe
 from . import parallel
-from .moe import GroupedExpertFfn
+from .moe import GroupedExpertFfn, GatedExpertFfn
 
-__all__ = ["Tcgen05Gemm", "FusedLmHead", "GroupedExpertFfn", "moe", "parallel", "B200GemmError", "GemmDesc", "_lib"]
+__all__ = ["Tcgen05Gemm", "FusedLmHead", "GroupedExpertFfn", "GatedExpertFfn", "moe", "parallel", "B200GemmError", "GemmDesc", "_lib"]

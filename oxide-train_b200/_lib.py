@@ -81,6 +81,10 @@ SIGNATURES = {
                                                 C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                                 C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int64,
                                                 C.c_int64, C.c_int64, C.c_int32]),
+    "b200gemm_grouped_gemm_swiglu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                               C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
+                                               C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                               C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
     "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                      C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                                      C.c_void_p, C.c_void_p, C.c_void_p]),

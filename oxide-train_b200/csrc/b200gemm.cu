@@ -503,38 +503,53 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
                  const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b, void* c,
                  int64_t ldc, const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
                  int64_t k, int32_t activation, const int32_t* group_b_index = nullptr,
-                 int32_t b_count = 0) {
+                 int32_t b_count = 0, void* panel = nullptr, int64_t ld_panel = 0) {
+  // activation 2 (SwiGLU): B is [gate | up], 2 * n columns; C = silu(gate) * up has n.
+  const bool glu = activation == 2;
+  const int64_t bn = glu ? 2 * n : n;                      // B's extent along N
   if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
   if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
   const int32_t b_mats = group_b_index ? b_count : groups;
-  if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 1)
+  if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 2)
     return fail(B200GEMM_ERR_INVALID, "bad layout or activation");
+  if (panel && !glu) return fail(B200GEMM_ERR_INVALID, "a gate/up panel is written only by the SwiGLU form");
+  if (glu && (n % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "SwiGLU needs ff to be a multiple of 8");
+  if (panel && (n % 64) != 0) return fail(B200GEMM_ERR_SHAPE, "the gate/up panel needs ff to be a multiple of 64");
   if (groups < 1 || groups > kMaxGroups) return fail(B200GEMM_ERR_SHAPE, "groups must be in [1, %d]", kMaxGroups);
   if (total_rows <= 0 || n <= 0 || k <= 0 || total_rows > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30))
     return fail(B200GEMM_ERR_SHAPE, "bad extent");
   const bool b_mn = b_layout == B200GEMM_MN_MAJOR;
   lda = lda ? lda : k;
-  ldb = ldb ? ldb : (b_mn ? n : k);
+  ldb = ldb ? ldb : (b_mn ? bn : k);
   ldc = ldc ? ldc : n;
-  if (lda < k || ldb < (b_mn ? n : k) || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
+  ld_panel = ld_panel ? ld_panel : 2 * n;
+  if (lda < k || ldb < (b_mn ? bn : k) || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
   if ((ldc % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "ldc must be a multiple of 8");
-  const int64_t bsb = batch_stride_b ? batch_stride_b : ldb * (b_mn ? k : n);
+  if (panel && (ld_panel < 2 * n || (ld_panel % 8) != 0))
+    return fail(B200GEMM_ERR_SHAPE, "panel row stride must be at least 2 * ff and a multiple of 8");
+  const int64_t bsb = batch_stride_b ? batch_stride_b : ldb * (b_mn ? k : bn);
   GemmParams params;
   memset(&params, 0, sizeof(params));
   const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   int rc = encode_map(ctx, &params.map_a, bf16, 2, a, k, total_rows, 1, lda, 0, 64, kTileMCta, "A");
   if (rc) return rc;
-  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, n, b_mats, ldb, bsb, 64, kTileN / 2, "B");
-  else rc = encode_map(ctx, &params.map_b, bf16, 2, b, n, k, b_mats, ldb, bsb, 64, 64, "B");
+  if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, bn, b_mats, ldb, bsb, 64, kTileN / 2, "B");
+  else rc = encode_map(ctx, &params.map_b, bf16, 2, b, bn, k, b_mats, ldb, bsb, 64, 64, "B");
   if (rc) return rc;
   rc = encode_map(ctx, &params.map_c, bf16, 2, c, n, total_rows, 1, ldc, 0, 64, 32, "C");
   if (rc) return rc;
+  if (panel) {
+    rc = encode_map(ctx, &params.map_d, bf16, 2, panel, 2 * n, total_rows, 1, ld_panel, 0, 64, 32, "panel");
+    if (rc) return rc;
+    params.d_bf16 = static_cast<uint16_t*>(panel);
+    params.ldd = ld_panel;
+  }
   params.status = ctx->status;
   params.c_bf16 = static_cast<uint16_t*>(c);
   params.ldc = ldc;
   params.m = static_cast<int>(total_rows);
   params.n = static_cast<int>(n);
-  params.tiles_n = ceil_div(n, kTileN);
+  params.tiles_n = ceil_div(n, glu ? kTileN / 2 : kTileN);
   params.tiles_m = 0;
   params.batch = groups;
   params.k_blocks = ceil_div(k, kBlockK);
@@ -544,12 +559,14 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   params.group_offsets = offsets;
   params.group_b_index = group_b_index;
   params.groups = groups;
-  params.act_silu = activation;
+  params.act_silu = activation == 1;
+  params.glu_cols = glu ? static_cast<int>(n) : 0;
   // The tile count depends on the device-side offsets; bound it from above
   // (each group wastes at most one partial tile) and let surplus clusters exit.
   const int units = std::max(1, ctx->sm_count / 2);
   const int64_t max_items = (ceil_div(total_rows, 2 * kTileMCta) + static_cast<int64_t>(groups)) * params.tiles_n;
   const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
+  if (glu) return launch_kernel<2, kEpiBf16GroupedGlu, kSchedGrouped>(ctx, params, grid, stream);
   return launch_kernel<2, kEpiBf16Grouped, kSchedGrouped>(ctx, params, grid, stream);
 }
 
@@ -899,6 +916,19 @@ int b200gemm_grouped_gemm_indexed(b200gemm_handle_t h, void* stream, const void*
   if (!group_b_index) return fail(B200GEMM_ERR_INVALID, "null group index");
   return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, c,
                       ldc, offsets, groups, total_rows, n, k, activation, group_b_index, b_count);
+}
+
+int b200gemm_grouped_gemm_swiglu(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                 const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b,
+                                 int32_t b_count, const int32_t* group_b_index, void* y, int64_t ldy,
+                                 void* gate_up, int64_t ld_gate_up, const int32_t* offsets,
+                                 int32_t groups, int64_t total_rows, int64_t ff, int64_t k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, y,
+                      ldy, offsets, groups, total_rows, ff, k, 2, group_b_index, b_count, gate_up,
+                      ld_gate_up);
 }
 
 int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream, const void* hidden,

@@ -81,7 +81,14 @@ enum EpilogueKind : int {
   kEpiCeForward = 3,    // no C: per-row running (max, sum-exp) and the target's logit
   kEpiCeBackward = 4,   // bf16 C = scale * (exp(acc - lse[row]) - [col == target[row]]), padding = 0
   kEpiBf16Grouped = 5,  // bf16 C for ragged row groups, optional SiLU; rows past the group are not written
+  // Ragged row groups, B = [gate | up] column blocks: C = silu(gate) * up (half as wide as
+  // the product), and optionally the bf16 gate/up panel itself as a second output.
+  kEpiBf16GroupedGlu = 6,
 };
+
+__host__ __device__ constexpr bool epi_is_grouped(int epi) {
+  return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu;
+}
 
 enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2 };
 
@@ -127,6 +134,11 @@ struct GemmParams {
   const int* group_b_index;  // [groups] which B matrix group g multiplies; null = g itself
   int groups;
   int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
+  // ---- kEpiBf16GroupedGlu (the reference's [rows, 2, ff] gate/up panel, gpu/ops/src/lib.rs:1149-1171)
+  int glu_cols;        // ff: B's "up" block starts this many columns after its "gate" block; C is [rows, ff]
+  CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1}
+  uint16_t* d_bf16;    // panel base (null = panel not written)
+  long long ldd;       // panel row stride, elements
 #ifdef B200_PROBE
   long long* probe;
   int probe_skip_loads;   // timing experiment: producers signal "full" without copying anything
@@ -281,8 +293,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     fence_mbar_init();
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
-    if (kEpi == kEpiF32Tma || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || kEpi == kEpiBf16Grouped)
+    if (kEpi == kEpiF32Tma || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || epi_is_grouped(kEpi))
       prefetch_tensormap(&p.map_c);
+    if (kEpi == kEpiBf16GroupedGlu) prefetch_tensormap(&p.map_d);
   }
   if constexpr (kSched == kSchedGrouped) {
     // Every CTA derives the same tile table from the offsets array.
@@ -326,7 +339,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       Tile t;
       for (; ok && walk.get(t); walk.next(t)) {
         const int m0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta;
-        const int n0 = t.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
+        // kEpiBf16GroupedGlu (CTA pairs only): the leader loads 128 "gate" columns of B, its
+        // peer the 128 "up" columns glu_cols further on, so the accumulator holds gate in
+        // columns 0-127 and the matching up values in columns 128-255.
+        const int n0 = kEpi == kEpiBf16GroupedGlu
+                           ? t.tile_n * (kTileN / 2) + static_cast<int>(cta_rank) * p.glu_cols
+                           : t.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
         const int a_batch = kSched == kSchedGrouped ? 0 : t.batch;   // grouped A is one [rows, K] matrix
         for (int kb = t.kb_begin; kb < t.kb_begin + t.kb_count; ++kb, ++g) {
           if ((g & 1u) != which) continue;
@@ -448,7 +466,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       PROBE_ADD(5);
       tcgen05_fence_after_sync();
       const int row0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta + lane_base;   // warp's first row
-      const int col0 = t.tile_n * kTileN;
+      const int col0 = t.tile_n * (kEpi == kEpiBf16GroupedGlu ? kTileN / 2 : kTileN);
       const uint32_t t_acc = tmem_base + (lane_base << 16) + acc * kTileN;
 
       auto release_accumulator = [&]() {
@@ -497,8 +515,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           PROBE_ADD(9);
           ++chunk_counter;
         }
-      } else if constexpr (kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || kEpi == kEpiBf16Grouped) {
-        constexpr int kChunks = kTileN / 64;
+      } else if constexpr (kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || epi_is_grouped(kEpi)) {
+        constexpr bool kGlu = kEpi == kEpiBf16GroupedGlu;
+        constexpr int kChunks = (kGlu ? kTileN / 2 : kTileN) / 64;
         const int row = row0 + lane;
         // kEpiCeBackward: p = exp(logit - lse) computed as exp2(logit*log2e - lse*log2e).
         float neg_lse2 = 0.f;
@@ -512,10 +531,76 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         // kEpiBf16Grouped: a warp whose 32 rows all belong to the group uses the
         // TMA store; a warp that straddles the group's end writes row by row.
         bool warp_inside = true;
-        if constexpr (kEpi == kEpiBf16Grouped) warp_inside = row0 + 32 <= t.m_end;
+        if constexpr (epi_is_grouped(kEpi)) warp_inside = row0 + 32 <= t.m_end;
+        // Stage 32 rows x 64 bf16 columns and send them through `map` to (col, row0), or,
+        // for a warp that straddles the end of its group, write this thread's row directly.
+        auto put_chunk = [&](const CUtensorMap* map, uint16_t* base_ptr, long long ld, int col, int col_end,
+                             const uint32_t* packed) {
+          if (warp_inside) {
+            const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+            if (lane == 0) tma_wait_group_read<1>();
+            __syncwarp();
+            stage_row(buf, packed);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(map, buf, col, row0, kSched == kSchedGrouped ? 0 : t.batch);
+              tma_commit_group();
+            }
+            ++chunk_counter;
+          } else if (row < t.m_end) {
+            uint16_t* crow = base_ptr + static_cast<long long>(row) * ld;
+            if (col + 64 <= col_end) {
+              uint4* ptr = reinterpret_cast<uint4*>(crow + col);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                ptr[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            } else {
+              for (int j = 0; j < 64 && col + j < col_end; ++j)
+                crow[col + j] = static_cast<uint16_t>((packed[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
+            }
+          }
+        };
 #pragma unroll 1
         for (int c = 0; c < kChunks; ++c) {
           uint32_t packed[32];
+          if constexpr (kGlu) {
+            // gate in accumulator columns [c*64, +64), up 128 columns further on
+            uint32_t pg[32], pu[32];
+            const bool panel = p.d_bf16 != nullptr;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t g[32], u[32];
+              tmem_ld_32x32(t_acc + c * 64 + h * 32, g);
+              tmem_ld_32x32(t_acc + kTileN / 2 + c * 64 + h * 32, u);
+              tmem_ld_wait();
+              if (panel) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  pg[h * 16 + j] = pack_bf16x2(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
+                  pu[h * 16 + j] = pack_bf16x2(__uint_as_float(u[2 * j]), __uint_as_float(u[2 * j + 1]));
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                // silu(g) * u with silu(g) = hg + hg * tanh(hg), hg = g / 2
+                const float hg = 0.5f * __uint_as_float(g[j]);
+                g[j] = __float_as_uint(fmaf(hg, fast_tanh(hg), hg) * __uint_as_float(u[j]));
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                packed[h * 16 + j] = pack_bf16x2(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
+            }
+            if (c == kChunks - 1) release_accumulator();
+            const int col = col0 + c * 64;
+            put_chunk(&p.map_c, p.c_bf16, p.ldc, col, p.n, packed);
+            // The panel's gate block ends where its up block starts, so a chunk of gate
+            // columns must not run past it (the host requires ff % 64 == 0 with a panel).
+            if (panel && col < p.glu_cols) {
+              put_chunk(&p.map_d, p.d_bf16, p.ldd, col, p.glu_cols, pg);
+              put_chunk(&p.map_d, p.d_bf16, p.ldd, p.glu_cols + col, 2 * p.glu_cols, pu);
+            }
+          } else {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t r[32];
@@ -560,30 +645,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               packed[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           }
           if (c == kChunks - 1) release_accumulator();
-          if (warp_inside) {
-            const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
-            if (lane == 0) tma_wait_group_read<1>();
-            __syncwarp();
-            stage_row(buf, packed);
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&p.map_c, buf, col0 + c * 64, row0, kSched == kSchedGrouped ? 0 : t.batch);
-              tma_commit_group();
-            }
-            ++chunk_counter;
-          } else if (row < t.m_end) {
-            uint16_t* crow = p.c_bf16 + static_cast<long long>(row) * p.ldc;
-            const int col = col0 + c * 64;
-            if (col + 64 <= p.n) {
-              uint4* ptr = reinterpret_cast<uint4*>(crow + col);
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                ptr[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            } else {
-              for (int j = 0; j < 64 && col + j < p.n; ++j)
-                crow[col + j] = static_cast<uint16_t>((packed[j >> 1] >> ((j & 1) * 16)) & 0xffffu);
-            }
+          put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
           }
         }
       } else if constexpr (kEpi == kEpiCeForward) {

@@ -95,6 +95,58 @@ def grouped_gemm(gemm: Tcgen05Gemm, a, b, offsets, out=None, transposed_b: bool 
     return out
 
 
+def grouped_gemm_swiglu(gemm: Tcgen05Gemm, a, w_gate_up, offsets, out=None, gate_up=None,
+                        want_gate_up: bool = False, group_b_index=None):
+    """``silu(a . W_gate) * (a . W_up)`` per row group in one launch.
+
+    ``w_gate_up`` is ``[matrices, k, 2, ff]`` (the reference's fused gate/up weight,
+    read in place).  Returns ``y [rows, ff]`` and, with ``want_gate_up`` (or a
+    ``gate_up`` buffer), the bf16 ``[rows, 2, ff]`` panel the activation's backward reads.
+    ``group_b_index`` (int32 ``[groups]``) picks the matrix of each group; without it
+    group ``g`` uses matrix ``g``."""
+    rows, k = a.shape
+    mats, kw, two, ff = w_gate_up.shape
+    if two != 2 or kw != k:
+        raise ValueError("w_gate_up must be [matrices, k, 2, ff] with a's reduction extent")
+    if not w_gate_up.is_contiguous():
+        raise ValueError("w_gate_up must be contiguous")
+    groups = offsets.numel() - 1
+    if offsets.dtype != torch.int32:
+        raise TypeError("offsets must be int32 on the device")
+    if group_b_index is None and groups != mats:
+        raise ValueError("one group per matrix unless group_b_index is given")
+    if out is None:
+        out = torch.empty((rows, ff), dtype=torch.bfloat16, device=a.device)
+    if gate_up is None and want_gate_up:
+        gate_up = torch.empty((rows, 2, ff), dtype=torch.bfloat16, device=a.device)
+    L.check(gemm._lib.b200gemm_grouped_gemm_swiglu(
+        gemm._h, _stream_ptr(), a.data_ptr(), a.stride(0), w_gate_up.data_ptr(), L.MN_MAJOR,
+        w_gate_up.stride(1), w_gate_up.stride(0), mats,
+        None if group_b_index is None else group_b_index.data_ptr(), out.data_ptr(), out.stride(0),
+        None if gate_up is None else gate_up.data_ptr(), 0 if gate_up is None else gate_up.stride(0),
+        offsets.data_ptr(), groups, rows, ff, k))
+    return (out, gate_up) if gate_up is not None else out
+
+
+class GatedExpertFfn:
+    """``y = down(silu(gate(x)) * up(x))`` per expert over routed rows -- the reference's
+    own expert (crates/nn/src/moe.rs:76-90: SwiGLU over a fused gate/up projection).
+
+    ``w_gate_up`` is ``[experts, d, 2, ff]``, ``w_down`` ``[experts, ff, d]``."""
+
+    def __init__(self, gemm: Tcgen05Gemm, w_gate_up, w_down):
+        self.gemm, self.w_gate_up, self.w_down = gemm, w_gate_up, w_down
+
+    def forward(self, x, scores, top_k: int, scores_are_logits: bool = False, residual=None,
+                out_dtype=torch.float32, keep_gate_up: bool = False):
+        r = route(self.gemm, scores, top_k, scores_are_logits=scores_are_logits)
+        xp = scatter(self.gemm, x, r)
+        res = grouped_gemm_swiglu(self.gemm, xp, self.w_gate_up, r.offsets, want_gate_up=keep_gate_up)
+        hidden, self.gate_up = res if keep_gate_up else (res, None)
+        yp = grouped_gemm(self.gemm, hidden, self.w_down, r.offsets, transposed_b=True)
+        return combine(self.gemm, yp, r, residual, out_dtype), r
+
+
 class GroupedExpertFfn:
     """``y = down(silu(up(x)))`` per expert over routed rows (BASELINE MoE config).
 

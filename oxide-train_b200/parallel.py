@@ -179,6 +179,31 @@ def _world(group):
     return dist.get_world_size(group), dist.get_rank(group)
 
 
+class _ReservedSms:
+    """``with _ReservedSms(ops, n):`` -- GEMMs launched inside spread over all but ``n`` SMs.
+
+    A persistent GEMM CTA takes all of an SM's shared memory, so a collective's kernel that
+    becomes ready while a GEMM runs waits for whole GEMM CTAs to finish -- and a GEMM that
+    starts while the collective holds some SMs runs part of its statically scheduled
+    clusters as a second wave.  Keeping ``n`` SMs out of the GEMM grid (the collective is
+    given a channel limit to match) lets both run side by side."""
+
+    def __init__(self, ops, sms: int):
+        self.gemm = getattr(ops, "gemm", None) if sms else None
+        self.sms = sms
+
+    def __enter__(self):
+        if self.gemm is not None:
+            total = torch.cuda.get_device_properties(self.gemm.device).multi_processor_count
+            self.gemm.set_sm_limit(max(2, total - self.sms))
+        return self
+
+    def __exit__(self, *exc):
+        if self.gemm is not None:
+            self.gemm.set_sm_limit(0)
+        return False
+
+
 # --------------------------------------------------------------------------- vocabulary-parallel head
 
 def vocab_shards(vocab_padded: int, world: int, tile: int = TILE_N):
@@ -211,8 +236,9 @@ def merge_softmax_stats(row_max, row_sum, row_target_logit, group=None):
 
 class VocabParallelHead:
     def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out",
-                 reduce_dtype=torch.bfloat16):
+                 reduce_dtype=torch.bfloat16, reserve_sms: int = 0):
         self.ops, self.group, self.w_layout, self.reduce_dtype = ops, group, w_layout, reduce_dtype
+        self.reserve_sms = reserve_sms      # SMs the weight-gradient GEMM leaves to d_hidden's all-reduce
         self.world, self.rank = _world(group)
         self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
@@ -255,7 +281,8 @@ class VocabParallelHead:
         with torch.cuda.stream(self._side):
             dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
         dh.record_stream(self._side)
-        dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
+        with _ReservedSms(self.ops, self.reserve_sms):
+            dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
         torch.cuda.current_stream().wait_stream(self._side)
         if dh.dtype != torch.float32:
             dh = self.ops.widen(dh)
@@ -359,19 +386,10 @@ class ExpertParallelMoe:
                          "token": torch.zeros(1, device=x.device)}
         dv = self._dev
         out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
-        # The expert GEMMs leave a few SMs free: a persistent GEMM CTA takes all of an SM's
-        # shared memory, and the one-element all-reduces used as barriers (and the other
-        # slice's small kernels) would otherwise wait for a whole GEMM to drain.
-        if hasattr(self.ops, "gemm") and self.reserve_sms:
-            self.ops.gemm.set_sm_limit(self._sm_total(x.device) - self.reserve_sms)
-        try:
+        # The expert GEMMs leave a few SMs to the one-element all-reduces used as barriers
+        # and to the other slice's small kernels.
+        with _ReservedSms(self.ops, self.reserve_sms):
             return self._forward_device_body(x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out)
-        finally:
-            if hasattr(self.ops, "gemm") and self.reserve_sms:
-                self.ops.gemm.set_sm_limit(0)
-
-    def _sm_total(self, device):
-        return torch.cuda.get_device_properties(device).multi_processor_count
 
     def _forward_device_body(self, x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out):
         n = x.shape[0]
@@ -640,8 +658,9 @@ class TensorParallelMlp:
     ``[c * m/chunks + r * m/(chunks*world), ...)`` of every piece ``c``."""
 
     def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks: int = 4,
-                 partial_dtype=torch.bfloat16):
+                 partial_dtype=torch.bfloat16, reserve_sms: int = 0):
         self.ops, self.group, self.chunks = ops, group, chunks
+        self.reserve_sms = reserve_sms      # SMs every GEMM leaves to the collectives on the side stream
         self.world, self.rank = _world(group)
         self.w_up, self.w_down = w_up_shard, w_down_shard
         self.partial_dtype = partial_dtype
@@ -663,6 +682,22 @@ class TensorParallelMlp:
         return torch.cat(idx)
 
     def forward(self, x):
+        with _ReservedSms(self.ops, self.reserve_sms if self.world > 1 else 0):
+            return self._forward(x)
+
+    def backward(self, x, dy_local, dw_up, dw_down):
+        """``dy_local`` is this rank's rows of dL/dy (layout of ``forward``'s output).
+
+        Accumulates the weight-gradient shards (fp32) and returns this rank's rows
+        of ``dx`` (same row ownership as ``forward``'s output) after a
+        reduce-scatter -- the mirror image of the all-gather that hands the MLP its
+        replicated ``x``.  Piece by piece: the all-gather of the next piece's ``dy``
+        and the reduce-scatter of the previous piece's ``dx`` run on a side stream
+        underneath the current piece's four GEMMs."""
+        with _ReservedSms(self.ops, self.reserve_sms if self.world > 1 else 0):
+            return self._backward(x, dy_local, dw_up, dw_down)
+
+    def _forward(self, x):
         m, d = x.shape[0], self.w_down.shape[1]
         if m % (self.chunks * self.world):
             raise ValueError("rows must divide by chunks * world")
@@ -689,15 +724,7 @@ class TensorParallelMlp:
             torch.cuda.current_stream().wait_stream(side)
         return out
 
-    def backward(self, x, dy_local, dw_up, dw_down):
-        """``dy_local`` is this rank's rows of dL/dy (layout of ``forward``'s output).
-
-        Accumulates the weight-gradient shards (fp32) and returns this rank's rows
-        of ``dx`` (same row ownership as ``forward``'s output) after a
-        reduce-scatter -- the mirror image of the all-gather that hands the MLP its
-        replicated ``x``.  Piece by piece: the all-gather of the next piece's ``dy``
-        and the reduce-scatter of the previous piece's ``dx`` run on a side stream
-        underneath the current piece's four GEMMs."""
+    def _backward(self, x, dy_local, dw_up, dw_down):
         m = x.shape[0]
         piece, share = m // self.chunks, m // (self.chunks * self.world)
         dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)

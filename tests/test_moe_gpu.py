@@ -114,6 +114,65 @@ def test_grouped_gemm_ragged_groups(pkg, oracle, gemm, transposed_b, silu):
         assert_gemm_close(got[lo:hi], ref, f"group {g}", rel_fro=4e-3, elem=8e-3)
 
 
+@pytest.mark.parametrize("ff,want_panel", [(768, True), (192, True), (320, True), (200, False)])
+def test_grouped_gemm_swiglu_matches_oracle(pkg, oracle, gemm, ff, want_panel):
+    """silu(x W_gate) * (x W_up) over ragged groups in one launch, and the bf16 [rows, 2, ff]
+    panel beside it (crates/nn/src/swiglu.rs:22-28 over the fused gate/up projection,
+    crates/nn/src/moe.rs:76-90).  ff = 192, 320 and 200 leave a partly filled column tile."""
+    import torch
+    sizes = [300, 0, 17, 256, 1, 513, 128, 31]
+    offsets = _ragged_offsets(sizes)
+    rows, k, G = int(offsets[-1]), 192, len(sizes)
+    a, av = bf16_operand(oracle, (rows, k), 45)
+    w, wv = bf16_operand(oracle, (G, k, 2, ff), 46, std=0.1)
+    y = torch.full((rows + 8, ff), 9.0, dtype=torch.bfloat16, device="cuda")
+    panel = torch.full((rows + 8, 2, ff), 7.0, dtype=torch.bfloat16, device="cuda") if want_panel else None
+    pkg.moe.grouped_gemm_swiglu(gemm, a, w, torch.from_numpy(offsets).cuda(), out=y[:rows],
+                                gate_up=None if panel is None else panel[:rows])
+    assert gemm.device_status() == 0
+    got = from_dev_bf16(y)
+    assert np.all(got[rows:] == 9.0)
+    if want_panel:
+        got_panel = from_dev_bf16(panel)
+        assert np.all(got_panel[rows:] == 7.0)
+    for g in range(G):
+        lo, hi = offsets[g], offsets[g + 1]
+        if lo == hi:
+            continue
+        gate = oracle.matmul(av[lo:hi], np.ascontiguousarray(wv[g, :, 0, :]), THREADS)
+        up = oracle.matmul(av[lo:hi], np.ascontiguousarray(wv[g, :, 1, :]), THREADS)
+        assert_gemm_close(got[lo:hi], oracle.swiglu(gate, up), f"group {g}", rel_fro=4e-3, elem=8e-3)
+        if want_panel:
+            assert_gemm_close(got_panel[lo:hi, 0], gate, f"gate {g}", rel_fro=4e-3, elem=8e-3)
+            assert_gemm_close(got_panel[lo:hi, 1], up, f"up {g}", rel_fro=4e-3, elem=8e-3)
+
+
+def test_grouped_gemm_swiglu_dense_and_indexed(pkg, oracle, gemm):
+    """One group is the dense gated MLP; an index maps several groups onto one matrix."""
+    import torch
+    rows, k, ff = 700, 128, 256
+    a, av = bf16_operand(oracle, (rows, k), 47)
+    w, wv = bf16_operand(oracle, (2, k, 2, ff), 48, std=0.1)
+    offsets = torch.tensor([0, rows], dtype=torch.int32, device="cuda")
+    y = pkg.moe.grouped_gemm_swiglu(gemm, a, w[:1], offsets)
+    ref0 = oracle.swiglu(oracle.matmul(av, np.ascontiguousarray(wv[0, :, 0, :]), THREADS),
+                         oracle.matmul(av, np.ascontiguousarray(wv[0, :, 1, :]), THREADS))
+    assert_gemm_close(from_dev_bf16(y), ref0, "dense", rel_fro=4e-3, elem=8e-3)
+    # three groups: matrices 1, 0, 1
+    offs = torch.tensor([0, 300, 301, rows], dtype=torch.int32, device="cuda")
+    index = torch.tensor([1, 0, 1], dtype=torch.int32, device="cuda")
+    y2 = from_dev_bf16(pkg.moe.grouped_gemm_swiglu(gemm, a, w, offs, group_b_index=index))
+    ref1 = oracle.swiglu(oracle.matmul(av, np.ascontiguousarray(wv[1, :, 0, :]), THREADS),
+                         oracle.matmul(av, np.ascontiguousarray(wv[1, :, 1, :]), THREADS))
+    assert_gemm_close(y2[:300], ref1[:300], "group 0", rel_fro=4e-3, elem=8e-3)
+    assert_gemm_close(y2[300:301], ref0[300:301], "group 1", rel_fro=4e-3, elem=8e-3)
+    assert_gemm_close(y2[301:], ref1[301:], "group 2", rel_fro=4e-3, elem=8e-3)
+    assert gemm.device_status() == 0
+    with pytest.raises(pkg.B200GemmError):                      # a panel needs ff % 64 == 0
+        w200, _ = bf16_operand(oracle, (1, k, 2, 200), 49)
+        pkg.moe.grouped_gemm_swiglu(gemm, a, w200, offsets, want_gate_up=True)
+
+
 def test_grouped_gemm_leaves_rows_outside_groups_untouched(pkg, oracle, gemm):
     import torch
     offsets = np.array([0, 100, 100, 260], np.int32)       # total 260 of 400 rows are routed

@@ -53,7 +53,8 @@ def _worker(rank, port, failures):
         _, dh2, dw2 = head.backward(h, ws, t, lse2)
         # partial sums cross the link as bf16: the GEMM contract's relative Frobenius bound
         assert float((dh1 - dh2).norm() / dh1.norm()) < 1e-2
-        head32 = par.VocabParallelHead(ops, classes, v, reduce_dtype=torch.float32)
+        # (the weight-gradient GEMM leaves 16 SMs to the all-reduce in this variant)
+        head32 = par.VocabParallelHead(ops, classes, v, reduce_dtype=torch.float32, reserve_sms=16)
         _, dh3, _ = head32.backward(h, ws, t, lse2)
         assert torch.allclose(dh1, dh3, atol=2e-5, rtol=2e-2), float((dh1 - dh3).abs().max())
         assert torch.allclose(dw1[:, head.c0:head.c1], dw2, atol=2e-5, rtol=2e-2)
@@ -96,7 +97,7 @@ def _worker(rank, port, failures):
         w2 = (torch.randn((ff, d), generator=gen, device=dev) * 0.05).to(bf)
         cols = slice(rank * ff // WORLD, (rank + 1) * ff // WORLD)
         mlp = par.TensorParallelMlp(ops, w1[:, cols].contiguous(), w2[cols].contiguous(), chunks=2,
-                                    partial_dtype=torch.float32)
+                                    partial_dtype=torch.float32, reserve_sms=8)
         y = mlp.forward(x2)
         hid = ops.linear(x2, w1)                               # bf16 hidden, as each shard rounds it
         full = hid.float() @ w2.float()
