@@ -308,6 +308,7 @@ def run_sharded(args):
     pkg = entry.load_package()
     par = pkg.parallel
     gemm = pkg.Tcgen05Gemm(local)
+    gemm.set_scheduler(args.scheduler == "dynamic")
     ops = par.DeviceOps(gemm)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1)                                    # replicated operands: same seed on every rank
@@ -318,7 +319,12 @@ def run_sharded(args):
 
     if args.workload == "lmhead":
         m, k, v, classes = M_TOKENS, D_MODEL, VOCAB_PAD, VOCAB
-        head = par.VocabParallelHead(ops, classes, v)
+        # Several GPUs: the weight-gradient GEMM leaves 16-32 SMs to d_hidden's all-reduce, which
+        # runs in a group limited to as many thread blocks, so the two overlap.
+        # (the all-reduce takes about the same time whatever N is while the GEMM shrinks with N)
+        reserve = 0 if world == 1 else (32 if world >= 8 else 16)
+        head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve,
+                                     group=par.nccl_group_with_cta_limit(reserve) if reserve else None)
         hidden = rnd((m, k), 1.0)
         w_shard = rnd((k, head.c1 - head.c0), 0.02)
         targets = torch.randint(0, classes, (m,), generator=gen, device=dev, dtype=torch.int32)
@@ -334,7 +340,8 @@ def run_sharded(args):
         flops = 3 * 2.0 * m * k * v
         name = ("fused lm-head + softmax cross-entropy (BASELINE configs[2]): M=32768 K=1536 V=50432 "
                 "(50257 classes), forward + backward; the backward's logit recompute is not credited")
-        par_text = f"vocabulary split over {world} GPU(s); all-reduce of row max / sum-exp and of d_hidden"
+        par_text = (f"vocabulary split over {world} GPU(s); all-reduce of row max / sum-exp and of d_hidden "
+                    f"(the latter under the weight-gradient GEMM, {reserve} SMs reserved for it)")
         host_in = (hidden, None)
     elif args.workload == "moe":
         # 32768 tokens PER GPU (weak scaling): expert parallelism serves data-parallel
@@ -357,21 +364,20 @@ def run_sharded(args):
         logits = (torch.randn((n_local, experts), generator=grank, device=dev) + bias).contiguous()
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
-        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=2, use_peer_copies=True)
+        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=2, exchange="device")
         result = {}
 
         def step():
             result["out"] = ep.forward(x, logits, scores_are_logits=True)
             return 9
 
-        extra_fn = lambda: {"rows_received_this_rank": ep.last.get("rows_received"),
-                            "rows_sent_this_rank": ep.last.get("rows_sent")}
 
         flops = 2.0 * n_tok * top_k * d * ff * 2
         name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens per GPU, D=1536, E=64, top-8, "
                 "expert FF=768, up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
-        par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch and combine by copy-engine "
-                    "pushes into peer memory (symmetric memory), NCCL for counts and barriers")
+        par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch by peer stores and combine by "
+                    "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
+                    "counts and the two barriers; two token slices on two streams")
         host_in = (x, None)
     else:
         m, d, ff = 65536, 4096, 16384
@@ -462,7 +468,7 @@ def run_sharded(args):
                      "algorithmic_flops_per_step": flops},
     }
     if args.workload == "moe":
-        recv = torch.tensor([float(ep.last.get("rows_received", 0))], device=dev)
+        recv = torch.tensor([float(ep.rows_received())], device=dev)
         allr = [torch.zeros_like(recv) for _ in range(world)]
         dist.all_gather(allr, recv)
         rows = [float(t.item()) for t in allr]
@@ -484,6 +490,7 @@ def run_only(args):
     dev = torch.device("cuda", 0)
     pkg = entry.load_package()
     gemm = pkg.Tcgen05Gemm(0)
+    gemm.set_scheduler(args.scheduler == "dynamic")
     name, kind = args.only.split(".")
     bf, f32 = torch.bfloat16, torch.float32
     if name == "lm_head" and kind.startswith("fused"):
@@ -628,6 +635,7 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
     pkg = entry.load_package()
     gemm = pkg.Tcgen05Gemm(local)
+    gemm.set_scheduler(args.scheduler == "dynamic")
     head = pkg.FusedLmHead(gemm, VOCAB, "in_out")
     buf = StepBuffers(torch, device, seed=rank)
 
@@ -730,6 +738,8 @@ def main():
                          "lm_head.fused_backward, moe.forward, moe.gated_forward, "
                          "mlp_gate_up.{swiglu,swiglu_no_panel,plain_gemm_only,unfused}")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
+    ap.add_argument("--scheduler", default="dynamic", choices=["static", "dynamic"],
+                    help="how the persistent kernels hand out tiles (see b200gemm_set_scheduler)")
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
                     help="dense_step (default) is the headline; the others are the sharded configurations")
     args = ap.parse_args()

@@ -106,6 +106,20 @@ B200GEMM_API int b200gemm_destroy(b200gemm_handle_t h);
  * same time, since a persistent grid would otherwise hold every SM until it ends. */
 B200GEMM_API int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms);
 
+/* How the persistent kernels of later launches hand out their tiles.
+ *   0  static: cluster c takes items c, c + clusters, ...  (the reference's walk,
+ *      gpu/gemm/src/optimized.rs:776-802)
+ *   1  dynamic (the default for 2-CTA launches): every cluster takes its next item from a
+ *      counter in device memory.  Same items, same order of hand-out; but a cluster that
+ *      runs slower or becomes resident late -- another kernel, e.g. a collective's, held
+ *      its SMs -- simply takes fewer items instead of running a fixed share as a second
+ *      wave.  Uses 8 bytes of device memory per stream, allocated (cudaMalloc) at the first
+ *      launch on that stream: make that launch outside a stream capture, or choose 0.
+ * Results are the same either way except where a launch reduce-adds split-K slices, whose
+ * order of arrival in memory is not fixed in either mode.
+ * b200gemm_lmhead_ce_forward_noalloc always uses the static walk. */
+B200GEMM_API int b200gemm_set_scheduler(b200gemm_handle_t h, int32_t mode);
+
 /* The tcgen05 GEMM (host.rs:616-1098, kernels gpu/gemm/src/optimized.rs:1138-1268). */
 B200GEMM_API int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
 

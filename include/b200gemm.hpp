@@ -186,6 +186,10 @@ class Tcgen05Gemm {
   void set_ldc(int64_t ldc, int64_t batch_stride_c = 0) { ldc_ = ldc; bsc_ = batch_stride_c; }
   /// 0 = let the library choose, 1 = never split, n = n slices (fp32 output only).
   void set_split_k(int split_k) { split_k_ = split_k; }
+  /// Persistent kernels on at most `sms` SMs (0 = all): room for a collective's kernels.
+  int set_sm_limit(int sms) const { return b200gemm_set_sm_limit(h_, sms); }
+  /// Tiles from a device-side counter (true, the default) or the fixed round-robin walk.
+  int set_scheduler(bool dynamic) const { return b200gemm_set_scheduler(h_, dynamic ? 1 : 0); }
 
  private:
   int run(void* stream, const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,

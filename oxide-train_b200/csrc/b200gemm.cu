@@ -73,6 +73,12 @@ struct b200gemm_context {
     size_t bytes = 0;
   };
   std::map<cudaStream_t, Scratch> moe_scratch;
+  // Dynamic tile scheduling (b200gemm_set_scheduler): two int32 counters per stream, zero
+  // between launches.  Launches on one stream run one after another and so can share a
+  // pair; launches on different streams may overlap and must not.
+  int scheduler = 1;         // 0 = static round-robin, 1 = dynamic (the default)
+  std::map<cudaStream_t, int*> sched_counters;
+  std::mutex sched_mu;       // guards sched_counters only: taken inside launches that may hold `mu`
   std::mutex mu;
 };
 
@@ -209,9 +215,34 @@ int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
   return B200GEMM_OK;
 }
 
+// GemmParams::sched_counter value a caller sets to keep a launch on the static schedule
+// whatever the handle's mode is (the entry point that must not allocate).
+int* const kStaticScheduleOnly = reinterpret_cast<int*>(1);
+
+// The stream's counter pair, created on first use (null: static schedule).
+int sched_counters_for(b200gemm_context* ctx, cudaStream_t stream, int** out) {
+  std::lock_guard<std::mutex> lock(ctx->sched_mu);
+  auto it = ctx->sched_counters.find(stream);
+  if (it == ctx->sched_counters.end()) {
+    int* ptr = nullptr;
+    CUDA_TRY(cudaMalloc(&ptr, 2 * sizeof(int)));
+    CUDA_TRY(cudaMemset(ptr, 0, 2 * sizeof(int)));
+    it = ctx->sched_counters.emplace(stream, ptr).first;
+  }
+  *out = it->second;
+  return B200GEMM_OK;
+}
+
 template <int CG, int EPI, int SCHED>
-int launch_kernel(b200gemm_context* ctx, const GemmParams& params, int grid, cudaStream_t stream) {
+int launch_kernel(b200gemm_context* ctx, const GemmParams& params_in, int grid, cudaStream_t stream) {
   auto kernel = gemm_tcgen05_kernel<CG, EPI, SCHED>;
+  GemmParams params = params_in;
+  const bool static_only = params.sched_counter == kStaticScheduleOnly;
+  params.sched_counter = nullptr;
+  if (CG == 2 && ctx->scheduler == 1 && !static_only) {
+    int rc = sched_counters_for(ctx, stream, &params.sched_counter);
+    if (rc) return rc;
+  }
   // Per-device opt-in to > 48 KiB dynamic shared memory, once per kernel
   // (the reference's opt_in_dynamic_smem, host.rs:485-505).
   bool& ready = ctx->smem_opt_in[CG - 1][EPI];
@@ -370,7 +401,7 @@ struct CeShardOut {
 int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, const void* weight,
                int32_t w_layout, const int32_t* targets, int64_t m, int64_t k, int64_t v,
                int64_t classes, float* lse, float* row_loss, float* loss, void* workspace,
-               size_t workspace_bytes, const CeShardOut* shard = nullptr) {
+               size_t workspace_bytes, const CeShardOut* shard = nullptr, bool may_allocate = true) {
   int rc = ce_check(hidden, weight, w_layout, targets, m, k, v, classes);
   if (rc) return rc;
   if (!shard && !lse) return fail(B200GEMM_ERR_INVALID, "lse output is required");
@@ -417,6 +448,7 @@ int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, c
   CUDA_TRY(cudaMemsetAsync(ws.accum, 0, sizeof(CeAccum), stream));
   // A row whose target lies in another shard gets no target logit from this one.
   if (shard) CUDA_TRY(cudaMemsetAsync(ws.target_logit, 0, static_cast<size_t>(m) * sizeof(float), stream));
+  if (!may_allocate) params.sched_counter = kStaticScheduleOnly;
   rc = launch_kernel<2, kEpiCeForward, kSchedCeForward>(ctx, params, grid, stream);
   if (rc) return rc;
   const int blocks = static_cast<int>(std::min<int64_t>((m + 255) / 256, ctx->sm_count * 4));
@@ -643,6 +675,14 @@ int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms) {
   return B200GEMM_OK;
 }
 
+int b200gemm_set_scheduler(b200gemm_handle_t h, int32_t mode) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (mode < 0 || mode > 1) return fail(B200GEMM_ERR_INVALID, "scheduler mode must be 0 (static) or 1 (dynamic)");
+  h->scheduler = mode;
+  return B200GEMM_OK;
+}
+
 #ifdef B200_PROBE
 __attribute__((visibility("default"))) void b200gemm_set_probe(long long* device_buffer) {
   g_probe = device_buffer;
@@ -698,6 +738,8 @@ int b200gemm_destroy(b200gemm_handle_t h) {
     if (p) cudaFree(p);
   for (auto& kv : h->moe_scratch)
     if (kv.second.ptr) cudaFree(kv.second.ptr);
+  for (auto& kv : h->sched_counters)
+    if (kv.second) cudaFree(kv.second);
   if (h->status) cudaFree(h->status);
   delete h;
   return B200GEMM_OK;
@@ -948,7 +990,7 @@ int b200gemm_lmhead_ce_forward_noalloc(b200gemm_handle_t h, void* stream, const 
   rc = ce_static_scratch(h->device, &scratch);
   if (rc) return rc;
   return ce_forward(h, static_cast<cudaStream_t>(stream), hidden, weight, w_layout, targets, m, k, v,
-                    classes, lse, row_loss, loss, scratch, kCeStaticBytes);
+                    classes, lse, row_loss, loss, scratch, kCeStaticBytes, nullptr, /*may_allocate=*/false);
 }
 
 int b200gemm_moe_ep_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts, int32_t world,
@@ -1080,6 +1122,11 @@ int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_co
   if (device_code) *device_code = code;
   if (code != 0) {
     CUDA_TRY(cudaMemsetAsync(h->status, 0, sizeof(int), s));
+    {
+      // A launch that gave up may have left its tile counters mid-count.
+      std::lock_guard<std::mutex> lock(h->sched_mu);
+      for (auto& kv : h->sched_counters) CUDA_TRY(cudaMemsetAsync(kv.second, 0, 2 * sizeof(int), s));
+    }
     return fail(B200GEMM_ERR_DEVICE, "a kernel gave up waiting (device status %d)", code);
   }
   return B200GEMM_OK;

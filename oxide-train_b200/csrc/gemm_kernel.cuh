@@ -139,11 +139,16 @@ struct GemmParams {
   CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1}
   uint16_t* d_bf16;    // panel base (null = panel not written)
   long long ldd;       // panel row stride, elements
+  // ---- dynamic tile scheduling (CTA pairs): [0] next work item, [1] clusters that have
+  // finished fetching; both are zero between launches.  Null = static round-robin.
+  int* sched_counter;
 #ifdef B200_PROBE
   long long* probe;
   int probe_skip_loads;   // timing experiment: producers signal "full" without copying anything
 #endif
 };
+
+constexpr int kSchedRing = 16;   // items in flight per cluster are far fewer (stages + accumulators + 2)
 
 struct Tile {
   int batch;       // index into the batch / expert dimension of B (and of A, C when dense)
@@ -161,9 +166,40 @@ struct TileWalk {
   const GemmParams& p;
   const int* group_tile_start;   // shared memory, kSchedGrouped: [groups + 1] first m-tile of each group
   int item, inner, step;
+  // Dynamic scheduling: the cluster's items arrive through a ring in shared memory,
+  // one 64-bit word (sequence number + 1, item or -1) per item, written by the
+  // scheduler warp; every role polls the same sequence, so they still agree.
+  const volatile unsigned long long* ring;   // null = static round-robin
+  uint32_t seq;
+  volatile int* abort_flag;
 
-  __device__ TileWalk(const GemmParams& p_, const int* gts, int cluster_id, int num_clusters)
-      : p(p_), group_tile_start(gts), item(cluster_id), inner(0), step(num_clusters) {}
+  __device__ TileWalk(const GemmParams& p_, const int* gts, int cluster_id, int num_clusters,
+                      const volatile unsigned long long* ring_ = nullptr, volatile int* abort_ = nullptr)
+      : p(p_), group_tile_start(gts), item(cluster_id), inner(0), step(num_clusters), ring(ring_), seq(0),
+        abort_flag(abort_) {
+    if (ring) item = fetch();
+  }
+
+  // Item number `seq` of this cluster, or -1 when the work has run out (or the wait did).
+  __device__ int fetch() const {
+    const volatile unsigned long long* slot = ring + (seq & (kSchedRing - 1));
+    uint64_t start = 0;
+    for (uint32_t spin = 1;; ++spin) {
+      const unsigned long long w = *slot;
+      if (static_cast<uint32_t>(w >> 32) == seq + 1u) return static_cast<int>(static_cast<uint32_t>(w));
+      if ((spin & 0xff) == 0) {
+        if (*abort_flag) return -1;
+        const uint64_t now = global_timer_ns();
+        if (start == 0) {
+          start = now;
+        } else if (now - start > kWaitLimitNs) {
+          *abort_flag = 1;
+          atomicCAS(p.status, 0, kDevTimeoutSchedule);
+          return -1;
+        }
+      }
+    }
+  }
 
   __device__ int total_items() const {
     if constexpr (kSched == kSchedDense) return p.batch * p.tiles_m * p.tiles_n * p.split_k;
@@ -172,7 +208,7 @@ struct TileWalk {
   }
 
   __device__ bool get(Tile& t) const {
-    if (item >= total_items()) return false;
+    if (item < 0 || item >= total_items()) return false;
     t.first = 1;
     t.last = 1;
     t.kb_begin = 0;
@@ -235,7 +271,12 @@ struct TileWalk {
       if (!t.last) { ++inner; return; }
       inner = 0;
     }
-    item += step;
+    if (ring) {
+      ++seq;
+      item = fetch();
+    } else {
+      item += step;
+    }
   }
 };
 
@@ -259,6 +300,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // kSchedGrouped: [0, groups]: first m-tile of each group; [kMaxGroups + 1, ...]: first row of each group
   __shared__ int group_tile_start[kSched == kSchedGrouped ? 2 * (kMaxGroups + 1) : 1];
+  // Dynamic scheduling (CTA pairs): this CTA's copy of the cluster's item ring, and how many
+  // items this CTA's first producer warp has started (what the scheduler warp paces itself by).
+  __shared__ __align__(8) unsigned long long sched_ring[kSchedRing];
+  __shared__ int sched_progress;
+  const bool dynamic = kCtaGroup == 2 && p.sched_counter != nullptr;
 
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
@@ -290,6 +336,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(tmem_empty_bar(a), 4 * kCtaGroup);   // one arrival per epilogue warp per CTA
     }
     *abort_flag = 0;
+    for (int i = 0; i < kSchedRing; ++i) sched_ring[i] = 0ull;
+    sched_progress = 0;
     fence_mbar_init();
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
@@ -335,9 +383,11 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       uint32_t g = 0;   // K blocks seen so far, over all of this CTA's tiles
       bool ok = true;
       PROBE_DECL_IF(which == 0 && lane == 0)
-      Walk walk(p, group_tile_start, cluster_id, num_clusters);
+      Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
       Tile t;
       for (; ok && walk.get(t); walk.next(t)) {
+        if (dynamic && which == 0 && cta_rank == 1 && lane == 0 && (kSched != kSchedCeForward || t.first))
+          *reinterpret_cast<volatile int*>(&sched_progress) = static_cast<int>(walk.seq) + 1;
         const int m0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta;
         // kEpiBf16GroupedGlu (CTA pairs only): the leader loads 128 "gate" columns of B, its
         // peer the 128 "up" columns glu_cols further on, so the accumulator holds gate in
@@ -408,7 +458,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       int it = 0;
       bool ok = true;
       PROBE_DECL_IF(lane == 0)
-      Walk walk(p, group_tile_start, cluster_id, num_clusters);
+      Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
       Tile t;
       for (; ok && walk.get(t); walk.next(t), ++it) {
         const int acc = it & 1;
@@ -439,6 +489,51 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         if (ok && elect_one()) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
         __syncwarp();
       }
+    } else if (dynamic) {
+      // ---------------------------------------------------------- tile scheduler
+      // The second CTA's warp 1 has no MMAs to issue; one of its lanes hands the cluster
+      // its work instead: it takes the next item from a counter in global memory and
+      // writes it into both CTAs' rings, staying exactly one item ahead of the producers.
+      // A cluster that becomes resident late (another kernel held its SMs) simply finds
+      // less work left, where a fixed round-robin share would make it a second wave.
+      if (lane == 0) {
+        Walk counting(p, group_tile_start, 0, 1);
+        const int total = counting.total_items();
+        const uint32_t own_ring = smem_u32(sched_ring);
+        const uint32_t leader_ring = map_to_cta(own_ring, 0);
+        bool ok = true;
+        for (uint32_t q = 0;; ++q) {
+          uint64_t start = 0;
+          for (uint32_t spin = 1;
+               ok && q > static_cast<uint32_t>(*reinterpret_cast<volatile int*>(&sched_progress)); ++spin) {
+            __nanosleep(64);
+            if ((spin & 0x3f) == 0) {
+              if (*abort_flag) { ok = false; break; }
+              const uint64_t now = global_timer_ns();
+              if (start == 0) {
+                start = now;
+              } else if (now - start > kWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(p.status, 0, kDevTimeoutSchedule);
+                ok = false;
+              }
+            }
+          }
+          const int item = ok ? atomicAdd(p.sched_counter, 1) : total;
+          const uint32_t v = item < total ? static_cast<uint32_t>(item) : 0xffffffffu;
+          const unsigned long long word = (static_cast<unsigned long long>(q + 1u) << 32) | v;
+          const uint32_t off = (q & (kSchedRing - 1)) * 8u;
+          st_shared_u64(own_ring + off, word);
+          st_shared_cluster_u64(leader_ring + off, word);
+          if (v == 0xffffffffu) break;
+        }
+        // The last cluster to run out of work leaves the counters at zero for the next launch.
+        __threadfence();
+        if (atomicAdd(p.sched_counter + 1, 1) == num_clusters - 1) {
+          atomicExch(p.sched_counter, 0);
+          atomicExch(p.sched_counter + 1, 0);
+        }
+      }
     }
     __syncwarp();
   } else {
@@ -454,7 +549,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     bool have_target = false;
     constexpr float kLog2e = 1.4426950408889634f;
     PROBE_DECL_IF(warp == 2 && lane == 0)
-    Walk walk(p, group_tile_start, cluster_id, num_clusters);
+    Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
     Tile t;
     for (; ok && walk.get(t); walk.next(t), ++it) {
       const int acc = it & 1;

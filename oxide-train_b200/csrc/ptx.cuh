@@ -16,6 +16,7 @@ enum DeviceStatus : int {
   kDevTimeoutMma = 102,        // MMA issuer waited too long for operands / a free accumulator
   kDevTimeoutEpilogue = 103,   // epilogue waited too long for a finished accumulator
   kDevTimeoutDrain = 104,      // teardown waited too long for outstanding work
+  kDevTimeoutSchedule = 106,   // a role waited too long for its next tile from the tile scheduler
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -64,6 +65,17 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
+}
+
+// One 64-bit word into this CTA's shared memory / into another CTA's of the cluster
+// (address from map_to_cta).  A naturally aligned 8-byte store is a single access, so a
+// reader polling the word sees either the old or the new value, never a mixture.
+__device__ __forceinline__ void st_shared_u64(uint32_t smem_addr, unsigned long long v) {
+  asm volatile("st.volatile.shared::cta.b64 [%0], %1;" ::"r"(smem_addr), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_cluster_u64(uint32_t cluster_addr, unsigned long long v) {
+  asm volatile("st.volatile.shared::cluster.b64 [%0], %1;" ::"r"(cluster_addr), "l"(v) : "memory");
 }
 
 // ------------------------------------------------------------------ mbarrier

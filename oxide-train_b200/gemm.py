@@ -108,6 +108,10 @@ class Tcgen05Gemm:
         """Keep the persistent kernels on at most ``sms`` SMs (0 = all of them)."""
         L.check(self._lib.b200gemm_set_sm_limit(self._h, int(sms)))
 
+    def set_scheduler(self, dynamic: bool) -> None:
+        """Tiles from a device-side counter (``True``) or the fixed round-robin walk (``False``)."""
+        L.check(self._lib.b200gemm_set_scheduler(self._h, 1 if dynamic else 0))
+
     def device_status(self) -> int:
         """Synchronise and return the device status word (0 = ok); raises on a timeout."""
         code = C.c_int32()

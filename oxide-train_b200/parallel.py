@@ -179,6 +179,17 @@ def _world(group):
     return dist.get_world_size(group), dist.get_rank(group)
 
 
+def nccl_group_with_cta_limit(max_ctas: int, ranks=None):
+    """A second NCCL process group over the same ranks whose collectives use at most
+    ``max_ctas`` thread blocks (one SM each): the partner of ``reserve_sms`` below -- the GEMMs
+    leave that many SMs free and the collective is told to fit into them."""
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.config.max_ctas = int(max_ctas)
+    opts.config.min_ctas = 1
+    ranks = list(range(dist.get_world_size())) if ranks is None else list(ranks)
+    return dist.new_group(ranks=ranks, pg_options=opts)
+
+
 class _ReservedSms:
     """``with _ReservedSms(ops, n):`` -- GEMMs launched inside spread over all but ``n`` SMs.
 
@@ -432,10 +443,19 @@ class ExpertParallelMoe:
         for st in streams:
             if st is not main:
                 main.wait_stream(st)
-        routed = [t[1] for t in routed]
-        self.last = {"routing": routed[0], "pieces": pieces, "exchange": "device",
-                     "rows_received": None, "rows_sent": n * self.top_k, "offsets": offsets}
+        # `rows_received` stays on the device (one int32 per slice: the last group offset);
+        # rows_received() reads it when a report wants it.
+        self.last = {"routing": routed[0][1], "pieces": pieces, "exchange": "device",
+                     "rows_received": None, "rows_sent": n * self.top_k,
+                     "group_offsets": [t[3] for t in routed]}
         return out
+
+    def rows_received(self) -> int:
+        """Rows this rank's experts multiplied in the last forward (synchronises when the
+        device-driven exchange left the count on the device)."""
+        if self.last.get("rows_received") is not None:
+            return int(self.last["rows_received"])
+        return int(sum(int(o[-1].item()) for o in self.last.get("group_offsets", [])))
 
     def _forward_peer(self, x, scores, scores_are_logits, residual, out_dtype):
         """Several GPUs, copy-engine exchange.  The tokens go through in ``pieces`` slices:

@@ -14,6 +14,12 @@ def pytest_configure(config):
 
 
 def pytest_collection_modifyitems(config, items):
+    # No test here needs minutes: a per-test limit (pytest-timeout, when installed) turns a
+    # stuck host call into one failed test instead of a run that never ends.
+    if config.pluginmanager.hasplugin("timeout"):
+        for item in items:
+            if item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(300))
     # GPU tests skip themselves on a machine without a device, so that the CPU
     # suite can be run with or without "-m 'not gpu'".
     try:
