@@ -601,6 +601,17 @@ def run_only(args):
     if kind == "forward":
         out = torch.empty((m, o), device=dev, dtype=bf if name == "lm_head" else f32)
         fn = lambda: gemm.gemm(x, w, out, transposed_b=True)
+    elif kind == "forward_dual":            # fp32 result + its bf16 copy from one launch
+        out = torch.empty((m, o), device=dev, dtype=f32)
+        out16 = torch.empty((m, o), device=dev, dtype=bf)
+        fn = lambda: gemm.f32_store_with_bf16_copy(x, w, out, out16, transposed_b=True)
+    elif kind == "forward_then_convert":    # the two passes the dual form replaces
+        out = torch.empty((m, o), device=dev, dtype=f32)
+        out16 = torch.empty((m, o), device=dev, dtype=bf)
+
+        def fn():
+            gemm.gemm(x, w, out, transposed_b=True)
+            gemm.convert_f32_to_bf16(out, out16)
     elif kind == "input_grad":
         out = torch.empty((m, i), device=dev, dtype=f32)
         fn = lambda: gemm.f32_store(dy, w, out)

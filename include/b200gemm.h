@@ -123,6 +123,15 @@ B200GEMM_API int b200gemm_set_scheduler(b200gemm_handle_t h, int32_t mode);
 /* The tcgen05 GEMM (host.rs:616-1098, kernels gpu/gemm/src/optimized.rs:1138-1268). */
 B200GEMM_API int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc);
 
+/* b200gemm_gemm as an fp32 store that ALSO writes the result rounded to bf16 (nearest even)
+ * into c_bf16 [m, n] (row stride ldc_bf16 elements, 0 = n; per-batch stride
+ * batch_stride_c_bf16, 0 = dense): the packed operand copy the next GEMM reads, produced by
+ * the kernel that computes it.  Replaces `f32_store` followed by
+ * `convert_f32_to_bf16_pairs` (gpu/model/src/lib.rs:1194-1199; gpu/tensor-gpu/src/lib.rs:322-326).
+ * desc->out_type must be F32, desc->mode STORE; K is not split. */
+B200GEMM_API int b200gemm_gemm_dual(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc,
+                                    void* c_bf16, int64_t ldc_bf16, int64_t batch_stride_c_bf16);
+
 /* The launch geometry b200gemm_gemm would use (tcgen05_launch_config,
  * host.rs:47-94): grid, cluster size (1 or 2), dynamic shared memory, chosen
  * split-K.  Any output pointer may be NULL. */

@@ -180,6 +180,15 @@ class Tcgen05Gemm {
                                         a.rows, ff, a.k);
   }
 
+  /// f32_store that also writes the result rounded to bf16 (the next GEMM's operand copy).
+  int f32_store_with_bf16_copy(void* stream, const Operand& a, const Operand& b, float* out, void* out_bf16,
+                               int64_t ld_bf16 = 0) const {
+    if (a.k != b.k) return B200GEMM_ERR_SHAPE;
+    b200gemm_desc_t d = describe(a, b, out, B200GEMM_OUT_F32, B200GEMM_STORE, 1);
+    d.split_k = 1;
+    return b200gemm_gemm_dual(h_, stream, &d, out_bf16, ld_bf16, 0);
+  }
+
   /// Output row stride (elements) for the next calls; 0 = dense.  Lets a GEMM
   /// write one column block of a wider matrix (the grouped QKV projections,
   /// gpu/model/src/lib.rs:1379-1562).
@@ -192,8 +201,8 @@ class Tcgen05Gemm {
   int set_scheduler(bool dynamic) const { return b200gemm_set_scheduler(h_, dynamic ? 1 : 0); }
 
  private:
-  int run(void* stream, const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,
-          b200gemm_mode_t mode, int experts) const {
+  b200gemm_desc_t describe(const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,
+                           b200gemm_mode_t mode, int experts) const {
     b200gemm_desc_t d{};
     d.a = a.ptr; d.b = b.ptr; d.c = out;
     d.m = a.rows; d.n = b.rows; d.k = a.k;
@@ -202,7 +211,12 @@ class Tcgen05Gemm {
     d.out_type = out_type; d.mode = mode;
     d.batch = experts; d.split_k = split_k_;
     d.batch_stride_a = a.batch_stride; d.batch_stride_b = b.batch_stride; d.batch_stride_c = bsc_;
+    return d;
+  }
+  int run(void* stream, const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,
+          b200gemm_mode_t mode, int experts) const {
     if (a.k != b.k) return B200GEMM_ERR_SHAPE;
+    b200gemm_desc_t d = describe(a, b, out, out_type, mode, experts);
     return b200gemm_gemm(h_, stream, &d);
   }
 

@@ -273,7 +273,8 @@ int launch_one(b200gemm_context* ctx, const GemmParams& params, const Plan& plan
   return launch_kernel<CG, EPI, kSchedDense>(ctx, params, plan.grid, stream);
 }
 
-int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_t* d) {
+int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_t* d,
+                void* dual_bf16 = nullptr, int64_t ld_dual = 0, int64_t batch_stride_dual = 0) {
   Plan plan;
   int rc = make_plan(ctx, d, &plan);
   if (rc) return rc;
@@ -293,6 +294,12 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
   else if (plan.epi == kEpiBf16Tma)
     rc = encode_map(ctx, &params.map_c, bf16, 2, d->c, d->n, d->m, d->batch, plan.ldc, plan.bsc, 64, 32, "C");
   if (rc) return rc;
+
+  if (dual_bf16) {
+    rc = encode_map(ctx, &params.map_d, bf16, 2, dual_bf16, d->n, d->m, d->batch, ld_dual, batch_stride_dual, 64, 32,
+                    "bf16 copy of C");
+    if (rc) return rc;
+  }
 
   params.status = ctx->status;
   params.c_bf16 = static_cast<uint16_t*>(d->c);
@@ -322,6 +329,10 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
     }
   }
 
+  if (dual_bf16) {
+    if (plan.cta_group == 1) return launch_one<1, kEpiF32DualBf16>(ctx, params, plan, stream);
+    return launch_one<2, kEpiF32DualBf16>(ctx, params, plan, stream);
+  }
   if (plan.cta_group == 1) {
     switch (plan.epi) {
       case kEpiF32Tma: return launch_one<1, kEpiF32Tma>(ctx, params, plan, stream);
@@ -749,6 +760,25 @@ int b200gemm_gemm(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc
   int rc = check_handle(h);
   if (rc) return rc;
   return launch_gemm(h, static_cast<cudaStream_t>(stream), desc);
+}
+
+int b200gemm_gemm_dual(b200gemm_handle_t h, void* stream, const b200gemm_desc_t* desc, void* c_bf16,
+                       int64_t ldc_bf16, int64_t batch_stride_c_bf16) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!desc) return fail(B200GEMM_ERR_INVALID, "null descriptor");
+  if (!c_bf16) return fail(B200GEMM_ERR_INVALID, "null bf16 output");
+  if (desc->out_type != B200GEMM_OUT_F32 || desc->mode != B200GEMM_STORE)
+    return fail(B200GEMM_ERR_UNSUPPORTED, "the dual-output form is an fp32 store");
+  if (desc->split_k > 1) return fail(B200GEMM_ERR_UNSUPPORTED, "the dual-output form does not split K");
+  if (ldc_bf16 == 0) ldc_bf16 = desc->n;
+  if (ldc_bf16 < desc->n || (ldc_bf16 % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "bf16 row stride must be at least n and a multiple of 8");
+  if (batch_stride_c_bf16 == 0) batch_stride_c_bf16 = ldc_bf16 * desc->m;
+  if ((batch_stride_c_bf16 % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "bf16 batch stride must be a multiple of 8");
+  b200gemm_desc_t d = *desc;
+  d.split_k = 1;                       // every element is written once, by one tile
+  return launch_gemm(h, static_cast<cudaStream_t>(stream), &d, c_bf16, ldc_bf16, batch_stride_c_bf16);
 }
 
 int b200gemm_launch_config(b200gemm_handle_t h, const b200gemm_desc_t* desc, int32_t* grid,

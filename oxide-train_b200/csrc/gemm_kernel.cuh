@@ -84,6 +84,9 @@ enum EpilogueKind : int {
   // Ragged row groups, B = [gate | up] column blocks: C = silu(gate) * up (half as wide as
   // the product), and optionally the bf16 gate/up panel itself as a second output.
   kEpiBf16GroupedGlu = 6,
+  // fp32 C through TMA store plus the same values rounded to bf16 into a second matrix
+  // (the operand copy the next GEMM reads; replaces a separate fp32 -> bf16 convert pass).
+  kEpiF32DualBf16 = 7,
 };
 
 __host__ __device__ constexpr bool epi_is_grouped(int epi) {
@@ -136,7 +139,8 @@ struct GemmParams {
   int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
   // ---- kEpiBf16GroupedGlu (the reference's [rows, 2, ff] gate/up panel, gpu/ops/src/lib.rs:1149-1171)
   int glu_cols;        // ff: B's "up" block starts this many columns after its "gate" block; C is [rows, ff]
-  CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1}
+  CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1};
+                       // kEpiF32DualBf16: the bf16 copy of C, {N, M, batch}, box {64, 32, 1}
   uint16_t* d_bf16;    // panel base (null = panel not written)
   long long ldd;       // panel row stride, elements
   // ---- dynamic tile scheduling (CTA pairs): [0] next work item, [1] clusters that have
@@ -341,9 +345,10 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     fence_mbar_init();
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
-    if (kEpi == kEpiF32Tma || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || epi_is_grouped(kEpi))
+    if (kEpi == kEpiF32Tma || kEpi == kEpiF32DualBf16 || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward ||
+        epi_is_grouped(kEpi))
       prefetch_tensormap(&p.map_c);
-    if (kEpi == kEpiBf16GroupedGlu) prefetch_tensormap(&p.map_d);
+    if (kEpi == kEpiBf16GroupedGlu || kEpi == kEpiF32DualBf16) prefetch_tensormap(&p.map_d);
   }
   if constexpr (kSched == kSchedGrouped) {
     // Every CTA derives the same tile table from the offsets array.
@@ -585,10 +590,15 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         }
       };
 
-      if constexpr (kEpi == kEpiF32Tma) {
+      if constexpr (kEpi == kEpiF32Tma || kEpi == kEpiF32DualBf16) {
         constexpr int kChunks = kTileN / 32;
+        [[maybe_unused]] uint32_t packed[32];       // kEpiF32DualBf16: two fp32 chunks make one bf16 chunk
+        constexpr int kStep = kEpi == kEpiF32DualBf16 ? 2 : 1;
 #pragma unroll 1
-        for (int c = 0; c < kChunks; ++c) {
+        for (int c0 = 0; c0 < kChunks; c0 += kStep) {
+#pragma unroll
+        for (int h = 0; h < kStep; ++h) {
+          const int c = c0 + h;
           uint32_t r[32];
           tmem_ld_32x32(t_acc + c * 32, r);
           tmem_ld_wait();
@@ -603,12 +613,31 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           __syncwarp();
           PROBE_ADD(8);
           if (lane == 0) {
-            if (p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
+            if (kEpi == kEpiF32Tma && p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
             else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
             tma_commit_group();
           }
           PROBE_ADD(9);
           ++chunk_counter;
+          if constexpr (kEpi == kEpiF32DualBf16) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              packed[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            if (h == 1) {
+              const uint32_t buf2 = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+              if (lane == 0) tma_wait_group_read<1>();
+              __syncwarp();
+              stage_row(buf2, packed);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&p.map_d, buf2, col0 + (c - 1) * 32, row0, t.batch);
+                tma_commit_group();
+              }
+              ++chunk_counter;
+            }
+          }
+        }
         }
       } else if constexpr (kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward || epi_is_grouped(kEpi)) {
         constexpr bool kGlu = kEpi == kEpiBf16GroupedGlu;

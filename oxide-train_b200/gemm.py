@@ -98,6 +98,18 @@ class Tcgen05Gemm:
         d = self._desc(a, b, c, **kw)
         L.check(self._lib.b200gemm_gemm(self._h, _stream_ptr(), C.byref(d)))
 
+    def f32_store_with_bf16_copy(self, a, b, out, out_bf16, **kw) -> None:
+        """``out = A . B^T`` in fp32 and, from the same launch, ``out_bf16`` = the result
+        rounded to bf16 (replaces ``f32_store`` + ``convert_f32_to_bf16_pairs``,
+        gpu/model/src/lib.rs:1194-1199)."""
+        if out.dtype != torch.float32 or out_bf16.dtype != torch.bfloat16:
+            raise TypeError("outputs must be fp32 and bf16")
+        if out_bf16.shape != out.shape or out_bf16.stride(-1) != 1:
+            raise ValueError("the bf16 copy must have the output's shape and contiguous rows")
+        d = self._desc(a, b, out, **kw)
+        L.check(self._lib.b200gemm_gemm_dual(self._h, _stream_ptr(), C.byref(d), out_bf16.data_ptr(),
+                                             out_bf16.stride(-2), out_bf16.stride(0) if out.dim() == 3 else 0))
+
     def launch_config(self, a, b, c, **kw) -> dict:
         d = self._desc(a, b, c, **kw)
         vals = [C.c_int32() for _ in range(4)]

@@ -250,3 +250,28 @@ def test_host_buffer_form_copies_in_and_out(pkg, oracle, gemm):
     L.check(gemm._lib.b200gemm_gemm_host(gemm._h, None, C.byref(d)))
     assert_gemm_close(c, 2 * ref, "host accumulate", rel_fro=2e-5, elem=2e-4)
     assert gemm.device_status() == 0
+
+
+# ---- fp32 result + bf16 operand copy from one launch (replaces f32_store followed by
+# ---- convert_f32_to_bf16_pairs, gpu/model/src/lib.rs:1194-1199) ------------------------
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("m,n,k,tb", [(512, 768, 256, True), (300, 200, 136, False), (2048, 1536, 512, True)])
+def test_f32_store_with_bf16_copy(pkg, oracle, gemm, cg, m, n, k, tb):
+    import torch
+    a, av = bf16_operand(oracle, (m, k), 71)
+    b, bv = bf16_operand(oracle, (k, n) if tb else (n, k), 72, std=0.1)
+    plain = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    gemm.gemm(a, b, plain, transposed_b=tb, split_k=1, flags=_flags(pkg, cg))
+    out = torch.full((m, n), 3.0, dtype=torch.float32, device="cuda")
+    copy = torch.full((m + 8, n), 5.0, dtype=torch.bfloat16, device="cuda")     # canary rows at the end
+    gemm.f32_store_with_bf16_copy(a, b, out, copy[:m], transposed_b=tb, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert torch.equal(out, plain)                               # the fp32 half is the plain store
+    assert torch.equal(copy[:m], plain.to(torch.bfloat16))       # the copy is its nearest-even rounding
+    assert torch.all(copy[m:] == 5.0).item()
+    w = bv if tb else bv.T
+    assert_gemm_close(out.cpu().numpy(), oracle.matmul(av, np.ascontiguousarray(w), THREADS), "dual fp32",
+                      rel_fro=2e-5, elem=2e-4)
+    with pytest.raises(pkg.B200GemmError):                       # an fp32 store only
+        gemm.f32_store_with_bf16_copy(a, b, out, copy[:m], transposed_b=tb, accumulate=True)
