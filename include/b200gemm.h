@@ -114,7 +114,9 @@ B200GEMM_API int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms);
  *      runs slower or becomes resident late -- another kernel, e.g. a collective's, held
  *      its SMs -- simply takes fewer items instead of running a fixed share as a second
  *      wave.  Uses 8 bytes of device memory per stream, allocated (cudaMalloc) at the first
- *      launch on that stream: make that launch outside a stream capture, or choose 0.
+ *      launch on that stream: make that launch outside a stream capture, or choose 0.  A
+ *      captured graph keeps the counters of the stream it was captured on, so two replays of
+ *      one such graph must not run at the same time.
  * Results are the same either way except where a launch reduce-adds split-K slices, whose
  * order of arrival in memory is not fixed in either mode.
  * b200gemm_lmhead_ce_forward_noalloc always uses the static walk. */

@@ -1,0 +1,74 @@
+"""The expert-parallel exchange kernels (plan / push / pull-combine) on ONE GPU.
+
+`world` ranks are emulated by `world` sets of buffers on the same device and the phases
+are launched rank after rank (none of these kernels waits on another, so the order of
+launches is the only synchronisation needed).  Every rank's output must equal what the
+single-GPU grouped path computes for that rank's tokens with all experts present; the
+plan's integers are checked against their definition.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from _util import bf16_operand
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world,experts,top_k,tokens", [(4, 8, 2, 384), (2, 6, 3, 500), (8, 64, 8, 256)])
+def test_emulated_ranks_match_single_gpu_moe(pkg, oracle, world, experts, top_k, tokens):
+    import torch
+    gemm = pkg.Tcgen05Gemm()
+    ops = pkg.parallel.DeviceOps(gemm)
+    d, ff, local = 128, 192, experts // world
+    w_up, _ = bf16_operand(oracle, (experts, d, ff), 301, std=0.1)
+    w_dn, _ = bf16_operand(oracle, (experts, ff, d), 302, std=0.1)
+    xs = [bf16_operand(oracle, (tokens, d), 310 + r)[0] for r in range(world)]
+    logits = [torch.from_numpy(oracle.normal(tokens * experts, 330 + r).reshape(tokens, experts)).cuda()
+              for r in range(world)]
+    want = [pkg.GroupedExpertFfn(gemm, w_up, w_dn).forward(xs[r], logits[r], top_k, scores_are_logits=True,
+                                                           residual=xs[r])[0] for r in range(world)]
+
+    routed = [ops.route(logits[r], top_k, True) for r in range(world)]
+    counts = torch.stack([t.accepted_counts.to(torch.int32) for t in routed]).contiguous()      # [world, experts]
+    plans = [ops.ep_plan(counts, world, r, experts) for r in range(world)]
+    c = counts.cpu().numpy().astype(np.int64)
+    for r, (dst_base, offsets, index) in enumerate(plans):
+        # rows that rank j receives, laid out by (source rank, local expert)
+        recv = c[:, r * local:(r + 1) * local]                               # [source, local expert]
+        assert np.array_equal(offsets.cpu().numpy(), np.concatenate([[0], np.cumsum(recv.reshape(-1))]))
+        assert np.array_equal(index.cpu().numpy(), np.tile(np.arange(local), world))
+        base = dst_base.cpu().numpy()
+        for e in range(experts):
+            owner, le = divmod(e, local)
+            own = c[:, owner * local:(owner + 1) * local]
+            assert base[e] == own[:r].sum() + own[r, :le].sum()
+
+    cap = tokens * top_k * world
+    inbox = [torch.zeros((cap, d), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    result = [torch.zeros((cap, d), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    hidden = torch.empty((cap, ff), dtype=torch.bfloat16, device="cuda")
+    ptr_in = (C.c_void_p * world)(*[t.data_ptr() for t in inbox])
+    ptr_res = (C.c_void_p * world)(*[t.data_ptr() for t in result])
+    for r in range(world):                                                   # phase 1: every rank pushes
+        ops.ep_push(xs[r], routed[r], plans[r][0], ptr_in, cap, world, experts)
+    for j in range(world):                                                   # phase 2: every rank multiplies
+        _, offsets, index = plans[j]
+        ops.grouped_indexed_into(inbox[j], w_up[j * local:(j + 1) * local], offsets, index, True, hidden)
+        ops.grouped_indexed_into(hidden, w_dn[j * local:(j + 1) * local], offsets, index, False, result[j])
+    for r in range(world):                                                   # phase 3: every rank pulls
+        out = torch.empty((tokens, d), dtype=torch.float32, device="cuda")
+        ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], xs[r], cap, world, experts, d, out)
+        assert torch.allclose(out, want[r], atol=1e-5, rtol=1e-5), float((out - want[r]).abs().max())
+    assert gemm.device_status() == 0
+
+    # an inbox that is too small: rows beyond it are dropped and the status word says so
+    # (the last rank's rows come last in every inbox, so some of them must fall beyond the limit)
+    small = max(1, int(c[:, :local].sum()) // 2)
+    last = world - 1
+    ops.ep_push(xs[last], routed[last], plans[last][0], ptr_in, small, world, experts)
+    with pytest.raises(pkg.B200GemmError):
+        gemm.device_status()
+    assert gemm.device_status() == 0
+    gemm.close()
