@@ -217,9 +217,14 @@ def run_step(gemm, head, buf):
 
 
 def per_shape_table(torch, gemm, head, buf, iters=3):
-    """TFLOP/s of every distinct GEMM of the step, timed alone (reported, not the headline)."""
+    """TFLOP/s of every distinct GEMM of the step, timed alone (reported, not the headline).
+
+    The timed steps before it leave the GPU at its power-capped clock; a short pause lets the
+    power controller recover, so that every row -- the first one too -- is a burst figure."""
     rows = []
     layer = buf.layers[0]
+    torch.cuda.synchronize()
+    time.sleep(1.0)
 
     def timed(fn, flops):
         fn()
