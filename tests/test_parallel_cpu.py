@@ -151,7 +151,7 @@ def case_head(rank, par, ops, orc):
     logits = orc.matmul(h, w)
     loss, probs, row_loss = orc.xent_forward(logits, t, classes)
     dl = orc.xent_backward(probs, t, classes)
-    head = par.VocabParallelHead(ops, classes, v)
+    head = par.VocabParallelHead(ops, classes, v, reserve_sms=16)   # no SMs to reserve on the CPU: a no-op
     assert (head.c0, head.c1) == ((0, 512), (512, 1024))[rank]
     ws = head.shard_weight(torch.from_numpy(w))
     g_loss, lse, g_row = head.forward(torch.from_numpy(h), ws, torch.from_numpy(t))
@@ -199,7 +199,7 @@ def case_tp_mlp(rank, par, ops, orc):
     w2 = orc.normal(ff * d, 23, 0.0, 0.2).reshape(ff, d)
     cols = slice(rank * ff // WORLD, (rank + 1) * ff // WORLD)
     mlp = par.TensorParallelMlp(ops, torch.from_numpy(w1[:, cols].copy()), torch.from_numpy(w2[cols].copy()),
-                                chunks=chunks, partial_dtype=torch.float32)
+                                chunks=chunks, partial_dtype=torch.float32, reserve_sms=8)
     y = mlp.forward(torch.from_numpy(x))
     full = (x @ w1) @ w2
     rows = mlp.owned_rows(m).numpy()
