@@ -189,6 +189,69 @@ class Tcgen05Gemm {
     return b200gemm_gemm_dual(h_, stream, &d, out_bf16, ld_bf16, 0);
   }
 
+  /// grouped_gemm where group g multiplies matrix group_b_index[g] of `b` (rows received from
+  /// several ranks, each run sorted by local expert, multiplied where they landed).
+  int grouped_gemm_indexed(void* stream, const Operand& a, const Operand& b, int32_t b_count,
+                           const int32_t* group_b_index, void* c, int64_t ldc, const int32_t* offsets,
+                           int32_t groups, int activation) const {
+    return b200gemm_grouped_gemm_indexed(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, b_count,
+                                         group_b_index, c, ldc, offsets, groups, a.rows, b.rows, a.k, activation);
+  }
+
+  // ---- the lm-head's other forms ----------------------------------------------
+  /// One vocabulary shard of the fused forward: per-row max, sum-exp (relative to that max)
+  /// and target logit, to be merged across shards by the caller's all-reduces.
+  int lmhead_ce_forward_shard(void* stream, const void* hidden, const void* weight_shard,
+                              b200gemm_layout_t w_layout, const int32_t* local_targets, int64_t m, int64_t k,
+                              int64_t v_local, int64_t classes_local, float* row_max, float* row_sum,
+                              float* row_target_logit, void* workspace, size_t workspace_bytes) const {
+    return b200gemm_lmhead_ce_forward_shard(h_, stream, hidden, weight_shard, w_layout, local_targets, m, k,
+                                            v_local, classes_local, row_max, row_sum, row_target_logit, workspace,
+                                            workspace_bytes);
+  }
+  /// The fused forward on the library's built-in scratch (m <= 32768): allocates nothing.
+  int lmhead_ce_forward_noalloc(void* stream, const void* hidden, const void* weight,
+                                b200gemm_layout_t w_layout, const int32_t* targets, int64_t m, int64_t k,
+                                int64_t v, int64_t classes, float* lse, float* row_loss, float* loss) const {
+    return b200gemm_lmhead_ce_forward_noalloc(h_, stream, hidden, weight, w_layout, targets, m, k, v, classes, lse,
+                                              row_loss, loss);
+  }
+
+  // ---- fp32 family, staging converts (gpu/tensor-gpu/src/lib.rs:403-507, 1754-1851) ----
+  /// op 0: C = A.B, 1: C = A^T.B, 2: C = A.B^T (fp32 operands, bit-exact with the CPU loops).
+  int sgemm(void* stream, int op, bool accumulate, const float* a, const float* b, float* c, int64_t m,
+            int64_t n, int64_t k) const {
+    return b200gemm_sgemm(h_, stream, op, accumulate ? 1 : 0, a, b, c, m, n, k);
+  }
+  int convert_f32_to_bf16(void* stream, const float* src, void* dst_bf16, int64_t count) const {
+    return b200gemm_convert_f32_to_bf16(h_, stream, src, dst_bf16, count);
+  }
+  int convert_bf16_to_f32(void* stream, const void* src_bf16, float* dst, int64_t count) const {
+    return b200gemm_convert_bf16_to_f32(h_, stream, src_bf16, dst, count);
+  }
+  int transpose_bf16(void* stream, const void* src, void* dst, int64_t rows, int64_t cols) const {
+    return b200gemm_transpose_bf16(h_, stream, src, dst, rows, cols);
+  }
+
+  // ---- launch geometry, host buffers, device status ------------------------------
+  /// tcgen05_launch_config (host.rs:47-94) for the GEMM `store`/`f32_store`/... would launch.
+  int launch_config(const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type, b200gemm_mode_t mode,
+                    int experts, int32_t* grid, int32_t* cluster, int32_t* smem_bytes, int32_t* split_k) const {
+    b200gemm_desc_t d = describe(a, b, out, out_type, mode, experts);
+    return b200gemm_launch_config(h_, &d, grid, cluster, smem_bytes, split_k);
+  }
+  /// The GEMM on host-resident matrices (copies in, runs, copies out, synchronises).
+  int gemm_host(void* stream, const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type,
+                b200gemm_mode_t mode) const {
+    b200gemm_desc_t d = describe(a, b, out, out_type, mode, 1);
+    return b200gemm_gemm_host(h_, stream, &d);
+  }
+  /// Synchronises `stream` and returns the device status word (0 = no kernel gave up waiting).
+  int device_status(void* stream, int32_t* code = nullptr) const { return b200gemm_device_status(h_, stream, code); }
+  /// Exercises the bounded wait: the next device_status reports code 104.
+  int wait_selftest(void* stream, int64_t limit_ms) const { return b200gemm_wait_selftest(h_, stream, limit_ms); }
+  static int version() { return b200gemm_version(); }
+
   /// Output row stride (elements) for the next calls; 0 = dense.  Lets a GEMM
   /// write one column block of a wider matrix (the grouped QKV projections,
   /// gpu/model/src/lib.rs:1379-1562).

@@ -71,20 +71,39 @@ def test_descriptor_struct_matches_the_c_layout(pkg):
     assert off_flags == D.flags.offset
 
 
-def test_cpp_host_mirror_compiles():
-    gxx = shutil.which("g++") or "/usr/bin/g++"
-    src = r'''
+def test_cpp_host_mirror_compiles_links_and_covers_the_header(pkg, tmp_path):
+    """The header-only C++ mirror calls every entry point the C header declares (except the
+    three that take no handle or create one), and a program using it links against the library."""
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
+    hpp = open(os.path.join(ROOT, "include", "b200gemm.hpp")).read()
+    missing = [sym for sym in _declared_symbols() if sym + "(" not in hpp]
+    assert missing == [], missing
+    src = tmp_path / "use.cpp"
+    src.write_text(r'''
     #include "b200gemm.hpp"
-    int use(void* stream) {
+    #include <cstdio>
+    // Never called: forces every inline method used here to be instantiated and type-checked.
+    int use(b200gemm::Tcgen05Gemm& g, void* stream, void* p, float* f, const int32_t* i) {
       b200gemm::Operand a, b;
-      a.rows = 256; a.k = 64; b.rows = 256; b.k = 64;
-      b200gemm::Tcgen05Gemm* g = nullptr;
-      (void)g; (void)stream;
-      return b200gemm::TC_M_TILE + (int)sizeof(b200gemm::Tcgen05Gemm);
-    }'''
+      a.ptr = p; b.ptr = p; a.rows = 256; a.k = 64; b.rows = 256; b.k = 64;
+      int rc = g.f32_store_with_bf16_copy(stream, a, b, f, p);
+      rc |= g.grouped_gemm_swiglu(stream, a, b, 1, i, p, 0, p, 0, i, 1, 128);
+      rc |= g.grouped_gemm_indexed(stream, a, b, 1, i, p, 0, i, 1, 0);
+      rc |= g.set_scheduler(true) | g.set_sm_limit(0) | g.device_status(stream);
+      rc |= g.convert_f32_to_bf16(stream, f, p, 8) | g.transpose_bf16(stream, p, p, 8, 8);
+      rc |= g.sgemm(stream, 0, false, f, f, f, 4, 4, 4);
+      return rc;
+    }
+    int main() { std::printf("%d\n", b200gemm::Tcgen05Gemm::version()); return 0; }
+    ''')
+    exe = tmp_path / "use"
+    lib_dir = os.path.dirname(pkg._lib.LIB_PATH)
     env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
-    subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-I", os.path.join(ROOT, "include"),
-                    "-x", "c++", "-"], input=src.encode(), check=True, env=env)
+    cuda_lib = "/usr/local/cuda/lib64"
+    subprocess.run([gxx, "-std=c++17", "-Wall", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                    "-L", lib_dir, "-lb200gemm", "-Wl,-rpath," + lib_dir, "-Wl,-rpath," + cuda_lib], check=True, env=env)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, env=env).stdout.decode().strip()
+    assert int(out) == pkg._lib.load().b200gemm_version()
 
 
 def test_create_fails_loudly_without_a_gpu(pkg):
