@@ -173,6 +173,28 @@ def test_grouped_gemm_swiglu_dense_and_indexed(pkg, oracle, gemm):
         pkg.moe.grouped_gemm_swiglu(gemm, a, w200, offsets, want_gate_up=True)
 
 
+def test_grouped_gemm_swiglu_k_major_weights(pkg, oracle, gemm):
+    """The same product with the gate/up matrices stored [2 * ff, k] (K-major), through the C ABI."""
+    import torch
+    from oxide_train_b200 import _lib as L
+    from oxide_train_b200.gemm import _stream_ptr
+    sizes = [129, 300, 0, 64]
+    offsets = _ragged_offsets(sizes)
+    rows, k, ff, G = int(offsets[-1]), 128, 192, len(sizes)
+    a, _ = bf16_operand(oracle, (rows, k), 61)
+    w, _ = bf16_operand(oracle, (G, k, 2, ff), 62, std=0.1)
+    offs = torch.from_numpy(offsets).cuda()
+    want_y, want_panel = pkg.moe.grouped_gemm_swiglu(gemm, a, w, offs, want_gate_up=True)
+    wk = w.permute(0, 2, 3, 1).contiguous().reshape(G, 2 * ff, k)          # [G, 2*ff, k]
+    y = torch.zeros((rows, ff), dtype=torch.bfloat16, device="cuda")
+    panel = torch.zeros((rows, 2, ff), dtype=torch.bfloat16, device="cuda")
+    L.check(gemm._lib.b200gemm_grouped_gemm_swiglu(
+        gemm._h, _stream_ptr(), a.data_ptr(), k, wk.data_ptr(), L.K_MAJOR, k, 2 * ff * k, G, None,
+        y.data_ptr(), ff, panel.data_ptr(), 2 * ff, offs.data_ptr(), G, rows, ff, k))
+    assert gemm.device_status() == 0
+    assert torch.equal(y, want_y) and torch.equal(panel, want_panel)
+
+
 def test_grouped_gemm_leaves_rows_outside_groups_untouched(pkg, oracle, gemm):
     import torch
     offsets = np.array([0, 100, 100, 260], np.int32)       # total 260 of 400 rows are routed
