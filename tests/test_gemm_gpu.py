@@ -275,3 +275,18 @@ def test_f32_store_with_bf16_copy(pkg, oracle, gemm, cg, m, n, k, tb):
                       rel_fro=2e-5, elem=2e-4)
     with pytest.raises(pkg.B200GemmError):                       # an fp32 store only
         gemm.f32_store_with_bf16_copy(a, b, out, copy[:m], transposed_b=tb, accumulate=True)
+
+
+def test_f32_store_with_bf16_copy_batched(pkg, oracle, gemm):
+    """The dual form over a batch ("experts"): both outputs strided per matrix."""
+    import torch
+    e, m, n, k = 3, 320, 256, 192
+    a, _ = bf16_operand(oracle, (e, m, k), 73)
+    b, _ = bf16_operand(oracle, (e, n, k), 74, std=0.1)
+    plain = torch.empty((e, m, n), dtype=torch.float32, device="cuda")
+    gemm.f32_store_batched(a, b, plain, split_k=1)
+    out = torch.zeros((e, m, n), dtype=torch.float32, device="cuda")
+    copy = torch.zeros((e, m, n), dtype=torch.bfloat16, device="cuda")
+    gemm.f32_store_with_bf16_copy(a, b, out, copy)
+    assert gemm.device_status() == 0
+    assert torch.equal(out, plain) and torch.equal(copy, plain.to(torch.bfloat16))

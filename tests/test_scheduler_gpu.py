@@ -119,3 +119,19 @@ def test_two_streams_at_once(pkg, oracle, gemms):
             dynamic.gemm(a, b2, got2, split_k=1)
     torch.cuda.synchronize()
     assert torch.equal(want1, got1) and torch.equal(want2, got2)
+
+
+def test_dynamic_schedule_on_a_limited_number_of_sms(pkg, oracle, gemms):
+    """`set_sm_limit` shrinks the grid; the counter still hands every item out exactly once."""
+    import torch
+    static, dynamic = gemms
+    a, _ = bf16_operand(oracle, (2048, 512), 214)
+    b, _ = bf16_operand(oracle, (512, 1280), 215, std=0.1)
+    want = torch.empty((2048, 1280), dtype=torch.float32, device="cuda")
+    static.gemm(a, b, want, transposed_b=True, split_k=1)
+    for sms in (100, 6, 2, 0):
+        dynamic.set_sm_limit(sms)
+        got = torch.zeros_like(want)
+        dynamic.gemm(a, b, got, transposed_b=True, split_k=1)
+        assert torch.equal(want, got), sms
+    dynamic.set_sm_limit(0)
