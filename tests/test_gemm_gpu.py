@@ -290,3 +290,47 @@ def test_f32_store_with_bf16_copy_batched(pkg, oracle, gemm):
     gemm.f32_store_with_bf16_copy(a, b, out, copy)
     assert gemm.device_status() == 0
     assert torch.equal(out, plain) and torch.equal(copy, plain.to(torch.bfloat16))
+
+
+# ---- gpu/gemm/src/bin/transpose_probe.rs:123-171: the four operand encodings of the layout
+# ---- sweep (128 x 64 x 64), in every storage order of A and B ---------------------------
+
+def _probe_operands(oracle, encoding):
+    M, N, K = 128, 64, 64
+    if encoding == "random":
+        return oracle.uniform(M * K, 71).reshape(M, K), oracle.uniform(N * K, 72).reshape(N, K)
+    a = np.zeros((M, K), np.float32)
+    b = np.zeros((N, K), np.float32)
+    if encoding == "outer":                      # C[m, n] = (m + 1)(n + 1)
+        a[:, 0] = np.arange(1, M + 1)
+        b[:, 0] = np.arange(1, N + 1)
+    elif encoding == "a_walk":                   # C[m, n] = (m mod K) + 1
+        a[np.arange(M), np.arange(M) % K] = 1.0
+        b[:] = np.arange(1, K + 1)
+    else:                                        # b_walk: C[m, n] = n + 1
+        a[:] = np.arange(1, K + 1)
+        b[np.arange(N), np.arange(N)] = 1.0
+    return a, b
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("encoding", ["outer", "a_walk", "b_walk", "random"])
+def test_transpose_probe_encodings_in_every_storage_order(pkg, oracle, gemm, cg, encoding):
+    import torch
+    a, b = _probe_operands(oracle, encoding)
+    a_bits, b_bits = oracle.bf16_bits(a.reshape(-1)).reshape(a.shape), oracle.bf16_bits(b.reshape(-1)).reshape(b.shape)
+    av, bv = oracle.bf16_to_f32(a_bits).reshape(a.shape), oracle.bf16_to_f32(b_bits).reshape(b.shape)
+    expected = oracle.matmul_nt(av, bv, THREADS)
+    if encoding == "outer":
+        assert np.array_equal(expected, np.outer(np.arange(1, 129), np.arange(1, 65)))
+    # the reference's tolerances (transpose_probe.rs:125-130): integers admit no slack
+    atol, rtol = (0.02, 0.01) if encoding == "random" else (1e-3, 0.0)
+    for ta in (False, True):
+        for tb in (False, True):
+            a_dev = to_dev_bf16(np.ascontiguousarray(a_bits.T) if ta else a_bits)
+            b_dev = to_dev_bf16(np.ascontiguousarray(b_bits.T) if tb else b_bits)
+            c = torch.full((128, 64), -1.0, dtype=torch.float32, device="cuda")
+            gemm.gemm(a_dev, b_dev, c, transposed_a=ta, transposed_b=tb, flags=_flags(pkg, cg))
+            got = c.cpu().numpy()
+            assert np.all(np.abs(got - expected) <= atol + rtol * np.abs(expected)), (encoding, ta, tb)
+    assert gemm.device_status() == 0
