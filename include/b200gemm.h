@@ -20,7 +20,12 @@
  *    dimensions must keep rows 16-byte aligned (multiples of 8 bf16 / 4 fp32);
  *  - either operand may be MN-major independently, so a `[IN, OUT]` weight can
  *    be read in place without a transposed shadow copy;
- *  - split-K for the deep (K = tokens) weight-gradient shapes.
+ *  - split-K for the deep (K = tokens) weight-gradient shapes;
+ *  - fused forms the reference runs as separate passes: the lm-head with its classifier
+ *    (b200gemm_lmhead_ce_*), SiLU / SwiGLU in the grouped expert GEMM
+ *    (b200gemm_grouped_gemm*), the fp32 result with its bf16 copy (b200gemm_gemm_dual);
+ *  - tiles handed out from a device-side counter (b200gemm_set_scheduler), and an SM cap
+ *    (b200gemm_set_sm_limit), for running beside a collective's kernels.
  */
 #ifndef B200GEMM_H_
 #define B200GEMM_H_
