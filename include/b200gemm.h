@@ -195,7 +195,9 @@ B200GEMM_API int b200gemm_gemm_host(b200gemm_handle_t h, void* stream, const b20
  *   hidden    device bf16 [m, k], row stride k
  *   weight    device bf16; w_layout == B200GEMM_MN_MAJOR: stored [k, v] (the
  *             reference's [IN, OUT] master), == B200GEMM_K_MAJOR: stored [v, k]
- *   targets   device int32 [m], each in [0, classes)
+ *   targets   device int32 [m], each in [0, classes) (crates/nn/src/cross_entropy.rs:38 asserts
+ *             it); a row whose target is outside gets a NaN loss -- so the mean is NaN -- and
+ *             device status 107 is recorded (b200gemm_device_status)
  *   v         padded vocabulary (row stride of a [k, v] weight); columns at or
  *             beyond `classes` are ignored (gpu/ops/src/lib.rs:1721-1829)
  *   lse       device fp32 [m] out: max + ln(sum exp) per row (input of backward)
@@ -232,6 +234,19 @@ B200GEMM_API int b200gemm_lmhead_ce_forward_shard(b200gemm_handle_t h, void* str
                                                   void* workspace, size_t workspace_bytes);
 
 /*
+ * Merge of the shards' statistics into the global result (the formula above), one launch
+ * for all rows instead of a chain of elementwise passes between two all-reduces:
+ *   stats   device fp32 [world][3][m]: every shard's row_max, row_sum, row_target_logit
+ *           (three consecutive [m] arrays per shard, i.e. what one all-gather of each rank's
+ *           [3][m] block produces)
+ *   lse, row_loss (may be NULL), loss (may be NULL; needs row_loss): as b200gemm_lmhead_ce_forward
+ * New: the reference is single-GPU.
+ */
+B200GEMM_API int b200gemm_lmhead_ce_merge_shards(b200gemm_handle_t h, void* stream, const float* stats,
+                                                 int32_t world, int64_t m, float* lse, float* row_loss,
+                                                 float* loss);
+
+/*
  * b200gemm_lmhead_ce_forward for callers that cannot hand the library a
  * workspace.  This entry point has no counterpart in the reference.
  *
@@ -247,9 +262,13 @@ B200GEMM_API int b200gemm_lmhead_ce_forward_shard(b200gemm_handle_t h, void* str
  *
  * Limits and rules:
  *   - m <= 32768 rows; larger m is refused with B200GEMM_ERR_SHAPE.
+ *   - The handle's device must be current on the calling thread at every call
+ *     (checked; B200GEMM_ERR_INVALID otherwise).
  *   - The first call on a device looks up the array's device address.  Make
- *     that first call with the handle's device current, and make it before any
- *     stream capture is begun on that device; later calls only launch kernels.
+ *     that first call before any stream capture is begun on that device; later
+ *     calls only launch kernels.  With lazy module loading the driver may give
+ *     the array its memory only at that first call, so a host that is about to
+ *     claim all of HBM for its arena makes one warm-up call BEFORE it does so.
  *   - All calls on one device share the one array: two calls whose kernels can
  *     overlap on the GPU (different streams, no ordering between them) race on
  *     it and corrupt each other's loss.  Order them on one stream or with events.
@@ -343,6 +362,114 @@ B200GEMM_API int b200gemm_grouped_gemm_swiglu(b200gemm_handle_t h, void* stream,
                                               int64_t total_rows, int64_t ff, int64_t k);
 
 /*
+ * b200gemm_grouped_gemm with activation 1 (SiLU) that can also keep what the activation
+ * was applied to: before[rows, n] (bf16, row stride ld_before, 0 = n; NULL skips it) gets
+ * A . B^T rounded to bf16, y[rows, n] gets silu of the fp32 product.  `before` is what
+ * b200gemm_activation_backward reads.  group_b_index / b_count as in
+ * b200gemm_grouped_gemm_indexed (NULL = group g uses B[g]).  New: the reference's expert
+ * is the gated form (b200gemm_grouped_gemm_swiglu).
+ */
+B200GEMM_API int b200gemm_grouped_gemm_silu(b200gemm_handle_t h, void* stream, const void* a,
+                                            int64_t lda, const void* b, int32_t b_layout, int64_t ldb,
+                                            int64_t batch_stride_b, int32_t b_count,
+                                            const int32_t* group_b_index, void* y, int64_t ldy,
+                                            void* before, int64_t ld_before, const int32_t* offsets,
+                                            int32_t groups, int64_t total_rows, int64_t n, int64_t k);
+
+/*
+ * Weight gradients of the expert linears over the routed permutation: the row groups are
+ * the REDUCTION axis.
+ *
+ *   for g in [0, groups):  C[i(g)] [m, n] (=|+=) A[rows_g, 0:m]^T . B[rows_g, 0:n]
+ *                          rows_g = [offsets[g], offsets[g+1]),  i(g) = group_c_index ? group_c_index[g] : g
+ *
+ * Replaces f32_accumulate_transposed_batched over capacity bins
+ * (gpu/gemm/src/host.rs:997-1026 as called from expert_linear_backward,
+ * gpu/model/src/lib.rs:2011-2055): here a group contributes exactly its own rows, not a
+ * bin padded to capacity.
+ *   a        device bf16 [total_rows, m], row stride lda (0 = m): the expert linear's input rows
+ *   b        device bf16 [total_rows, n], row stride ldb (0 = n): the gradient of its output rows
+ *   c        device fp32, c_count (or `groups`) matrices [m, n], row stride ldc (0 = n),
+ *            batch_stride_c elements apart (0 = dense)
+ *   offsets  DEVICE int32 [groups + 1], as b200gemm_grouped_gemm; groups <= 192
+ *   accumulate != 0 adds into C; 0 overwrites it (C is cleared first; an empty group
+ *            leaves its matrix zero).  Several groups may share one matrix (rows received
+ *            from several ranks for the same expert).
+ * Long groups are cut into chunks of a few thousand rows that different CTA pairs multiply
+ * at the same time and add into C with the copy engine's fp32 reduction, so a hot expert
+ * does not serialise on one pair; the order of those additions is not fixed.
+ */
+B200GEMM_API int b200gemm_grouped_wgrad(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                        const void* b, int64_t ldb, float* c, int64_t ldc,
+                                        int64_t batch_stride_c, int32_t c_count,
+                                        const int32_t* group_c_index, const int32_t* offsets,
+                                        int32_t groups, int64_t total_rows, int64_t m, int64_t n,
+                                        int32_t accumulate);
+
+/*
+ * Backward of b200gemm_moe_combine (crates/nn/src/moe.rs:360-381): for every accepted
+ * (token, rank) pair
+ *   dy_permuted[dest_row, :] = gate * dy[token, :]                         bf16
+ *   gate_grad[pair] = sum_d y_permuted[dest_row, d] * dy[token, d]         fp32; 0 for a dropped pair
+ * dy is [tokens, d] fp32 or bf16 (dy_type: b200gemm_out_t).  y_permuted (the expert outputs
+ * the forward combined) and gate_grad may both be NULL when the router is not trained.
+ * Rows of dy_permuted that no pair maps to are left untouched.
+ */
+B200GEMM_API int b200gemm_moe_combine_backward(b200gemm_handle_t h, void* stream, const void* dy,
+                                               int32_t dy_type, const void* y_permuted,
+                                               const uint32_t* dest_row, const float* gates,
+                                               int64_t tokens, int32_t top_k, int64_t d,
+                                               void* dy_permuted, float* gate_grad);
+
+/*
+ * Backward of the expert's activation over the routed rows, bf16 in and out.
+ *   activation 1 (SiLU, y = silu(a)):       saved = a [rows, ff] (b200gemm_grouped_gemm_silu's
+ *       `before`), d_saved[rows, ff] = d_y * s * (1 + a * (1 - s)), s = sigmoid(a)
+ *   activation 2 (SwiGLU, y = silu(g) * u): saved = the [rows, 2, ff] gate/up panel
+ *       (b200gemm_grouped_gemm_swiglu's `gate_up`), d_saved likewise:
+ *       d_g = d_y * u * s * (1 + g * (1 - s)),  d_u = d_y * g * s
+ *       (crates/nn/src/swiglu.rs:30-47; gpu/ops/src/lib.rs:1453 swiglu_backward_interleaved_packed)
+ * Row strides in elements, 0 = packed; ff % 8 == 0.  d_saved may alias d_y only for SiLU.
+ */
+B200GEMM_API int b200gemm_activation_backward(b200gemm_handle_t h, void* stream, int32_t activation,
+                                              const void* saved, int64_t ld_saved, const void* d_y,
+                                              int64_t ld_dy, int64_t rows, int64_t ff, void* d_saved,
+                                              int64_t ld_dsaved);
+
+/*
+ * Backward of the routing (crates/nn/src/moe.rs:397-445): from the gradients of the combine
+ * weights to the gradient of the router's logits, fp32 [tokens, experts].
+ *   probs    the router's softmax (the `scores` b200gemm_moe_route selected from)
+ *   gate_grad from b200gemm_moe_combine_backward; aux_coefficient weighs the load-balancing
+ *   term experts * fraction[e] / tokens, fraction[e] = assignment_counts[e] / (tokens * top_k).
+ */
+B200GEMM_API int b200gemm_moe_route_backward(b200gemm_handle_t h, void* stream, const float* probs,
+                                             const uint32_t* selected, const float* gates,
+                                             const float* gate_grad, const uint32_t* assignment_counts,
+                                             float aux_coefficient, int64_t tokens, int32_t experts,
+                                             int32_t top_k, float* dlogits);
+
+/*
+ * Router logits (gpu/ops/src/lib.rs:2319-2429 router_logits_bf16, whose ROUTER_MAX_EXPERTS
+ * is 8): logits[tokens, experts] = x[tokens, d] (bf16) . w[d, experts] (fp32), experts <= 256.
+ * fp32 arithmetic on CUDA cores, products rounded and added in ascending k: the CPU
+ * router's own sums (crates/nn/src/moe.rs:290 `self.router.forward`), bit for bit, so
+ * that expert selection cannot differ from the reference's on near-ties.
+ */
+B200GEMM_API int b200gemm_router_logits(b200gemm_handle_t h, void* stream, const void* x, const float* w,
+                                        int64_t tokens, int64_t d, int32_t experts, float* logits);
+
+/*
+ * The scalar training loss (gpu/ops/src/lib.rs:2852-2904 loss_mean_with_aux):
+ *   loss[0] = mean(row_loss[0:tokens]) + coefficient * sum(aux_terms[0:aux_count])
+ * row_loss as written by b200gemm_lmhead_ce_forward; aux_terms one per MoE layer (device
+ * fp32, may be NULL with aux_count 0).  The token sum is carried in f64.
+ */
+B200GEMM_API int b200gemm_loss_mean_with_aux(b200gemm_handle_t h, void* stream, const float* row_loss,
+                                             int64_t tokens, const float* aux_terms, int32_t aux_count,
+                                             float coefficient, float* loss);
+
+/*
  * MoE routing integers and gates (crates/nn/src/moe.rs:205-254 `MoeFfn::route`;
  * GPU counterparts gpu/ops/src/lib.rs:2435-2511 router_softmax_topk, :2569-2705
  * moe_bin_assign_parallel).  All pointers are device pointers.
@@ -372,7 +499,9 @@ B200GEMM_API int b200gemm_moe_scatter(b200gemm_handle_t h, void* stream, const v
 
 /* Combine (gpu/ops/src/lib.rs:3064-3130 moe_gather_combine_add_quad_packed):
  * out[t, :] = residual[t, :] + sum_r gates[t,r] * y_permuted[dest_row[t,r], :], ranks
- * added in order in fp32.  residual may be NULL.  out_type: b200gemm_out_t. */
+ * added in order in fp32.  residual may be NULL.  out_type: b200gemm_out_t.
+ * gates == NULL means weights of one: then this is the backward of the dispatch,
+ * dx[t, :] = sum_r dx_permuted[dest_row[t,r], :] (crates/nn/src/moe.rs:383-395). */
 B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permuted,
                                       const uint32_t* dest_row, const float* gates,
                                       const void* residual, int64_t tokens, int32_t top_k, int64_t d,

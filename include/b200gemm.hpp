@@ -198,6 +198,51 @@ class Tcgen05Gemm {
                                          group_b_index, c, ldc, offsets, groups, a.rows, b.rows, a.k, activation);
   }
 
+  // ---- backward of the expert path (crates/nn/src/moe.rs:354-445) ----------------
+  /// grouped_gemm with SiLU that also keeps the values before the activation (`before`, may be null).
+  int grouped_gemm_silu(void* stream, const Operand& a, const Operand& b, int32_t b_count,
+                        const int32_t* group_b_index, void* y, int64_t ldy, void* before, int64_t ld_before,
+                        const int32_t* offsets, int32_t groups) const {
+    return b200gemm_grouped_gemm_silu(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, b_count,
+                                      group_b_index, y, ldy, before, ld_before, offsets, groups, a.rows, b.rows, a.k);
+  }
+  /// dW[g] (=|+=) A[rows_g]^T . B[rows_g]: the row groups are the reduction axis
+  /// (f32_accumulate_transposed_batched over exact groups instead of capacity bins).
+  int grouped_wgrad(void* stream, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc,
+                    int64_t batch_stride_c, int32_t c_count, const int32_t* group_c_index, const int32_t* offsets,
+                    int32_t groups, int64_t total_rows, int64_t m, int64_t n, bool accumulate) const {
+    return b200gemm_grouped_wgrad(h_, stream, a, lda, b, ldb, c, ldc, batch_stride_c, c_count, group_c_index,
+                                  offsets, groups, total_rows, m, n, accumulate ? 1 : 0);
+  }
+  int moe_combine_backward(void* stream, const void* dy, b200gemm_out_t dy_type, const void* y_permuted,
+                           const uint32_t* dest_row, const float* gates, int64_t tokens, int32_t top_k, int64_t d,
+                           void* dy_permuted, float* gate_grad) const {
+    return b200gemm_moe_combine_backward(h_, stream, dy, dy_type, y_permuted, dest_row, gates, tokens, top_k, d,
+                                         dy_permuted, gate_grad);
+  }
+  /// activation 1 = SiLU (saved = values before it), 2 = SwiGLU (saved = the [rows, 2, ff] panel).
+  int activation_backward(void* stream, int activation, const void* saved, int64_t ld_saved, const void* d_y,
+                          int64_t ld_dy, int64_t rows, int64_t ff, void* d_saved, int64_t ld_dsaved) const {
+    return b200gemm_activation_backward(h_, stream, activation, saved, ld_saved, d_y, ld_dy, rows, ff, d_saved,
+                                        ld_dsaved);
+  }
+  int moe_route_backward(void* stream, const float* probs, const uint32_t* selected, const float* gates,
+                         const float* gate_grad, const uint32_t* assignment_counts, float aux_coefficient,
+                         int64_t tokens, int32_t experts, int32_t top_k, float* dlogits) const {
+    return b200gemm_moe_route_backward(h_, stream, probs, selected, gates, gate_grad, assignment_counts,
+                                       aux_coefficient, tokens, experts, top_k, dlogits);
+  }
+  /// logits = x (bf16) . w (fp32 [d, experts]); router_logits_bf16 for up to 256 experts.
+  int router_logits(void* stream, const void* x, const float* w, int64_t tokens, int64_t d, int32_t experts,
+                    float* logits) const {
+    return b200gemm_router_logits(h_, stream, x, w, tokens, d, experts, logits);
+  }
+  /// mean(row_loss) + coefficient * sum(aux_terms)  (loss_mean_with_aux).
+  int loss_mean_with_aux(void* stream, const float* row_loss, int64_t tokens, const float* aux_terms,
+                         int32_t aux_count, float coefficient, float* loss) const {
+    return b200gemm_loss_mean_with_aux(h_, stream, row_loss, tokens, aux_terms, aux_count, coefficient, loss);
+  }
+
   // ---- the lm-head's other forms ----------------------------------------------
   /// One vocabulary shard of the fused forward: per-row max, sum-exp (relative to that max)
   /// and target logit, to be merged across shards by the caller's all-reduces.
@@ -208,6 +253,11 @@ class Tcgen05Gemm {
     return b200gemm_lmhead_ce_forward_shard(h_, stream, hidden, weight_shard, w_layout, local_targets, m, k,
                                             v_local, classes_local, row_max, row_sum, row_target_logit, workspace,
                                             workspace_bytes);
+  }
+  /// Shards' (max, sum-exp, target logit) blocks, gathered as [world][3][m], into lse / row losses / mean.
+  int lmhead_ce_merge_shards(void* stream, const float* stats, int32_t world, int64_t m, float* lse,
+                             float* row_loss, float* loss) const {
+    return b200gemm_lmhead_ce_merge_shards(h_, stream, stats, world, m, lse, row_loss, loss);
   }
   /// The fused forward on the library's built-in scratch (m <= 32768): allocates nothing.
   int lmhead_ce_forward_noalloc(void* stream, const void* hidden, const void* weight,

@@ -453,3 +453,100 @@ ORC_API void orc_swiglu(const float* gate, const float* up, float* out, size_t n
     out[i] = gate[i] * sigmoid * up[i];
   }
 }
+
+/* ------------------------------------------------------------------------ */
+/* MoE backward: crates/nn/src/moe.rs:354-445, crates/nn/src/swiglu.rs:30-47  */
+/* ------------------------------------------------------------------------ */
+
+/* SwiGLU backward (swiglu.rs:30-47): dgate = dy*up*dsilu, dup = dy*silu. */
+ORC_API void orc_swiglu_backward(const float* gate, const float* up, const float* dy, float* dgate,
+                                 float* dup, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    float sigmoid = 1.0f / (1.0f + expf(-gate[i]));
+    float silu = gate[i] * sigmoid;
+    float dsilu = sigmoid * (1.0f + gate[i] * (1.0f - sigmoid));
+    dgate[i] = dy[i] * up[i] * dsilu;
+    dup[i] = dy[i] * silu;
+  }
+}
+
+/* SiLU backward: the gate half of the above with up = 1. */
+ORC_API void orc_silu_backward(const float* g, const float* dy, float* dg, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    float sigmoid = 1.0f / (1.0f + expf(-g[i]));
+    float dsilu = sigmoid * (1.0f + g[i] * (1.0f - sigmoid));
+    dg[i] = dy[i] * dsilu;
+  }
+}
+
+/*
+ * Backward of the combine (moe.rs:360-381) over the permuted row layout: for every
+ * accepted pair, dy_permuted[dest_row] = gate * dy[token] and
+ * gate_grad[pair] = sum_d expert_out[dest_row][d] * dy[token][d] summed in f64.
+ * Rows of dy_permuted that no pair maps to, and gate_grad of dropped pairs, are zero.
+ */
+ORC_API void orc_moe_combine_backward(const float* dy, const float* y_permuted, const uint32_t* dest_row,
+                                      const float* gates, size_t N, size_t K, size_t D, size_t rows,
+                                      float* dy_permuted, float* gate_grad) {
+  memset(dy_permuted, 0, rows * D * sizeof(float));
+  for (size_t token = 0; token < N; ++token) {
+    for (size_t rank = 0; rank < K; ++rank) {
+      size_t pair = token * K + rank;
+      gate_grad[pair] = 0.0f;
+      if (dest_row[pair] == ORC_DROPPED) continue;
+      size_t row = dest_row[pair];
+      float gate = gates[pair];
+      double gg = 0.0;
+      for (size_t d = 0; d < D; ++d) {
+        dy_permuted[row * D + d] += gate * dy[token * D + d];
+        gg += (double)y_permuted[row * D + d] * (double)dy[token * D + d];
+      }
+      gate_grad[pair] = (float)gg;
+    }
+  }
+}
+
+/* Backward of the dispatch (moe.rs:383-395): dx[token] = sum over accepted ranks, in
+ * order, of dx_permuted[dest_row]. */
+ORC_API void orc_moe_scatter_backward(const float* dx_permuted, const uint32_t* dest_row, size_t N, size_t K,
+                                      size_t D, float* dx) {
+  memset(dx, 0, N * D * sizeof(float));
+  for (size_t token = 0; token < N; ++token)
+    for (size_t rank = 0; rank < K; ++rank) {
+      size_t pair = token * K + rank;
+      if (dest_row[pair] == ORC_DROPPED) continue;
+      for (size_t d = 0; d < D; ++d) dx[token * D + d] += dx_permuted[(size_t)dest_row[pair] * D + d];
+    }
+}
+
+/* Backward of the routing (moe.rs:397-445): gate gradients -> probability gradients
+ * (renormalised top-k + the load-balancing term) -> router logit gradients. */
+ORC_API void orc_moe_route_backward(const float* probs, const uint32_t* selected, const float* gates,
+                                    const float* gate_grad, const uint32_t* assignment_counts,
+                                    float aux_coefficient, size_t N, size_t E, size_t K, float* dlogits) {
+  float* dprob = (float*)malloc(E * sizeof(float));
+  for (size_t token = 0; token < N; ++token) {
+    const float* p = probs + token * E;
+    for (size_t e = 0; e < E; ++e) dprob[e] = 0.0f;
+    double weighted = 0.0, psum = 0.0;
+    for (size_t rank = 0; rank < K; ++rank) {
+      size_t pair = token * K + rank;
+      weighted += (double)gate_grad[pair] * (double)gates[pair];
+      psum += (double)p[selected[pair]];
+    }
+    float weighted_f = (float)weighted, psum_f = (float)psum;
+    for (size_t rank = 0; rank < K; ++rank) {
+      size_t pair = token * K + rank;
+      dprob[selected[pair]] += (gate_grad[pair] - weighted_f) / psum_f;
+    }
+    for (size_t e = 0; e < E; ++e) {
+      float fraction = (float)assignment_counts[e] / (float)(N * K);
+      dprob[e] += aux_coefficient * (float)E * fraction / (float)N;
+    }
+    double dot = 0.0;
+    for (size_t e = 0; e < E; ++e) dot += (double)p[e] * (double)dprob[e];
+    float dot_f = (float)dot;
+    for (size_t e = 0; e < E; ++e) dlogits[token * E + e] = p[e] * (dprob[e] - dot_f);
+  }
+  free(dprob);
+}

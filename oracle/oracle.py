@@ -79,6 +79,11 @@ def _declare(L: C.CDLL) -> None:
     L.orc_moe_permutation.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, sz, C.c_void_p]
     L.orc_silu.argtypes = [f32p, f32p, sz]
     L.orc_swiglu.argtypes = [f32p, f32p, f32p, sz]
+    L.orc_swiglu_backward.argtypes = [f32p] * 5 + [sz]
+    L.orc_silu_backward.argtypes = [f32p] * 3 + [sz]
+    L.orc_moe_combine_backward.argtypes = [f32p, f32p, C.c_void_p, f32p, sz, sz, sz, sz, f32p, f32p]
+    L.orc_moe_scatter_backward.argtypes = [f32p, C.c_void_p, sz, sz, sz, f32p]
+    L.orc_moe_route_backward.argtypes = [f32p, C.c_void_p, f32p, f32p, C.c_void_p, C.c_float, sz, sz, sz, f32p]
 
 
 def _p(a: np.ndarray):
@@ -245,4 +250,55 @@ def swiglu(gate, up) -> np.ndarray:
     gate, up = _f32(gate), _f32(up)
     out = np.empty_like(gate)
     lib().orc_swiglu(_p(gate), _p(up), _p(out), gate.size)
+    return out
+
+
+# --------------------------------------------------------------------------- MoE backward
+
+def swiglu_backward(gate, up, dy):
+    """``SwiGlu::backward``: returns ``(dgate, dup)``."""
+    gate, up, dy = _f32(gate), _f32(up), _f32(dy)
+    dg, du = np.empty_like(gate), np.empty_like(gate)
+    lib().orc_swiglu_backward(_p(gate), _p(up), _p(dy), _p(dg), _p(du), gate.size)
+    return dg, du
+
+
+def silu_backward(g, dy) -> np.ndarray:
+    g, dy = _f32(g), _f32(dy)
+    dg = np.empty_like(g)
+    lib().orc_silu_backward(_p(g), _p(dy), _p(dg), g.size)
+    return dg
+
+
+def moe_combine_backward(dy, y_permuted, dest_row, gates, top_k: int):
+    """Backward of the combine: ``(dy_permuted [rows, D], gate_grad [N*K])``."""
+    dy, y_permuted, gates = _f32(dy), _f32(y_permuted), _f32(gates)
+    dest_row = np.ascontiguousarray(dest_row, dtype=np.uint32)
+    n, d = dy.shape
+    rows = y_permuted.shape[0]
+    dyp = np.empty((rows, d), dtype=np.float32)
+    gg = np.empty(n * top_k, dtype=np.float32)
+    lib().orc_moe_combine_backward(_p(dy), _p(y_permuted), _p(dest_row), _p(gates), n, top_k, d, rows,
+                                   _p(dyp), _p(gg))
+    return dyp, gg
+
+
+def moe_scatter_backward(dx_permuted, dest_row, tokens: int, top_k: int) -> np.ndarray:
+    dx_permuted = _f32(dx_permuted)
+    dest_row = np.ascontiguousarray(dest_row, dtype=np.uint32)
+    d = dx_permuted.shape[1]
+    dx = np.empty((tokens, d), dtype=np.float32)
+    lib().orc_moe_scatter_backward(_p(dx_permuted), _p(dest_row), tokens, top_k, d, _p(dx))
+    return dx
+
+
+def moe_route_backward(probs, selected, gates, gate_grad, assignment_counts, aux_coefficient: float,
+                       top_k: int) -> np.ndarray:
+    probs, gates, gate_grad = _f32(probs), _f32(gates), _f32(gate_grad)
+    selected = np.ascontiguousarray(selected, dtype=np.uint32)
+    counts = np.ascontiguousarray(assignment_counts, dtype=np.uint32)
+    n, e = probs.shape
+    out = np.empty_like(probs)
+    lib().orc_moe_route_backward(_p(probs), _p(selected), _p(gates), _p(gate_grad), _p(counts),
+                                 aux_coefficient, n, e, top_k, _p(out))
     return out

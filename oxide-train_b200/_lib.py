@@ -87,6 +87,28 @@ SIGNATURES = {
                                                C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                                C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
                                                C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "b200gemm_grouped_gemm_silu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                             C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
+                                             C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                             C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "b200gemm_grouped_wgrad": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                         C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
+                                         C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),
+    "b200gemm_moe_combine_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+                                                C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64,
+                                                C.c_void_p, C.c_void_p]),
+    "b200gemm_activation_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int64,
+                                               C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                               C.c_int64]),
+    "b200gemm_moe_route_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_float, C.c_int64, C.c_int32,
+                                              C.c_int32, C.c_void_p]),
+    "b200gemm_router_logits": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                         C.c_int32, C.c_void_p]),
+    "b200gemm_loss_mean_with_aux": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                              C.c_int32, C.c_float, C.c_void_p]),
+    "b200gemm_lmhead_ce_merge_shards": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
+                                                  C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                                      C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                                      C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -28,10 +28,6 @@ namespace {
 using namespace b200;
 
 thread_local char g_error[512] = "";
-#ifdef B200_PROBE
-long long* g_probe = nullptr;   // diagnostic builds only: device buffer of phase counters
-int g_probe_skip_loads = 0;
-#endif
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -65,7 +61,7 @@ struct b200gemm_context {
   // staging for b200gemm_gemm_host
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
-  bool smem_opt_in[2][8] = {};   // [cta_group - 1][epilogue kind]
+  bool smem_opt_in[2][8][4] = {};   // [cta_group - 1][epilogue kind][schedule kind]: one per kernel instantiation
   // per-segment expert counts of b200gemm_moe_route: one buffer per stream, so that routing
   // calls issued on different streams can overlap on the GPU without sharing scratch
   struct Scratch {
@@ -245,7 +241,7 @@ int launch_kernel(b200gemm_context* ctx, const GemmParams& params_in, int grid, 
   }
   // Per-device opt-in to > 48 KiB dynamic shared memory, once per kernel
   // (the reference's opt_in_dynamic_smem, host.rs:485-505).
-  bool& ready = ctx->smem_opt_in[CG - 1][EPI];
+  bool& ready = ctx->smem_opt_in[CG - 1][EPI][SCHED];
   if (!ready) {
     CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   GemmCfg<CG>::kSmemBytes));
@@ -316,10 +312,6 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
   params.a_mn = a_mn;
   params.b_mn = b_mn;
   params.reduce = plan.reduce;
-#ifdef B200_PROBE
-  params.probe = g_probe;
-  params.probe_skip_loads = g_probe_skip_loads;
-#endif
 
   if (plan.epi == kEpiF32Tma && d->mode == B200GEMM_STORE && plan.split_k > 1) {
     // K slices all reduce-add into C, so a store starts from zeros.
@@ -470,8 +462,9 @@ int ce_forward(b200gemm_context* ctx, cudaStream_t stream, const void* hidden, c
     CUDA_TRY(cudaGetLastError());
     return B200GEMM_OK;
   }
-  ce_combine_kernel<<<blocks, 256, 0, stream>>>(ws.partials, ws.target_logit, static_cast<int>(m),
-                                                params.ce_chunks, lse, row_loss, loss, ws.accum);
+  ce_combine_kernel<<<blocks, 256, 0, stream>>>(ws.partials, ws.target_logit, targets, static_cast<int>(classes),
+                                                static_cast<int>(m), params.ce_chunks, lse, row_loss, loss,
+                                                ws.accum, ctx->status);
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
 }
@@ -555,9 +548,9 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const int32_t b_mats = group_b_index ? b_count : groups;
   if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 2)
     return fail(B200GEMM_ERR_INVALID, "bad layout or activation");
-  if (panel && !glu) return fail(B200GEMM_ERR_INVALID, "a gate/up panel is written only by the SwiGLU form");
+  if (panel && activation == 0) return fail(B200GEMM_ERR_INVALID, "a second output is written only with an activation");
   if (glu && (n % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "SwiGLU needs ff to be a multiple of 8");
-  if (panel && (n % 64) != 0) return fail(B200GEMM_ERR_SHAPE, "the gate/up panel needs ff to be a multiple of 64");
+  if (panel && glu && (n % 64) != 0) return fail(B200GEMM_ERR_SHAPE, "the gate/up panel needs ff to be a multiple of 64");
   if (groups < 1 || groups > kMaxGroups) return fail(B200GEMM_ERR_SHAPE, "groups must be in [1, %d]", kMaxGroups);
   if (total_rows <= 0 || n <= 0 || k <= 0 || total_rows > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30))
     return fail(B200GEMM_ERR_SHAPE, "bad extent");
@@ -565,11 +558,12 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   lda = lda ? lda : k;
   ldb = ldb ? ldb : (b_mn ? bn : k);
   ldc = ldc ? ldc : n;
-  ld_panel = ld_panel ? ld_panel : 2 * n;
+  const int64_t panel_cols = glu ? 2 * n : n;            // SiLU keeps the [rows, n] values before the activation
+  ld_panel = ld_panel ? ld_panel : panel_cols;
   if (lda < k || ldb < (b_mn ? bn : k) || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
   if ((ldc % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "ldc must be a multiple of 8");
-  if (panel && (ld_panel < 2 * n || (ld_panel % 8) != 0))
-    return fail(B200GEMM_ERR_SHAPE, "panel row stride must be at least 2 * ff and a multiple of 8");
+  if (panel && (ld_panel < panel_cols || (ld_panel % 8) != 0))
+    return fail(B200GEMM_ERR_SHAPE, "second output's row stride must cover its row and be a multiple of 8");
   const int64_t bsb = batch_stride_b ? batch_stride_b : ldb * (b_mn ? k : bn);
   GemmParams params;
   memset(&params, 0, sizeof(params));
@@ -582,7 +576,7 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   rc = encode_map(ctx, &params.map_c, bf16, 2, c, n, total_rows, 1, ldc, 0, 64, 32, "C");
   if (rc) return rc;
   if (panel) {
-    rc = encode_map(ctx, &params.map_d, bf16, 2, panel, 2 * n, total_rows, 1, ld_panel, 0, 64, 32, "panel");
+    rc = encode_map(ctx, &params.map_d, bf16, 2, panel, panel_cols, total_rows, 1, ld_panel, 0, 64, 32, "panel");
     if (rc) return rc;
     params.d_bf16 = static_cast<uint16_t*>(panel);
     params.ldd = ld_panel;
@@ -611,6 +605,64 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
   if (glu) return launch_kernel<2, kEpiBf16GroupedGlu, kSchedGrouped>(ctx, params, grid, stream);
   return launch_kernel<2, kEpiBf16Grouped, kSchedGrouped>(ctx, params, grid, stream);
+}
+
+// Weight gradients of the grouped GEMM: the row groups are the reduction axis.
+int grouped_wgrad(b200gemm_context* ctx, cudaStream_t stream, const void* a, int64_t lda, const void* b,
+                  int64_t ldb, float* c, int64_t ldc, int64_t batch_stride_c, int32_t c_count,
+                  const int32_t* group_c_index, const int32_t* offsets, int32_t groups, int64_t total_rows,
+                  int64_t m, int64_t n, int32_t accumulate) {
+  if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (groups < 1 || groups > kMaxGroups) return fail(B200GEMM_ERR_SHAPE, "groups must be in [1, %d]", kMaxGroups);
+  if (group_c_index && c_count < 1) return fail(B200GEMM_ERR_SHAPE, "c_count must be positive with a group index");
+  const int32_t c_mats = group_c_index ? c_count : groups;
+  if (total_rows <= 0 || m <= 0 || n <= 0 || total_rows > (1ll << 30) || m > (1ll << 30) || n > (1ll << 30))
+    return fail(B200GEMM_ERR_SHAPE, "bad extent");
+  lda = lda ? lda : m;
+  ldb = ldb ? ldb : n;
+  ldc = ldc ? ldc : n;
+  if (lda < m || ldb < n || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
+  const int64_t bsc = batch_stride_c ? batch_stride_c : ldc * m;
+  GemmParams params;
+  memset(&params, 0, sizeof(params));
+  const auto bf16 = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  // Both operands are [rows = K, width] row-major: MN-major boxes of 64 x 64.
+  int rc = encode_map(ctx, &params.map_a, bf16, 2, a, m, total_rows, 1, lda, 0, 64, 64, "A");
+  if (rc) return rc;
+  rc = encode_map(ctx, &params.map_b, bf16, 2, b, n, total_rows, 1, ldb, 0, 64, 64, "B");
+  if (rc) return rc;
+  rc = encode_map(ctx, &params.map_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, c, n, m, c_mats, ldc, bsc, 32, 32, "C");
+  if (rc) return rc;
+  params.status = ctx->status;
+  params.m = static_cast<int>(m);
+  params.n = static_cast<int>(n);
+  params.tiles_m = ceil_div(m, 2 * kTileMCta);
+  params.tiles_n = ceil_div(n, kTileN);
+  params.batch = c_mats;
+  params.a_mn = 1;
+  params.b_mn = 1;
+  params.reduce = 1;                       // every (group, chunk) item adds its part into C
+  params.group_offsets = offsets;
+  params.group_b_index = group_c_index;
+  params.groups = groups;
+  params.split_k = 1;
+  // Rows per chunk: short enough that the items outnumber the clusters several times over
+  // (hot experts then spread over many clusters instead of serialising on one), long enough
+  // that the reduce-add traffic of an item stays small beside its products.
+  const int units = std::max(1, ctx->sm_count / 2);
+  const int64_t tiles = static_cast<int64_t>(params.tiles_m) * params.tiles_n;
+  const int64_t total_kb = ceil_div(total_rows, kBlockK);
+  int64_t chunk = total_kb * tiles / (8ll * units);
+  chunk = std::max<int64_t>(8, std::min<int64_t>(64, chunk));
+  params.kb_per_split = static_cast<int>(chunk);
+  params.k_blocks = static_cast<int>(chunk);
+  if (!accumulate) {
+    for (int e = 0; e < c_mats; ++e)
+      CUDA_TRY(cudaMemset2DAsync(c + static_cast<int64_t>(e) * bsc, ldc * sizeof(float), 0, n * sizeof(float), m, stream));
+  }
+  const int64_t max_items = (ceil_div(total_kb, chunk) + static_cast<int64_t>(groups)) * tiles;
+  const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
+  return launch_kernel<2, kEpiF32Tma, kSchedGroupedWgrad>(ctx, params, grid, stream);
 }
 
 // ---------------------------------------------------------------- MoE routing
@@ -650,13 +702,15 @@ int ce_static_scratch(int device, void** out) {
   if (device < 0 || device >= kCeStaticMaxDevices)
     return fail(B200GEMM_ERR_UNSUPPORTED, "device ordinal %d is beyond the %d this entry point tracks",
                 device, kCeStaticMaxDevices);
+  // Every call, not only the first: the launches below go to whichever device is current,
+  // with pointers that belong to `device`.
+  int current = -1;
+  CUDA_TRY(cudaGetDevice(&current));
+  if (current != device)
+    return fail(B200GEMM_ERR_INVALID, "device %d must be current on the calling thread (device %d is)",
+                device, current);
   std::lock_guard<std::mutex> lock(g_ce_static_mu);
   if (!g_ce_static_ptr[device]) {
-    int current = -1;
-    CUDA_TRY(cudaGetDevice(&current));
-    if (current != device)
-      return fail(B200GEMM_ERR_INVALID, "device %d must be current on the calling thread (device %d is)",
-                  device, current);
     void* ptr = nullptr;
     CUDA_TRY(cudaGetSymbolAddress(&ptr, g_ce_static_scratch));
     if (!ptr) return fail(B200GEMM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
@@ -693,15 +747,6 @@ int b200gemm_set_scheduler(b200gemm_handle_t h, int32_t mode) {
   h->scheduler = mode;
   return B200GEMM_OK;
 }
-
-#ifdef B200_PROBE
-__attribute__((visibility("default"))) void b200gemm_set_probe(long long* device_buffer) {
-  g_probe = device_buffer;
-}
-__attribute__((visibility("default"))) void b200gemm_set_probe_skip_loads(int on) {
-  g_probe_skip_loads = on;
-}
-#endif
 
 const char* b200gemm_last_error_string(void) { return g_error; }
 
@@ -951,8 +996,9 @@ int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const void* y_permut
                          int64_t tokens, int32_t top_k, int64_t d, void* out, int32_t out_type) {
   int rc = check_handle(h);
   if (rc) return rc;
-  if (!y_permuted || !dest_row || !gates || !out) return fail(B200GEMM_ERR_INVALID, "null pointer");
-  if (tokens <= 0 || top_k < 1 || d <= 0 || (d % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "need tokens, top_k > 0 and d a multiple of 8");
+  if (!y_permuted || !dest_row || !out) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
   if (out_type < 0 || out_type > 1) return fail(B200GEMM_ERR_INVALID, "bad output type");
   const int grid = stream_grid(tokens * 32, h->sm_count);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -1096,6 +1142,145 @@ int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const*
   return B200GEMM_OK;
 }
 
+int b200gemm_grouped_wgrad(b200gemm_handle_t h, void* stream, const void* a, int64_t lda, const void* b,
+                           int64_t ldb, float* c, int64_t ldc, int64_t batch_stride_c, int32_t c_count,
+                           const int32_t* group_c_index, const int32_t* offsets, int32_t groups,
+                           int64_t total_rows, int64_t m, int64_t n, int32_t accumulate) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  return grouped_wgrad(h, static_cast<cudaStream_t>(stream), a, lda, b, ldb, c, ldc, batch_stride_c, c_count,
+                       group_c_index, offsets, groups, total_rows, m, n, accumulate);
+}
+
+int b200gemm_grouped_gemm_silu(b200gemm_handle_t h, void* stream, const void* a, int64_t lda, const void* b,
+                               int32_t b_layout, int64_t ldb, int64_t batch_stride_b, int32_t b_count,
+                               const int32_t* group_b_index, void* y, int64_t ldy, void* before,
+                               int64_t ld_before, const int32_t* offsets, int32_t groups, int64_t total_rows,
+                               int64_t n, int64_t k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, y, ldy,
+                      offsets, groups, total_rows, n, k, 1, group_b_index, b_count, before, ld_before);
+}
+
+int b200gemm_moe_combine_backward(b200gemm_handle_t h, void* stream, const void* dy, int32_t dy_type,
+                                  const void* y_permuted, const uint32_t* dest_row, const float* gates,
+                                  int64_t tokens, int32_t top_k, int64_t d, void* dy_permuted,
+                                  float* gate_grad) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!dy || !dest_row || !gates || !dy_permuted) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if ((gate_grad != nullptr) != (y_permuted != nullptr))
+    return fail(B200GEMM_ERR_INVALID, "y_permuted and gate_grad go together");
+  if (dy_type < 0 || dy_type > 1) return fail(B200GEMM_ERR_INVALID, "bad dy type");
+  if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
+  const int grid = stream_grid(tokens * 32, h->sm_count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dy_type == B200GEMM_OUT_BF16)
+    moe_combine_backward_kernel<true><<<grid, 256, 0, s>>>(dy, static_cast<const uint16_t*>(y_permuted), dest_row,
+                                                           gates, tokens, top_k, d,
+                                                           static_cast<uint16_t*>(dy_permuted), gate_grad);
+  else
+    moe_combine_backward_kernel<false><<<grid, 256, 0, s>>>(dy, static_cast<const uint16_t*>(y_permuted), dest_row,
+                                                            gates, tokens, top_k, d,
+                                                            static_cast<uint16_t*>(dy_permuted), gate_grad);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_activation_backward(b200gemm_handle_t h, void* stream, int32_t activation, const void* saved,
+                                 int64_t ld_saved, const void* d_y, int64_t ld_dy, int64_t rows, int64_t ff,
+                                 void* d_saved, int64_t ld_dsaved) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!saved || !d_y || !d_saved) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (activation != 1 && activation != 2) return fail(B200GEMM_ERR_INVALID, "activation is 1 (SiLU) or 2 (SwiGLU)");
+  if (rows <= 0 || ff <= 0 || (ff % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "need rows > 0 and ff a positive multiple of 8");
+  const int64_t width = activation == 2 ? 2 * ff : ff;
+  ld_saved = ld_saved ? ld_saved : width;
+  ld_dsaved = ld_dsaved ? ld_dsaved : width;
+  ld_dy = ld_dy ? ld_dy : ff;
+  if (ld_saved < width || ld_dsaved < width || ld_dy < ff || (ld_saved % 8) || (ld_dsaved % 8) || (ld_dy % 8))
+    return fail(B200GEMM_ERR_SHAPE, "row strides must cover their rows and be multiples of 8");
+  if (((reinterpret_cast<uintptr_t>(saved) | reinterpret_cast<uintptr_t>(d_y) | reinterpret_cast<uintptr_t>(d_saved)) & 15u) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "buffers must be 16-byte aligned");
+  const int grid = stream_grid(rows * (ff / 8), h->sm_count);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (activation == 2)
+    activation_backward_kernel<true><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(saved), ld_saved,
+                                                          static_cast<const uint16_t*>(d_y), ld_dy, rows, ff,
+                                                          static_cast<uint16_t*>(d_saved), ld_dsaved);
+  else
+    activation_backward_kernel<false><<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(saved), ld_saved,
+                                                           static_cast<const uint16_t*>(d_y), ld_dy, rows, ff,
+                                                           static_cast<uint16_t*>(d_saved), ld_dsaved);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_moe_route_backward(b200gemm_handle_t h, void* stream, const float* probs, const uint32_t* selected,
+                                const float* gates, const float* gate_grad, const uint32_t* assignment_counts,
+                                float aux_coefficient, int64_t tokens, int32_t experts, int32_t top_k,
+                                float* dlogits) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!probs || !selected || !gates || !gate_grad || !assignment_counts || !dlogits)
+    return fail(B200GEMM_ERR_INVALID, "null pointer");
+  rc = moe_check(tokens, experts, top_k);
+  if (rc) return rc;
+  const int blocks = static_cast<int>((tokens * 32 + 255) / 256);
+  moe_route_backward_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      probs, selected, gates, gate_grad, assignment_counts, aux_coefficient, tokens, experts, top_k, dlogits);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_router_logits(b200gemm_handle_t h, void* stream, const void* x, const float* w, int64_t tokens,
+                           int64_t d, int32_t experts, float* logits) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!x || !w || !logits) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (tokens <= 0 || tokens > (1ll << 28) || d <= 0 || d > (1ll << 24))
+    return fail(B200GEMM_ERR_SHAPE, "bad token count or width");
+  if (experts < 1 || experts > kMoeMaxExperts) return fail(B200GEMM_ERR_SHAPE, "experts must be in [1, %d]", kMoeMaxExperts);
+  dim3 grid(static_cast<unsigned>((tokens + 63) / 64), static_cast<unsigned>((experts + 63) / 64));
+  router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), w, tokens, static_cast<int>(d), experts, logits);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_loss_mean_with_aux(b200gemm_handle_t h, void* stream, const float* row_loss, int64_t tokens,
+                                const float* aux_terms, int32_t aux_count, float coefficient, float* loss) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!row_loss || !loss || (aux_count > 0 && !aux_terms)) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (tokens <= 0 || aux_count < 0) return fail(B200GEMM_ERR_SHAPE, "need tokens > 0 and aux_count >= 0");
+  loss_mean_with_aux_kernel<<<1, kLossTailThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      row_loss, tokens, aux_terms, aux_count, coefficient, loss);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_lmhead_ce_merge_shards(b200gemm_handle_t h, void* stream, const float* stats, int32_t world,
+                                    int64_t m, float* lse, float* row_loss, float* loss) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!stats || !lse) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (loss && !row_loss) return fail(B200GEMM_ERR_INVALID, "the mean needs row_loss");
+  if (world < 1 || world > 64 || m <= 0 || m > (1ll << 30)) return fail(B200GEMM_ERR_SHAPE, "bad world or row count");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ce_merge_shards_kernel<<<stream_grid(m, h->sm_count), 256, 0, s>>>(stats, world, m, lse, row_loss);
+  CUDA_TRY(cudaGetLastError());
+  if (loss) {
+    loss_mean_with_aux_kernel<<<1, kLossTailThreads, 0, s>>>(row_loss, m, nullptr, 0, 0.f, loss);
+    CUDA_TRY(cudaGetLastError());
+  }
+  return B200GEMM_OK;
+}
+
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {
   int rc = check_handle(h);
   if (rc) return rc;
@@ -1104,30 +1289,57 @@ int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t
   if (rc) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   std::lock_guard<std::mutex> lock(h->mu);
+  const bool a_mn = desc->a_layout == B200GEMM_MN_MAJOR, b_mn = desc->b_layout == B200GEMM_MN_MAJOR;
   const size_t c_elem = desc->out_type == B200GEMM_OUT_F32 ? 4 : 2;
-  const size_t bytes[3] = {static_cast<size_t>(plan.bsa) * desc->batch * 2,
-                           static_cast<size_t>(plan.bsb) * desc->batch * 2,
-                           static_cast<size_t>(plan.bsc) * desc->batch * c_elem};
+  // Each matrix as stored: `rows` rows of `width` elements, `ld` elements apart, `batch`
+  // matrices `bs` elements apart.  Only the `width` elements of a row belong to the matrix:
+  // with ld > width the rest of the row is the caller's (a column slice of a wider matrix),
+  // so it is neither read nor written.  The device copies keep the host's strides.
+  struct Mat {
+    const void* host;
+    int64_t rows, width, ld, bs;
+    size_t elem;
+  };
+  const Mat mats[3] = {
+      {desc->a, a_mn ? desc->k : desc->m, a_mn ? desc->m : desc->k, plan.lda, plan.bsa, 2},
+      {desc->b, b_mn ? desc->k : desc->n, b_mn ? desc->n : desc->k, plan.ldb, plan.bsb, 2},
+      {desc->c, desc->m, desc->n, plan.ldc, plan.bsc, c_elem},
+  };
   for (int i = 0; i < 3; ++i) {
-    if (h->stage_bytes[i] < bytes[i]) {
+    const Mat& t = mats[i];
+    const size_t bytes = static_cast<size_t>((desc->batch - 1) * t.bs + (t.rows - 1) * t.ld + t.width) * t.elem;
+    if (h->stage_bytes[i] < bytes) {
       if (h->stage[i]) CUDA_TRY(cudaFree(h->stage[i]));
       h->stage[i] = nullptr;
       h->stage_bytes[i] = 0;
-      CUDA_TRY(cudaMalloc(&h->stage[i], bytes[i]));
-      h->stage_bytes[i] = bytes[i];
+      CUDA_TRY(cudaMalloc(&h->stage[i], bytes));
+      h->stage_bytes[i] = bytes;
     }
   }
-  CUDA_TRY(cudaMemcpyAsync(h->stage[0], desc->a, bytes[0], cudaMemcpyHostToDevice, stream));
-  CUDA_TRY(cudaMemcpyAsync(h->stage[1], desc->b, bytes[1], cudaMemcpyHostToDevice, stream));
-  if (desc->mode == B200GEMM_ACCUMULATE)
-    CUDA_TRY(cudaMemcpyAsync(h->stage[2], desc->c, bytes[2], cudaMemcpyHostToDevice, stream));
+  auto copy = [&](int i, cudaMemcpyKind kind) -> cudaError_t {
+    const Mat& t = mats[i];
+    for (int e = 0; e < desc->batch; ++e) {
+      const size_t off = static_cast<size_t>(e) * t.bs * t.elem;
+      uint8_t* dev = static_cast<uint8_t*>(h->stage[i]) + off;
+      uint8_t* host = static_cast<uint8_t*>(const_cast<void*>(t.host)) + off;
+      const size_t pitch = static_cast<size_t>(t.ld) * t.elem;
+      cudaError_t err = kind == cudaMemcpyHostToDevice
+                            ? cudaMemcpy2DAsync(dev, pitch, host, pitch, t.width * t.elem, t.rows, kind, stream)
+                            : cudaMemcpy2DAsync(host, pitch, dev, pitch, t.width * t.elem, t.rows, kind, stream);
+      if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+  };
+  CUDA_TRY(copy(0, cudaMemcpyHostToDevice));
+  CUDA_TRY(copy(1, cudaMemcpyHostToDevice));
+  if (desc->mode == B200GEMM_ACCUMULATE) CUDA_TRY(copy(2, cudaMemcpyHostToDevice));
   b200gemm_desc_t dev = *desc;
   dev.a = h->stage[0];
   dev.b = h->stage[1];
   dev.c = h->stage[2];
   rc = launch_gemm(h, stream, &dev);
   if (rc) return rc;
-  CUDA_TRY(cudaMemcpyAsync(desc->c, h->stage[2], bytes[2], cudaMemcpyDeviceToHost, stream));
+  CUDA_TRY(copy(2, cudaMemcpyDeviceToHost));
   CUDA_TRY(cudaStreamSynchronize(stream));
   return B200GEMM_OK;
 }
@@ -1157,7 +1369,10 @@ int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_co
       std::lock_guard<std::mutex> lock(h->sched_mu);
       for (auto& kv : h->sched_counters) CUDA_TRY(cudaMemsetAsync(kv.second, 0, 2 * sizeof(int), s));
     }
-    return fail(B200GEMM_ERR_DEVICE, "a kernel gave up waiting (device status %d)", code);
+    return fail(B200GEMM_ERR_DEVICE,
+                "a kernel reported device status %d (101-104, 106: a bounded wait ran out; 105: a row fell "
+                "outside an exchange buffer; 107: a cross-entropy target outside [0, classes))",
+                code);
   }
   return B200GEMM_OK;
 }

@@ -32,30 +32,14 @@
 //                   softmax statistics of its rows
 //   kSchedGrouped   variable-length row groups (experts) found through a
 //                   device-side offsets array
+//   kSchedGroupedWgrad  the same row groups as the REDUCTION axis: one output
+//                   matrix per group, (group, row chunk, tile) items that
+//                   reduce-add into it
 //
 // Epilogues (template parameter kEpi) are listed at EpilogueKind.
 #pragma once
 
 #include "ptx.cuh"
-
-// Optional phase probe (compile with -DB200_PROBE): one thread per role adds the
-// clock cycles it spends in each phase into p.probe[blockIdx.x * 16 + slot].
-// Not compiled into the product library.
-#ifdef B200_PROBE
-#define PROBE_DECL long long probe_t_ = clock64(); const bool probe_on_ = true;
-#define PROBE_DECL_IF(cond) long long probe_t_ = clock64(); const bool probe_on_ = (cond);
-#define PROBE_ADD(slot)                                                        \
-  do {                                                                         \
-    long long now_ = clock64();                                                \
-    if (p.probe && probe_on_) atomicAdd(reinterpret_cast<unsigned long long*>(p.probe) + blockIdx.x * 16 + (slot), \
-                           static_cast<unsigned long long>(now_ - probe_t_));  \
-    probe_t_ = now_;                                                           \
-  } while (0)
-#else
-#define PROBE_DECL
-#define PROBE_DECL_IF(cond)
-#define PROBE_ADD(slot)
-#endif
 
 namespace b200 {
 
@@ -93,7 +77,11 @@ __host__ __device__ constexpr bool epi_is_grouped(int epi) {
   return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu;
 }
 
-enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2 };
+enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2, kSchedGroupedWgrad = 3 };
+
+__host__ __device__ constexpr bool sched_is_grouped(int sched) {
+  return sched == kSchedGrouped || sched == kSchedGroupedWgrad;
+}
 
 template <int kCtaGroup>
 struct GemmCfg {
@@ -140,16 +128,13 @@ struct GemmParams {
   // ---- kEpiBf16GroupedGlu (the reference's [rows, 2, ff] gate/up panel, gpu/ops/src/lib.rs:1149-1171)
   int glu_cols;        // ff: B's "up" block starts this many columns after its "gate" block; C is [rows, ff]
   CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1};
-                       // kEpiF32DualBf16: the bf16 copy of C, {N, M, batch}, box {64, 32, 1}
+                       // kEpiF32DualBf16: the bf16 copy of C, {N, M, batch}, box {64, 32, 1};
+                       // kEpiBf16Grouped: C before the activation, {N, rows, 1}, box {64, 32, 1}
   uint16_t* d_bf16;    // panel base (null = panel not written)
   long long ldd;       // panel row stride, elements
   // ---- dynamic tile scheduling (CTA pairs): [0] next work item, [1] clusters that have
   // finished fetching; both are zero between launches.  Null = static round-robin.
   int* sched_counter;
-#ifdef B200_PROBE
-  long long* probe;
-  int probe_skip_loads;   // timing experiment: producers signal "full" without copying anything
-#endif
 };
 
 constexpr int kSchedRing = 16;   // items in flight per cluster are far fewer (stages + accumulators + 2)
@@ -160,6 +145,8 @@ struct Tile {
   int m_end;       // rows at or beyond this are outside the tile's group (grouped schedule)
   int tile_n;
   int kb_begin, kb_count;
+  int k0;          // first element of the tile's walk along K (kb_begin * 64 except in kSchedGroupedWgrad)
+  int k_tail;      // elements of the walk's last K block that belong to it (64 = all of them)
   int first, last;  // position inside a kSchedCeForward run
 };
 
@@ -208,7 +195,8 @@ struct TileWalk {
   __device__ int total_items() const {
     if constexpr (kSched == kSchedDense) return p.batch * p.tiles_m * p.tiles_n * p.split_k;
     else if constexpr (kSched == kSchedCeForward) return p.tiles_m * p.ce_chunks;
-    else return group_tile_start[p.groups] * p.tiles_n;
+    else if constexpr (kSched == kSchedGrouped) return group_tile_start[p.groups] * p.tiles_n;
+    else return group_tile_start[p.groups] * p.tiles_m * p.tiles_n;
   }
 
   __device__ bool get(Tile& t) const {
@@ -217,6 +205,8 @@ struct TileWalk {
     t.last = 1;
     t.kb_begin = 0;
     t.kb_count = p.k_blocks;
+    t.k0 = 0;
+    t.k_tail = kBlockK;
     t.m_end = p.m;
     if constexpr (kSched == kSchedDense) {
       int split = item % p.split_k;
@@ -233,6 +223,7 @@ struct TileWalk {
       t.tile_n = in_group / group_rows;
       t.kb_begin = split * p.kb_per_split;
       t.kb_count = min(p.kb_per_split, p.k_blocks - t.kb_begin);
+      t.k0 = t.kb_begin * kBlockK;
     } else if constexpr (kSched == kSchedCeForward) {
       // Row blocks vary fastest, so the clusters running side by side walk the
       // same vocabulary chunk (shared W tiles in L2) on different rows.
@@ -246,7 +237,7 @@ struct TileWalk {
       t.tile_n = first_tile + inner;
       t.first = inner == 0;
       t.last = inner == count - 1;
-    } else {
+    } else if constexpr (kSched == kSchedGrouped) {
       // item -> (m-tile over all groups, n-tile) with n fastest: the clusters running
       // side by side then cover a couple of dozen consecutive m-tiles (one to three
       // experts) times all n-tiles, so every A tile is fetched from HBM once and the
@@ -266,6 +257,32 @@ struct TileWalk {
       t.m0 = group_row_start[g] + (tm - group_tile_start[g]) * kTileM;
       t.m_end = group_row_start[g + 1];
       t.tile_n = tn;
+    }
+    if constexpr (kSched == kSchedGroupedWgrad) {
+      // item -> (row chunk over all groups, output tile) with the tile fastest: the clusters
+      // running side by side multiply the same few thousand rows into different tiles of one
+      // group's output, so those rows come from HBM once.  A chunk is kb_per_split K blocks of
+      // one group's rows, counted from the group's first row; only a group's last block can be
+      // short, and the rows behind it belong to the next group (see the MMA issuer).
+      const int tiles = p.tiles_m * p.tiles_n;
+      const int chunk = item / tiles;
+      const int tile = item - chunk * tiles;
+      int lo = 0, hi = p.groups - 1;
+      while (lo < hi) {
+        int mid = (lo + hi + 1) >> 1;
+        if (group_tile_start[mid] <= chunk) lo = mid; else hi = mid - 1;
+      }
+      while (lo + 1 < p.groups && group_tile_start[lo + 1] <= chunk) ++lo;
+      const int g = lo;
+      const int* group_row_start = group_tile_start + kMaxGroups + 1;
+      const int first_row = group_row_start[g] + (chunk - group_tile_start[g]) * p.kb_per_split * kBlockK;
+      const int rows = min(group_row_start[g + 1] - first_row, p.kb_per_split * kBlockK);
+      t.batch = p.group_b_index ? p.group_b_index[g] : g;
+      t.m0 = (tile % p.tiles_m) * kTileM;
+      t.tile_n = tile / p.tiles_m;
+      t.kb_count = (rows + kBlockK - 1) / kBlockK;
+      t.k0 = first_row;
+      t.k_tail = rows - (t.kb_count - 1) * kBlockK;
     }
     return true;
   }
@@ -303,7 +320,8 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using Walk = TileWalk<kSched, Cfg::kTileM>;
   extern __shared__ uint8_t smem_raw[];
   // kSchedGrouped: [0, groups]: first m-tile of each group; [kMaxGroups + 1, ...]: first row of each group
-  __shared__ int group_tile_start[kSched == kSchedGrouped ? 2 * (kMaxGroups + 1) : 1];
+  // kSchedGroupedWgrad: [0, groups]: first row chunk of each group; then the first rows likewise
+  __shared__ int group_tile_start[sched_is_grouped(kSched) ? 2 * (kMaxGroups + 1) : 1];
   // Dynamic scheduling (CTA pairs): this CTA's copy of the cluster's item ring, and how many
   // items this CTA's first producer warp has started (what the scheduler warp paces itself by).
   __shared__ __align__(8) unsigned long long sched_ring[kSchedRing];
@@ -348,19 +366,22 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     if (kEpi == kEpiF32Tma || kEpi == kEpiF32DualBf16 || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward ||
         epi_is_grouped(kEpi))
       prefetch_tensormap(&p.map_c);
-    if (kEpi == kEpiBf16GroupedGlu || kEpi == kEpiF32DualBf16) prefetch_tensormap(&p.map_d);
+    if (kEpi == kEpiBf16GroupedGlu || kEpi == kEpiF32DualBf16 || (kEpi == kEpiBf16Grouped && p.d_bf16))
+      prefetch_tensormap(&p.map_d);
   }
-  if constexpr (kSched == kSchedGrouped) {
+  if constexpr (sched_is_grouped(kSched)) {
     // Every CTA derives the same tile table from the offsets array.
     if (warp == 3) {
       for (int g = lane; g <= p.groups; g += 32) group_tile_start[kMaxGroups + 1 + g] = p.group_offsets[g];
       __syncwarp();
       if (lane == 0) {
+        // rows per unit of the table: an output tile's rows, or a reduction chunk's
+        const int unit = kSched == kSchedGrouped ? Cfg::kTileM : p.kb_per_split * kBlockK;
         int run = 0;
         for (int g = 0; g < p.groups; ++g) {
           group_tile_start[g] = run;
           int rows = group_tile_start[kMaxGroups + 2 + g] - group_tile_start[kMaxGroups + 1 + g];
-          run += (max(rows, 0) + Cfg::kTileM - 1) / Cfg::kTileM;
+          run += (max(rows, 0) + unit - 1) / unit;
         }
         group_tile_start[p.groups] = run;
       }
@@ -387,7 +408,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t which = warp == 0 ? 0u : 1u;
       uint32_t g = 0;   // K blocks seen so far, over all of this CTA's tiles
       bool ok = true;
-      PROBE_DECL_IF(which == 0 && lane == 0)
       Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
       Tile t;
       for (; ok && walk.get(t); walk.next(t)) {
@@ -400,45 +420,37 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const int n0 = kEpi == kEpiBf16GroupedGlu
                            ? t.tile_n * (kTileN / 2) + static_cast<int>(cta_rank) * p.glu_cols
                            : t.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
-        const int a_batch = kSched == kSchedGrouped ? 0 : t.batch;   // grouped A is one [rows, K] matrix
+        const int a_batch = sched_is_grouped(kSched) ? 0 : t.batch;   // grouped A is one [rows, K] matrix
+        const int b_batch = kSched == kSchedGroupedWgrad ? 0 : t.batch;   // and so is a weight gradient's B
         for (int kb = t.kb_begin; kb < t.kb_begin + t.kb_count; ++kb, ++g) {
           if ((g & 1u) != which) continue;
           const uint32_t stage = g % Cfg::kStages;
           const uint32_t phase = (g / Cfg::kStages) & 1u;
           ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, p.status, kDevTimeoutProducer, abort_flag));
           if (!ok) break;
-          PROBE_ADD(0);
           // Both CTAs of a pair complete their bytes on the leader's barrier.
           const uint32_t fb = kCtaGroup == 2 ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
           const uint32_t a_dst = ring + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kABytes;
-          const int k0 = kb * kBlockK;
+          const int k0 = t.k0 + (kb - t.kb_begin) * kBlockK;
           if (elect_one()) {
-#ifdef B200_PROBE
-            if (p.probe_skip_loads) {
-              if (cta_rank == 0) mbar_arrive(full_bar(stage));
-            } else
-#endif
-            {
-              if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
-              if (!p.a_mn) {
-                tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, a_batch);
-              } else {
+            if (cta_rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCtaGroup);
+            if (!p.a_mn) {
+              tma_load_3d<kCtaGroup>(a_dst, &p.map_a, fb, k0, m0, a_batch);
+            } else {
 #pragma unroll
-                for (int i = 0; i < kTileMCta / 64; ++i)
-                  tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
-              }
-              if (!p.b_mn) {
-                tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, t.batch);
-              } else {
+              for (int i = 0; i < kTileMCta / 64; ++i)
+                tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
+            }
+            if (!p.b_mn) {
+              tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, b_batch);
+            } else {
 #pragma unroll
-                for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
-                  tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, t.batch);
-              }
+              for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
+                tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, b_batch);
             }
           }
           __syncwarp();
-          PROBE_ADD(1);
         }
       }
     }
@@ -462,7 +474,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
-      PROBE_DECL_IF(lane == 0)
       Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
       Tile t;
       for (; ok && walk.get(t); walk.next(t), ++it) {
@@ -470,14 +481,35 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t acc_phase = (it >> 1) & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag));
         if (!ok) break;
-        PROBE_ADD(2);
         tcgen05_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kTileN;
         for (int kb = 0; kb < t.kb_count; ++kb) {
           ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag));
           if (!ok) break;
-          PROBE_ADD(3);
           tcgen05_fence_after_sync();
+          if constexpr (kSched == kSchedGroupedWgrad) {
+            // The last K block of a group runs past the group's end: the copy engine clips
+            // only at the end of the whole array, so rows k_tail..63 of this stage hold the
+            // NEXT group's rows.  A product is unaffected by garbage in one operand where the
+            // other is zero, so those rows of A alone are zeroed, in this CTA's stage and in
+            // the peer's, before the tensor cores read them.  An MN-major stage keeps one K row
+            // per 128-byte line of each 64-column subtile, so this is whole lines.
+            if (kb == t.kb_count - 1 && t.k_tail < kBlockK) {
+              const uint32_t a_stage = ring + stage * Cfg::kStageBytes;
+              const int lines = kBlockK - t.k_tail;                 // per subtile
+              const int chunks = lines * 8;                          // 16-byte pieces per subtile
+              for (int c = lane; c < chunks * (kTileMCta / 64) * kCtaGroup; c += 32) {
+                const int cta = c / (chunks * (kTileMCta / 64));
+                const int rest = c - cta * chunks * (kTileMCta / 64);
+                const int sub = rest / chunks;
+                const uint32_t off = a_stage + sub * kSubtileBytes + t.k_tail * 128 + (rest - sub * chunks) * 16;
+                if (cta == 0) st_shared_zero16(off);
+                else st_shared_cluster_zero16(map_to_cta(off, 1));
+              }
+              fence_proxy_async_all();
+              __syncwarp();
+            }
+          }
           const uint64_t da = a_desc0 + stage * kStageAdd;
           const uint64_t db = b_desc0 + stage * kStageAdd;
           if (elect_one()) {
@@ -489,7 +521,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           }
           __syncwarp();
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
-          PROBE_ADD(4);
         }
         if (ok && elect_one()) umma_commit<kCtaGroup>(tmem_full_bar(acc));   // accumulator ready for the epilogue
         __syncwarp();
@@ -553,7 +584,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     float run_max = -INFINITY, run_sum = 0.f, target_logit = 0.f;
     bool have_target = false;
     constexpr float kLog2e = 1.4426950408889634f;
-    PROBE_DECL_IF(warp == 2 && lane == 0)
     Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
     Tile t;
     for (; ok && walk.get(t); walk.next(t), ++it) {
@@ -563,7 +593,6 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         ok = false;
         break;
       }
-      PROBE_ADD(5);
       tcgen05_fence_after_sync();
       const int row0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta + lane_base;   // warp's first row
       const int col0 = t.tile_n * (kEpi == kEpiBf16GroupedGlu ? kTileN / 2 : kTileN);
@@ -603,21 +632,17 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           tmem_ld_32x32(t_acc + c * 32, r);
           tmem_ld_wait();
           if (c == kChunks - 1) release_accumulator();
-          PROBE_ADD(6);
           const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
           if (lane == 0) tma_wait_group_read<1>();   // the store that last read this buffer is done
           __syncwarp();
-          PROBE_ADD(7);
           stage_row(buf, r);
           fence_proxy_async_smem();
           __syncwarp();
-          PROBE_ADD(8);
           if (lane == 0) {
             if (kEpi == kEpiF32Tma && p.reduce) tma_reduce_add_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
             else tma_store_3d(&p.map_c, buf, col0 + c * 32, row0, t.batch);
             tma_commit_group();
           }
-          PROBE_ADD(9);
           ++chunk_counter;
           if constexpr (kEpi == kEpiF32DualBf16) {
 #pragma unroll
@@ -668,7 +693,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_3d(map, buf, col, row0, kSched == kSchedGrouped ? 0 : t.batch);
+              tma_store_3d(map, buf, col, row0, sched_is_grouped(kSched) ? 0 : t.batch);
               tma_commit_group();
             }
             ++chunk_counter;
@@ -725,11 +750,22 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               put_chunk(&p.map_d, p.d_bf16, p.ldd, p.glu_cols + col, 2 * p.glu_cols, pu);
             }
           } else {
+          // kEpiBf16Grouped with a second output: the values before the activation, which the
+          // activation's backward reads.
+          [[maybe_unused]] uint32_t before[32];
+          const bool keep_before = kEpi == kEpiBf16Grouped && p.d_bf16 != nullptr;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * 64 + h * 32, r);
             tmem_ld_wait();
+            if constexpr (kEpi == kEpiBf16Grouped) {
+              if (keep_before) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  before[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+              }
+            }
             if constexpr (kEpi == kEpiCeBackward) {
               // scale * exp(logit - lse) = exp2(logit*log2e + (log2(scale) - lse*log2e)): one
               // FMA and one ex2 per element; the target and the padding mask are
@@ -770,6 +806,9 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           }
           if (c == kChunks - 1) release_accumulator();
           put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
+          if constexpr (kEpi == kEpiBf16Grouped) {
+            if (keep_before) put_chunk(&p.map_d, p.d_bf16, p.ldd, col0 + c * 64, p.n, before);
+          }
           }
         }
       } else if constexpr (kEpi == kEpiCeForward) {

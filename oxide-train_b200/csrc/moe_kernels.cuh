@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
   const long long vecs = d / 8;
   for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
     const uint32_t my_row = lane < top_k ? dest_row[token * top_k + lane] : kMoeDropped;
-    const float my_gate = lane < top_k ? gates[token * top_k + lane] : 0.f;
+    const float my_gate = lane < top_k ? (gates ? gates[token * top_k + lane] : 1.f) : 0.f;
     uint32_t rows[kMoeMaxTopK];
     float gs[kMoeMaxTopK];
 #pragma unroll
@@ -324,6 +324,247 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
         o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
         o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
       }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ backward of the expert path
+// (crates/nn/src/moe.rs:354-445 MoeFfn::backward; crates/nn/src/swiglu.rs:30-47)
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[2 * j] = __uint_as_float(w[j] << 16);
+    f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(const float (&f)[8]) {
+  uint4 o;
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ow[j]) : "f"(f[2 * j + 1]), "f"(f[2 * j]));
+  return o;
+}
+
+// Backward of the combine (moe.rs:360-381): for every accepted (token, rank) pair
+//   dy_permuted[dest_row, :] = gate * dy[token, :]                      (bf16)
+//   gate_grad[pair]          = sum_d y_permuted[dest_row, d] * dy[token, d]   (0 for a dropped pair)
+// One warp per token; dy is read once.  `y_permuted` / `gate_grad` may be null together.
+template <bool kDyBf16>
+__global__ void __launch_bounds__(256) moe_combine_backward_kernel(
+    const void* __restrict__ dy, const uint16_t* __restrict__ y_permuted, const uint32_t* __restrict__ dest_row,
+    const float* __restrict__ gates, long long tokens, int top_k, long long d,
+    uint16_t* __restrict__ dy_permuted, float* __restrict__ gate_grad) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long vecs = d / 8;
+  for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
+    const uint32_t my_row = lane < top_k ? dest_row[token * top_k + lane] : kMoeDropped;
+    const float my_gate = lane < top_k ? gates[token * top_k + lane] : 0.f;
+    float dots[kMoeMaxTopK];
+#pragma unroll
+    for (int r = 0; r < kMoeMaxTopK; ++r) dots[r] = 0.f;
+    for (long long v = lane; v < vecs; v += 32) {
+      float g[8];
+      if (kDyBf16) {
+        unpack_bf16x8(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(dy) + token * d)[v], g);
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(dy) + token * d) + 2 * v;
+        const float4 lo = src[0], hi = src[1];
+        g[0] = lo.x; g[1] = lo.y; g[2] = lo.z; g[3] = lo.w;
+        g[4] = hi.x; g[5] = hi.y; g[6] = hi.z; g[7] = hi.w;
+      }
+#pragma unroll
+      for (int r = 0; r < kMoeMaxTopK; ++r) {
+        if (r >= top_k) break;
+        const uint32_t row = __shfl_sync(0xffffffffu, my_row, r);
+        const float gate = __shfl_sync(0xffffffffu, my_gate, r);
+        if (row == kMoeDropped) continue;
+        float scaled[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) scaled[j] = __fmul_rn(gate, g[j]);
+        reinterpret_cast<uint4*>(dy_permuted + static_cast<long long>(row) * d)[v] = pack_bf16x8(scaled);
+        if (gate_grad) {
+          float y[8];
+          unpack_bf16x8(reinterpret_cast<const uint4*>(y_permuted + static_cast<long long>(row) * d)[v], y);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dots[r] = fmaf(y[j], g[j], dots[r]);
+        }
+      }
+    }
+    if (gate_grad) {
+#pragma unroll
+      for (int r = 0; r < kMoeMaxTopK; ++r) {
+        if (r >= top_k) break;
+        float sum = dots[r];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (lane == 0) gate_grad[token * top_k + r] = sum;
+      }
+    }
+  }
+}
+
+// Backward of the expert's activation, elementwise over the routed rows.
+//   kGlu == false (SiLU, y = silu(a)):        d_a = d_y * s * (1 + a * (1 - s)),  s = sigmoid(a)
+//   kGlu == true  (SwiGLU, y = silu(g) * u):  d_g = d_y * u * s * (1 + g * (1 - s)),  d_u = d_y * g * s
+//     with `saved` and `d_saved` the [rows, 2, ff] gate/up panel and its gradient
+//     (gpu/ops/src/lib.rs:1453 swiglu_backward_interleaved_packed).
+// All operands bf16; eight elements per thread per step; ff a multiple of 8.  Row strides in elements.
+template <bool kGlu>
+__global__ void __launch_bounds__(256) activation_backward_kernel(
+    const uint16_t* __restrict__ saved, long long ld_saved, const uint16_t* __restrict__ d_y, long long ld_dy,
+    long long rows, long long ff, uint16_t* __restrict__ d_saved, long long ld_dsaved) {
+  const long long vecs_per_row = ff / 8;
+  const long long total = rows * vecs_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long row = i / vecs_per_row, v = i - row * vecs_per_row;
+    float g[8], u[8], dy[8], dg[8], du[8];
+    unpack_bf16x8(reinterpret_cast<const uint4*>(saved + row * ld_saved)[v], g);
+    if (kGlu) unpack_bf16x8(reinterpret_cast<const uint4*>(saved + row * ld_saved + ff)[v], u);
+    unpack_bf16x8(reinterpret_cast<const uint4*>(d_y + row * ld_dy)[v], dy);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + expf(-g[j]));
+      const float dsilu = s * (1.f + g[j] * (1.f - s));
+      if (kGlu) {
+        dg[j] = dy[j] * u[j] * dsilu;
+        du[j] = dy[j] * (g[j] * s);
+      } else {
+        dg[j] = dy[j] * dsilu;
+      }
+    }
+    reinterpret_cast<uint4*>(d_saved + row * ld_dsaved)[v] = pack_bf16x8(dg);
+    if (kGlu) reinterpret_cast<uint4*>(d_saved + row * ld_dsaved + ff)[v] = pack_bf16x8(du);
+  }
+}
+
+// Backward of the routing (moe.rs:397-445): from the gradients of the combine weights to the
+// gradient of the router's logits.  One warp per token.
+//   weighted = sum_r gate_grad[r] * gate[r]          (f64)
+//   psum     = sum_r probs[selected_r]               (f64)
+//   dprob[selected_r] += (gate_grad[r] - weighted) / psum
+//   dprob[e] += aux_coefficient * experts * fraction[e] / tokens,  fraction[e] = assignment_counts[e] / (tokens * top_k)
+//   dlogits[e] = probs[e] * (dprob[e] - sum_e' probs[e'] * dprob[e'])
+__global__ void __launch_bounds__(256) moe_route_backward_kernel(
+    const float* __restrict__ probs, const uint32_t* __restrict__ selected, const float* __restrict__ gates,
+    const float* __restrict__ gate_grad, const uint32_t* __restrict__ assignment_counts, float aux_coefficient,
+    long long tokens, int experts, int top_k, float* __restrict__ dlogits) {
+  const int lane = threadIdx.x & 31;
+  const long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (token >= tokens) return;
+  const float* prow = probs + token * experts;
+  constexpr int kPerLane = kMoeMaxExperts / 32;
+  float p[kPerLane], dp[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    p[i] = e < experts ? prow[e] : 0.f;
+    const float fraction = e < experts ? static_cast<float>(assignment_counts[e]) / static_cast<float>(tokens * top_k) : 0.f;
+    dp[i] = e < experts ? aux_coefficient * static_cast<float>(experts) * fraction / static_cast<float>(tokens) : 0.f;
+  }
+  // lane r holds pair r
+  const uint32_t my_e = lane < top_k ? selected[token * top_k + lane] : 0u;
+  const float my_gg = lane < top_k ? gate_grad[token * top_k + lane] : 0.f;
+  const float my_gate = lane < top_k ? gates[token * top_k + lane] : 0.f;
+  double weighted = 0.0, psum = 0.0;
+  for (int r = 0; r < top_k; ++r) {
+    const float gg = __shfl_sync(0xffffffffu, my_gg, r);
+    const float gt = __shfl_sync(0xffffffffu, my_gate, r);
+    const uint32_t e = __shfl_sync(0xffffffffu, my_e, r);
+    weighted += static_cast<double>(gg) * static_cast<double>(gt);
+    psum += static_cast<double>(prow[e]);
+  }
+  const float wf = static_cast<float>(weighted), pf = static_cast<float>(psum);
+  // The routing term is added first and the auxiliary term on top of it, as the reference does.
+  float routed[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) routed[i] = 0.f;
+  for (int r = 0; r < top_k; ++r) {
+    const float gg = __shfl_sync(0xffffffffu, my_gg, r);
+    const uint32_t e = __shfl_sync(0xffffffffu, my_e, r);
+    if ((e & 31u) == static_cast<uint32_t>(lane)) {
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i)
+        if (i == static_cast<int>(e >> 5)) routed[i] += (gg - wf) / pf;
+    }
+  }
+  double dot = 0.0;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    dp[i] = routed[i] + dp[i];
+    dot += static_cast<double>(p[i]) * static_cast<double>(dp[i]);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+  const float df = static_cast<float>(dot);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    if (e < experts) dlogits[token * experts + e] = p[i] * (dp[i] - df);
+  }
+}
+
+// Router logits (gpu/ops/src/lib.rs:2319-2429 router_logits_bf16, which stops at 8 experts):
+// logits[tokens, experts] = x[tokens, d] (bf16) . w[d, experts] (fp32), fp32 arithmetic on
+// CUDA cores with products rounded and added in ascending k, i.e. the CPU router's
+// `Linear::forward` (crates/tensor-cpu/src/ops.rs:87-104) bit for bit, so the expert
+// selection downstream cannot differ from the reference's.  64-token x 64-expert tile per
+// block, 16-deep slices, 4 x 4 outputs per thread.
+__global__ void __launch_bounds__(256) router_logits_kernel(const uint16_t* __restrict__ x,
+                                                            const float* __restrict__ w, long long tokens,
+                                                            int d, int experts, float* __restrict__ logits) {
+  constexpr int kT = 64, kK = 16;
+  __shared__ float xs[kK][kT + 4];
+  __shared__ float ws[kK][kT + 4];
+  const int tid = threadIdx.x;
+  const long long row0 = static_cast<long long>(blockIdx.x) * kT;
+  const int col0 = blockIdx.y * kT;
+  const int tr = (tid / 16) * 4, tc = (tid % 16) * 4;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < d; k0 += kK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      {
+        const int kk = idx % kK, r = idx / kK;
+        const long long gr = row0 + r;
+        const int gk = k0 + kk;
+        xs[kk][r] = (gr < tokens && gk < d) ? __uint_as_float(static_cast<uint32_t>(x[gr * d + gk]) << 16) : 0.f;
+      }
+      {
+        const int cc = idx % kT, kk = idx / kT;
+        const int gc = col0 + cc, gk = k0 + kk;
+        ws[kk][cc] = (gc < experts && gk < d) ? w[static_cast<size_t>(gk) * experts + gc] : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kK; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = xs[kk][tr + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = ws[kk][tc + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(av[i], bv[j]));
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long gr = row0 + tr + i;
+    if (gr >= tokens) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gc = col0 + tc + j;
+      if (gc < experts) logits[gr * experts + gc] = acc[i][j];
     }
   }
 }

@@ -16,7 +16,9 @@ enum DeviceStatus : int {
   kDevTimeoutMma = 102,        // MMA issuer waited too long for operands / a free accumulator
   kDevTimeoutEpilogue = 103,   // epilogue waited too long for a finished accumulator
   kDevTimeoutDrain = 104,      // teardown waited too long for outstanding work
+  kDevInboxOverflow = 105,     // expert-parallel exchange: a row fell outside the owner's buffer
   kDevTimeoutSchedule = 106,   // a role waited too long for its next tile from the tile scheduler
+  kDevBadTarget = 107,         // cross-entropy: a target index outside [0, classes)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -76,6 +78,15 @@ __device__ __forceinline__ void st_shared_u64(uint32_t smem_addr, unsigned long 
 
 __device__ __forceinline__ void st_shared_cluster_u64(uint32_t cluster_addr, unsigned long long v) {
   asm volatile("st.volatile.shared::cluster.b64 [%0], %1;" ::"r"(cluster_addr), "l"(v) : "memory");
+}
+
+// Sixteen zero bytes into this CTA's shared memory / the peer CTA's (address from map_to_cta).
+__device__ __forceinline__ void st_shared_zero16(uint32_t smem_addr) {
+  asm volatile("st.shared::cta.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem_addr), "r"(0u) : "memory");
+}
+
+__device__ __forceinline__ void st_shared_cluster_zero16(uint32_t cluster_addr) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(cluster_addr), "r"(0u) : "memory");
 }
 
 // ------------------------------------------------------------------ mbarrier
@@ -210,6 +221,13 @@ __device__ __forceinline__ void tma_wait_group() {
 // Make generic-proxy writes to shared memory visible to the async proxy (TMA).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// The same for every state space: after plain stores into the shared memory of another CTA of
+// the cluster (and this CTA's), before tensor-core instructions of this thread read them.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async;" ::: "memory");
 }
 
 // ------------------------------------------------------------------ tcgen05

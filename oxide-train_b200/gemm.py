@@ -40,6 +40,7 @@ class Tcgen05Gemm:
         with torch.cuda.device(self.device):
             L.check(self._lib.b200gemm_create(self.device, C.byref(h)))
         self._h = h
+        self.sm_limit = 0          # 0 = every SM; what set_sm_limit was last given
 
     @classmethod
     def load(cls, device: int | None = None) -> "Tcgen05Gemm":
@@ -119,6 +120,7 @@ class Tcgen05Gemm:
     def set_sm_limit(self, sms: int = 0) -> None:
         """Keep the persistent kernels on at most ``sms`` SMs (0 = all of them)."""
         L.check(self._lib.b200gemm_set_sm_limit(self._h, int(sms)))
+        self.sm_limit = int(sms)
 
     def set_scheduler(self, dynamic: bool) -> None:
         """Tiles from a device-side counter (``True``) or the fixed round-robin walk (``False``)."""

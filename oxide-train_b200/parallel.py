@@ -48,13 +48,28 @@ class DeviceOps:
         need = self.gemm._lib.b200gemm_lmhead_ce_workspace_bytes(m)
         if getattr(self, "_ws", None) is None or self._ws.numel() < need:
             self._ws = torch.empty(need, dtype=torch.uint8, device=dev)
-        out = [torch.empty(m, dtype=torch.float32, device=dev) for _ in range(3)]
+        # one [3, m] block (row_max, row_sum, row_target_logit): what the ranks all-gather
+        out = torch.empty((3, m), dtype=torch.float32, device=dev)
         L.check(self.gemm._lib.b200gemm_lmhead_ce_forward_shard(
             self.gemm._h, _stream_ptr(), hidden.data_ptr(), weight_shard.data_ptr(),
             L.MN_MAJOR if w_layout == "in_out" else L.K_MAJOR, local_targets.data_ptr(), m, k, v_local,
             classes_local, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(),
             self._ws.data_ptr(), self._ws.numel()))
-        return tuple(out)
+        return out
+
+    def head_merge_shards(self, gathered):
+        """``gathered`` is ``[world, 3, m]``: returns ``(lse, row_loss, loss)`` from one launch."""
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        world, _, m = gathered.shape
+        dev = gathered.device
+        lse = torch.empty(m, dtype=torch.float32, device=dev)
+        row_loss = torch.empty(m, dtype=torch.float32, device=dev)
+        loss = torch.empty(1, dtype=torch.float32, device=dev)
+        L.check(self.gemm._lib.b200gemm_lmhead_ce_merge_shards(
+            self.gemm._h, _stream_ptr(), gathered.data_ptr(), world, m, lse.data_ptr(), row_loss.data_ptr(),
+            loss.data_ptr()))
+        return lse, row_loss, loss
 
     def head_backward_shard(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy,
                             d_weight, accumulate_dw):
@@ -206,12 +221,14 @@ class _ReservedSms:
     def __enter__(self):
         if self.gemm is not None:
             total = torch.cuda.get_device_properties(self.gemm.device).multi_processor_count
-            self.gemm.set_sm_limit(max(2, total - self.sms))
+            self.before = self.gemm.sm_limit            # a limit the caller set outlives this block
+            in_force = self.before or total
+            self.gemm.set_sm_limit(max(2, min(in_force, total - self.sms)))
         return self
 
     def __exit__(self, *exc):
         if self.gemm is not None:
-            self.gemm.set_sm_limit(0)
+            self.gemm.set_sm_limit(self.before)
         return False
 
 
@@ -254,6 +271,7 @@ class VocabParallelHead:
         self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
         self._side = None
+        self._lt = None
 
     def shard_weight(self, weight_full):
         """This rank's columns of a full ``[hidden, vocab_padded]`` weight (a copy)."""
@@ -262,12 +280,27 @@ class VocabParallelHead:
         return weight_full[self.c0:self.c1].contiguous()
 
     def local_targets(self, targets):
-        return (targets - self.c0).to(torch.int32)
+        """Targets relative to this shard's first column; kept from the forward for the backward
+        of the same batch."""
+        cached = self._lt
+        if cached is not None and cached[0] is targets and cached[1] == targets._version:
+            return cached[2]
+        lt = (targets - self.c0).to(torch.int32)
+        self._lt = (targets, targets._version, lt)
+        return lt
 
     def forward(self, hidden, weight_shard, targets):
         lt = self.local_targets(targets)
         stats = self.ops.head_forward_shard(hidden, weight_shard, lt, self.classes_local, self.w_layout)
-        lse, row_loss, loss = merge_softmax_stats(*stats, group=self.group)
+        if hasattr(self.ops, "head_merge_shards") and hidden.device.type == "cuda":
+            # ONE collective (an all-gather of every rank's [3, rows] block, 384 KB per rank at
+            # 32768 rows) and ONE kernel, instead of a MAX all-reduce, a SUM all-reduce and the
+            # elementwise passes between them.
+            gathered = torch.empty((self.world,) + tuple(stats.shape), dtype=stats.dtype, device=stats.device)
+            dist.all_gather_into_tensor(gathered, stats, group=self.group)
+            lse, row_loss, loss = self.ops.head_merge_shards(gathered)
+        else:
+            lse, row_loss, loss = merge_softmax_stats(*stats, group=self.group)
         return loss, lse, row_loss
 
     def backward(self, hidden, weight_shard, targets, lse, dy: float = 1.0, d_weight=None,

@@ -40,7 +40,7 @@ def test_library_loads_on_cpu_and_exports_every_declared_symbol(pkg):
     assert lib.b200gemm_last_error_string() is not None
 
 
-def test_descriptor_struct_matches_the_c_layout(pkg):
+def test_descriptor_struct_matches_the_c_layout(pkg, tmp_path):
     # b200gemm_desc_t: 3 pointers, 6 int64, 6 int32, 3 int64, 2 uint32 = 112 bytes, no padding surprises
     assert C.sizeof(pkg.GemmDesc) == 3 * 8 + 6 * 8 + 6 * 4 + 3 * 8 + 2 * 4
     probe = r'''
@@ -53,17 +53,11 @@ def test_descriptor_struct_matches_the_c_layout(pkg):
       return 0;
     }'''
     gcc = shutil.which("gcc") or "/usr/bin/gcc"
-    tmp = os.path.join(ROOT, "tests", "_abi_probe")
-    try:
-        with open(tmp + ".c", "w") as f:
-            f.write(probe)
-        env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
-        subprocess.check_call([gcc, "-I", os.path.join(ROOT, "include"), tmp + ".c", "-o", tmp], env=env)
-        size, off_layout, off_bsa, off_flags = map(int, subprocess.check_output([tmp]).split())
-    finally:
-        for ext in (".c", ""):
-            if os.path.exists(tmp + ext):
-                os.remove(tmp + ext)
+    src, exe = tmp_path / "abi_probe.c", tmp_path / "abi_probe"
+    src.write_text(probe)
+    env = {k: v for k, v in os.environ.items() if k not in ("CC", "CXX")}
+    subprocess.check_call([gcc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], env=env)
+    size, off_layout, off_bsa, off_flags = map(int, subprocess.check_output([str(exe)]).split())
     D = pkg.GemmDesc
     assert size == C.sizeof(D)
     assert off_layout == D.a_layout.offset

@@ -334,3 +334,108 @@ def test_transpose_probe_encodings_in_every_storage_order(pkg, oracle, gemm, cg,
             got = c.cpu().numpy()
             assert np.all(np.abs(got - expected) <= atol + rtol * np.abs(expected)), (encoding, ta, tb)
     assert gemm.device_status() == 0
+
+
+# ---- the weight-gradient methods the reference gates at 256^3 (gpu/gemm/src/main.rs:343-391,
+# ---- 515-620; gpu/gemm/src/host.rs:837-1026), plus one ragged shape each -----------------
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (200, 328, 456)])
+def test_bf16_accumulate_transposed(pkg, oracle, gemm, cg, m, n, k):
+    """``accumulate_transposed`` (host.rs:875-900): bf16 ``C += A^T.B``, both operands MN-major --
+    the reference's lm-head weight-gradient form (gpu/model/src/lib.rs:3103-3123)."""
+    a, av = bf16_operand(oracle, (k, m), 81)
+    b, bv = bf16_operand(oracle, (k, n), 82, std=0.05)
+    c0, c0v = bf16_operand(oracle, (m + 8, n), 83)                  # canary rows at the end
+    ref = oracle.matmul_tn(av, bv, THREADS)
+    gemm.accumulate_transposed(a, b, c0[:m], flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    got = from_dev_bf16(c0)
+    assert np.array_equal(got[m:], c0v[m:])
+    # one rounding of (old + product): half a bf16 ulp of the sum
+    assert_gemm_close(got[:m], c0v[:m] + ref, "bf16 accumulate_transposed", rel_fro=4e-3, elem=8e-3)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (192, 264, 328)])
+def test_f32_accumulate_transposed_batched(pkg, oracle, gemm, cg, m, n, k):
+    """``f32_accumulate_transposed_batched`` (host.rs:997-1026): the reference's expert
+    weight-gradient form, one launch over the experts' capacity bins."""
+    import torch
+    E = 3
+    a, av = bf16_operand(oracle, (E, k, m), 84)
+    b, bv = bf16_operand(oracle, (E, k, n), 85, std=0.05)
+    c0 = oracle.normal(E * m * n, 86).reshape(E, m, n)
+    ref = np.stack([oracle.matmul_tn(av[e], bv[e], THREADS) for e in range(E)])
+    c = torch.from_numpy(c0).cuda()
+    gemm.f32_accumulate_transposed_batched(a, b, c, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    assert_gemm_close(c.cpu().numpy(), c0 + ref, "f32_accumulate_transposed_batched", rel_fro=2e-5, elem=2e-4)
+    # dead capacity rows (zero-filled bins, gpu/model/src/lib.rs:1717-1748) add exactly nothing
+    a2 = a.clone()
+    a2[:, k // 2:] = 0
+    c2 = torch.zeros((E, m, n), dtype=torch.float32, device="cuda")
+    gemm.f32_accumulate_transposed_batched(a2, b, c2, flags=_flags(pkg, cg))
+    half = np.stack([oracle.matmul_tn(av[e][:k // 2], bv[e][:k // 2], THREADS) for e in range(E)])
+    assert_gemm_close(c2.cpu().numpy(), half, "dead bin rows", rel_fro=2e-5, elem=2e-4)
+
+
+@pytest.mark.parametrize("cg", CTA_GROUPS, ids=["cg1", "cg2"])
+def test_f32_accumulate_at_forms(pkg, oracle, gemm, cg):
+    """``f32_accumulate_at`` (host.rs:837-864) and ``f32_accumulate_transposed_at`` (host.rs:914-941):
+    add into a region of a larger buffer; the neighbours keep their values."""
+    import torch
+    M, N, K = 256, 256, 192
+    a, av = bf16_operand(oracle, (M, K), 87)
+    b, bv = bf16_operand(oracle, (N, K), 88, std=0.05)
+    base = oracle.normal(3 * M * N, 89).astype(np.float32)
+    buf = torch.from_numpy(base.copy()).cuda()
+    gemm.f32_accumulate_at(a, b, buf, M * N, M * N, N, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    host = buf.cpu().numpy()
+    assert np.array_equal(host[:M * N], base[:M * N]) and np.array_equal(host[2 * M * N:], base[2 * M * N:])
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    assert_gemm_close(host[M * N:2 * M * N].reshape(M, N), base[M * N:2 * M * N].reshape(M, N) + ref,
+                      "f32_accumulate_at", rel_fro=2e-5, elem=2e-4)
+    at, atv = bf16_operand(oracle, (K, M), 90)
+    bt, btv = bf16_operand(oracle, (K, N), 91, std=0.05)
+    buf = torch.from_numpy(base.copy()).cuda()
+    gemm.f32_accumulate_transposed_at(at, bt, buf, 2 * M * N, M * N, N, flags=_flags(pkg, cg))
+    assert gemm.device_status() == 0
+    host = buf.cpu().numpy()
+    assert np.array_equal(host[:2 * M * N], base[:2 * M * N])
+    assert_gemm_close(host[2 * M * N:].reshape(M, N), base[2 * M * N:].reshape(M, N) + oracle.matmul_tn(atv, btv, THREADS),
+                      "f32_accumulate_transposed_at", rel_fro=2e-5, elem=2e-4)
+
+
+def test_host_buffer_form_leaves_the_callers_padding_alone(pkg, oracle, gemm):
+    """b200gemm_gemm_host with C a column slice of a wider host matrix (ldc > n) and A, B with
+    padded rows: only the matrices' own elements are read or written; the canary columns of
+    the caller's buffers survive, in store and in accumulate mode."""
+    import ctypes as C
+    L = pkg._lib
+    M, N, K, LDA, LDB, LDC = 200, 136, 72, 96, 80, 3 * 136
+    a_full = np.full((M, LDA), 0x7FC0, np.uint16)                       # NaN canaries in the padding
+    b_full = np.full((N, LDB), 0x7FC0, np.uint16)
+    av = oracle.bf16_round(oracle.uniform(M * K, 92)).reshape(M, K)
+    bv = oracle.bf16_round(oracle.uniform(N * K, 93)).reshape(N, K)
+    a_full[:, :K] = oracle.bf16_bits(av).reshape(M, K)
+    b_full[:, :K] = oracle.bf16_bits(bv).reshape(N, K)
+    # The last row is shortened to its K real elements: reading a whole padded row there would run off the buffer.
+    a_buf = np.ascontiguousarray(a_full.reshape(-1)[: (M - 1) * LDA + K])
+    b_buf = np.ascontiguousarray(b_full.reshape(-1)[: (N - 1) * LDB + K])
+    wide = np.full((M, LDC), -7.0, np.float32)
+    d = L.GemmDesc()
+    d.a, d.b = a_buf.ctypes.data, b_buf.ctypes.data
+    d.c = wide.ctypes.data + N * 4                                        # the middle column block
+    d.m, d.n, d.k, d.lda, d.ldb, d.ldc = M, N, K, LDA, LDB, LDC
+    d.out_type, d.mode, d.batch = L.OUT_F32, L.STORE, 1
+    L.check(gemm._lib.b200gemm_gemm_host(gemm._h, None, C.byref(d)))
+    ref = oracle.matmul_nt(av, bv, THREADS)
+    assert np.all(wide[:, :N] == -7.0) and np.all(wide[:, 2 * N:] == -7.0)
+    assert_gemm_close(wide[:, N:2 * N], ref, "host store into a column slice", rel_fro=2e-5, elem=2e-4)
+    d.mode = L.ACCUMULATE
+    L.check(gemm._lib.b200gemm_gemm_host(gemm._h, None, C.byref(d)))
+    assert np.all(wide[:, :N] == -7.0) and np.all(wide[:, 2 * N:] == -7.0)
+    assert_gemm_close(wide[:, N:2 * N], 2 * ref, "host accumulate into a column slice", rel_fro=2e-5, elem=2e-4)
+    assert gemm.device_status() == 0

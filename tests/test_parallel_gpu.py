@@ -1,6 +1,8 @@
-"""The sharded paths on real GPUs: 2 ranks over NCCL, compared with the same
-computation done by the single-GPU kernels on each rank.  Needs two GPUs; skips
-itself otherwise.  Child processes, NVLS off, ranks leave only between steps."""
+"""The sharded paths on real GPUs: 2 ranks over NCCL, compared with the CPU oracle (whole
+matrices for the head, sampled rows for the expert and MLP paths) and with the same
+computation done by the single-GPU kernels on each rank.  Needs two GPUs; skips itself
+otherwise (the shard arithmetic itself is also covered on one GPU, ranks emulated, in the
+lm-head and MoE-exchange tests).  Child processes, NVLS off, ranks leave only between steps."""
 import os
 import socket
 import sys
@@ -30,6 +32,9 @@ def _worker(rank, port, failures):
         dist.init_process_group("nccl", rank=rank, world_size=WORLD, device_id=dev)
         import __graft_entry__ as entry
         pkg = entry.load_package()
+        import numpy as np
+        from oracle import oracle as orc
+        orc.lib()
         par = pkg.parallel
         gemm = pkg.Tcgen05Gemm(rank)
         ops = par.DeviceOps(gemm)
@@ -58,6 +63,20 @@ def _worker(rank, port, failures):
         _, dh3, _ = head32.backward(h, ws, t, lse2)
         assert torch.allclose(dh1, dh3, atol=2e-5, rtol=2e-2), float((dh1 - dh3).abs().max())
         assert torch.allclose(dw1[:, head.c0:head.c1], dw2, atol=2e-5, rtol=2e-2)
+        # ... and against the oracle: Linear::forward + SoftmaxCrossEntropy + Linear::backward on the CPU
+        hv, wv, tv = h.float().cpu().numpy(), w.float().cpu().numpy(), t.cpu().numpy()
+        o_logits = orc.matmul(hv, wv, 8)
+        o_loss, o_probs, o_rows = orc.xent_forward(o_logits, tv, classes)
+        o_dl = orc.xent_backward(o_probs, tv, classes)
+        assert abs(float(loss2.item()) - float(o_loss)) <= 5e-5 * max(1.0, abs(float(o_loss)))
+        assert np.allclose(row2.cpu().numpy(), o_rows, atol=2e-4, rtol=1e-5)
+        o_dh = orc.matmul_nt(o_dl, wv, 8)
+        for name, got in (("bf16 partial sums", dh2), ("fp32 partial sums", dh3)):
+            rel = np.linalg.norm(got.cpu().numpy() - o_dh) / np.linalg.norm(o_dh)
+            assert rel <= 1e-2, (name, rel)
+        o_dw = orc.matmul_tn(hv, np.ascontiguousarray(o_dl[:, head.c0:head.c1]), 8)
+        rel = np.linalg.norm(dw2.cpu().numpy() - o_dw) / np.linalg.norm(o_dw)
+        assert rel <= 1e-2, ("d_weight shard", rel)
 
         # ---- expert-parallel MoE vs the single-GPU grouped path on this rank's tokens
         n_local, d, ff, experts, top_k = 512, 256, 384, 8, 2
@@ -72,6 +91,20 @@ def _worker(rank, port, failures):
                                    dn[rank * local:(rank + 1) * local].contiguous())
         out = ep.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
         assert torch.allclose(out, ref, atol=1e-5, rtol=1e-5), float((out - ref).abs().max())
+        # sampled tokens against the oracle: route on the CPU, each selected expert's
+        # down(silu(up(x))) with the bf16 roundings the kernels apply, gates in rank order
+        xr = x[rank].float().cpu().numpy()
+        probs = orc.softmax_rows(logits[rank].cpu().numpy())
+        want = orc.moe_route(probs, top_k, n_local * top_k)
+        upv, dnv = up.float().cpu().numpy(), dn.float().cpu().numpy()
+        for tok in (0, 17, n_local - 1):
+            acc = np.zeros(d, np.float32)
+            for rk in range(top_k):
+                e = int(want["selected"][tok * top_k + rk])
+                hdn = orc.bf16_round(orc.silu(orc.matmul(xr[tok:tok + 1], upv[e], 1)))
+                acc += want["gates"][tok * top_k + rk] * orc.bf16_round(orc.matmul(hdn, dnv[e], 1))[0]
+            got = out[tok].cpu().numpy()
+            assert np.max(np.abs(got - acc) / (1.0 + np.abs(acc))) <= 2e-2, tok
         # the same exchange by copy-engine pushes into peer memory, in two slices, twice in a row
         ep2 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
                                     dn[rank * local:(rank + 1) * local].contiguous(), pieces=2,
@@ -99,10 +132,14 @@ def _worker(rank, port, failures):
         mlp = par.TensorParallelMlp(ops, w1[:, cols].contiguous(), w2[cols].contiguous(), chunks=2,
                                     partial_dtype=torch.float32, reserve_sms=8)
         y = mlp.forward(x2)
-        hid = ops.linear(x2, w1)                               # bf16 hidden, as each shard rounds it
-        full = hid.float() @ w2.float()
-        rows = mlp.owned_rows(m).to(dev)
-        assert torch.allclose(y, full[rows], atol=2e-3, rtol=2e-2), float((y - full[rows]).abs().max())
+        # oracle on sampled rows: hidden = bf16(x W1) as each shard rounds it, y = hidden W2
+        rows = mlp.owned_rows(m)
+        pick = rows[[0, 1, len(rows) // 2, len(rows) - 1]]
+        hid = orc.bf16_round(orc.matmul(x2[pick].float().cpu().numpy(), w1.float().cpu().numpy(), 4))
+        full = orc.matmul(hid, w2.float().cpu().numpy(), 4)
+        got = y[[0, 1, len(rows) // 2, len(rows) - 1]].cpu().numpy()
+        assert np.max(np.abs(got - full) / (1.0 + np.abs(full))) <= 2e-2
+        assert np.linalg.norm(got - full) / np.linalg.norm(full) <= 1e-2
         assert gemm.device_status() == 0
         dist.barrier()
         torch.cuda.synchronize()

@@ -75,3 +75,55 @@ def test_noalloc_head_forward_matches_workspace_form_twice_in_a_row(pkg):
         assert b"32768" in lib.b200gemm_last_error_string()
     finally:
         gemm.close()
+
+
+def test_noalloc_head_forward_at_its_row_limit_allocates_nothing(pkg, oracle):
+    """m = 32768, the largest row count the built-in array holds (the only size that uses all
+    of it): sampled rows against the oracle, the whole result against the workspace form, and
+    the entry point's one promise -- the device's free memory is the same before and after a call."""
+    import torch
+    from _util import THREADS
+    torch.cuda.set_device(0)
+    gemm = pkg.Tcgen05Gemm(0)
+    lib, handle, L = gemm._lib, gemm._h, pkg._lib
+    stream = torch.cuda.current_stream().cuda_stream
+    m, k, v, classes = 32768, 256, 2048, 2000
+    try:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(9)
+        hidden = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+        weight = (torch.randn((k, v), generator=gen, device="cuda") * 0.2).to(torch.bfloat16)
+        targets = torch.randint(0, classes, (m,), generator=gen, device="cuda", dtype=torch.int32)
+        lse, row, loss = (torch.empty(m, dtype=torch.float32, device="cuda"),
+                          torch.empty(m, dtype=torch.float32, device="cuda"),
+                          torch.empty(1, dtype=torch.float32, device="cuda"))
+        args = (handle, stream, hidden.data_ptr(), weight.data_ptr(), L.MN_MAJOR, targets.data_ptr(), m, k, v,
+                classes, lse.data_ptr(), row.data_ptr(), loss.data_ptr())
+        L.check(lib.b200gemm_lmhead_ce_forward_noalloc(*args))          # first call: looks the array up
+        torch.cuda.synchronize()
+        first = (lse.clone(), row.clone(), float(loss.item()))
+        free_before, _ = torch.cuda.mem_get_info()
+        L.check(lib.b200gemm_lmhead_ce_forward_noalloc(*args))          # later calls only launch
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before, "the call changed the device's free memory"
+        assert torch.equal(lse, first[0]) and torch.equal(row, first[1])
+        assert abs(float(loss.item()) - first[2]) <= 1e-6 * abs(first[2])
+        assert gemm.device_status() == 0
+        rows = np.array([0, 255, 256, 4097, 16383, 20000, 32767])
+        logits = oracle.matmul(hidden[rows].float().cpu().numpy(), weight.float().cpu().numpy(), THREADS)
+        _, _, rl = oracle.xent_forward(logits, targets.cpu().numpy()[rows], classes)
+        assert np.allclose(row.cpu().numpy()[rows], rl, atol=5e-4, rtol=1e-5)
+        # the whole result against the entry point that takes a workspace
+        need = lib.b200gemm_lmhead_ce_workspace_bytes(m)
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        lse0, row0, loss0 = torch.empty_like(lse), torch.empty_like(row), torch.empty_like(loss)
+        L.check(lib.b200gemm_lmhead_ce_forward(handle, stream, hidden.data_ptr(), weight.data_ptr(), L.MN_MAJOR,
+                                               targets.data_ptr(), m, k, v, classes, lse0.data_ptr(),
+                                               row0.data_ptr(), loss0.data_ptr(), ws.data_ptr(), need))
+        torch.cuda.synchronize()
+        assert np.allclose(lse.cpu().numpy(), lse0.cpu().numpy(), rtol=1e-6, atol=1e-6)
+        assert np.allclose(row.cpu().numpy(), row0.cpu().numpy(), rtol=1e-6, atol=1e-6)
+        assert abs(float(loss.item()) - float(loss0.item())) <= 5e-5 * abs(float(loss0.item()))
+    finally:
+        gemm.close()
