@@ -31,7 +31,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# ---- the workload: BASELINE "configs[1]" -----------------------------------
+# ---- the workload: the full-step GEMM set of the ~183M dense model --------------
 M_TOKENS, D_MODEL, D_FF, N_LAYERS, VOCAB_PAD, VOCAB = 32768, 1536, 4096, 12, 50432, 50257
 PROJECTIONS = [("qkv", D_MODEL, 3 * D_MODEL), ("attn_out", D_MODEL, D_MODEL),
                ("mlp_up", D_MODEL, D_FF), ("mlp_down", D_FF, D_MODEL)]
@@ -155,8 +155,13 @@ def workload_config(n_gpus):
                         "B=32 T=1024 M=32768 D=1536 FF=4096 L=12, lm-head 1536->50432; "
                         "forward + input-gradient + weight-gradient layouts",
             "m_tokens": M_TOKENS, "d_model": D_MODEL, "d_ff": D_FF, "layers": N_LAYERS,
-            "vocab_padded": VOCAB_PAD, "parallelism": f"replicas x{n_gpus} (one token batch per GPU)",
-            "l2": "operands of successive launches differ and exceed the 126 MB L2"}
+            "vocab_padded": VOCAB_PAD,
+            "parallelism": f"replicas x{n_gpus} (one token batch per GPU, no data-path collective); the paths "
+                           "that do shard -- fused head, tensor-parallel MLP, expert-parallel MoE -- are "
+                           "timed at this N in the line's `sharded` block",
+            "l2": "no flush: one step touches about 8 GB of operands and outputs; the only operand shared by "
+                  "successive launches (the 100.7 MB token activations, read by three of a layer's four forward "
+                  "GEMMs) is followed by 201-604 MB of output writes that push most of it out of the 126 MB L2"}
 
 
 # ---- the GPU arm ----------------------------------------------------------------
@@ -216,6 +221,57 @@ def run_step(gemm, head, buf):
     return n
 
 
+class CublasLtComparator:
+    """cuBLASLt beside every row of the per-shape table, the way the reference builds its
+    denominator (gpu/gemm/src/cublaslt.rs:55-61, 434-470; gpu/gemm/src/bin/model_shapes.rs:425-441):
+    called directly, 32 MiB workspace, the heuristic's first algorithm, beta = 1 where the
+    kernel adds into C, and its C compared with this library's before its time is believed.
+    A separate shared library that only this column loads; never on the product path."""
+
+    def __init__(self):
+        path = os.path.join(ROOT, "oxide-train_b200", "comparator", "libcublaslt_compare.so")
+        self.lib, self.session = None, C.c_void_p()
+        if not os.path.exists(path):
+            return
+        lib = C.CDLL(path)
+        lib.cmp_last_error.restype = C.c_char_p
+        lib.cmp_create.argtypes = [C.POINTER(C.c_void_p)]
+        lib.cmp_plan.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int,
+                                 C.POINTER(C.c_void_p)]
+        lib.cmp_run.argtypes = [C.c_void_p] * 6
+        lib.cmp_plan_destroy.argtypes = [C.c_void_p]
+        lib.cmp_destroy.argtypes = [C.c_void_p]
+        if lib.cmp_create(C.byref(self.session)) == 0:
+            self.lib = lib
+
+    def plan(self, m, n, k, a_mn, b_mn, out_bf16, accumulate):
+        plan = C.c_void_p()
+        if self.lib is None or self.lib.cmp_plan(self.session, m, n, k, int(a_mn), int(b_mn), int(out_bf16),
+                                                 int(accumulate), C.byref(plan)) != 0:
+            return None
+        return plan
+
+    def run(self, plan, torch, a, b, c):
+        rc = self.lib.cmp_run(self.session, plan, torch.cuda.current_stream().cuda_stream, a.data_ptr(),
+                              b.data_ptr(), c.data_ptr())
+        if rc != 0:
+            raise RuntimeError(self.lib.cmp_last_error().decode())
+
+    @staticmethod
+    def agrees(torch, theirs, ours):
+        """The reference's check (model_shapes.rs:485-510): |d| <= max(|theirs|, 1) / 32 for fp32
+        results, 4/256 for bf16 ones -- loose, because the two sides add K in different orders;
+        a transposed operand or a wrong stride is wrong by whole values."""
+        tol = 1.0 / 32.0 if theirs.dtype == torch.float32 else 4.0 / 256.0
+        t, o = theirs.float(), ours.float()
+        return bool(((t - o).abs() <= tol * t.abs().clamp_min(1.0)).all().item())
+
+    def close(self):
+        if self.lib is not None:
+            self.lib.cmp_destroy(self.session)
+            self.lib = None
+
+
 def per_shape_table(torch, gemm, head, buf, iters=3):
     """TFLOP/s of every distinct GEMM of the step, timed alone (reported, not the headline).
 
@@ -238,91 +294,100 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
         ms = s.elapsed_time(e) / iters
         return ms, flops / ms / 1e9
 
-    # Comparator column: the same products through cuBLASLt (torch.mm, fp32 output like the
-    # rows they stand beside), timed the same way.  Reported only; not on the product path.
+    # Comparator column: the same products through cuBLASLt, same operands, same timing loop.
     f32 = torch.float32
+    cmp = CublasLtComparator()
 
-    def cublas(fn, flops):
-        try:
-            return round(timed(fn, flops)[1], 1)
-        except Exception:                                   # a torch build without out_dtype
-            return None
+    def cublas(m, n, k, a, b, a_mn, b_mn, ours, flops, accumulate=False, out_dtype=f32):
+        """TFLOP/s of cuBLASLt on one product, or None; `ours` = this library's C for the check
+        (with `accumulate` the check runs on a zeroed C with beta = 1, which is the same sum)."""
+        plan = cmp.plan(m, n, k, a_mn, b_mn, out_dtype != f32, accumulate)
+        if plan is None:
+            return None, None
+        c = torch.zeros((m, n), device=a.device, dtype=out_dtype)
+        cmp.run(plan, torch, a, b, c)
+        ok = cmp.agrees(torch, c, ours) if ours is not None else None
+        ms, tf = timed(lambda: cmp.run(plan, torch, a, b, c), flops)
+        cmp.lib.cmp_plan_destroy(plan)
+        del c
+        return round(tf, 1), ok
 
     for name, i, o in PROJECTIONS:
         fl = 2.0 * M_TOKENS * i * o
         w, dw = layer[name]["w"], layer[name]["dw"]
         x, dy = buf.x[i], buf.dy[o]
+        check = torch.zeros((i, o), device=x.device, dtype=f32)          # the weight gradient from zero, for the check
+        gemm.f32_accumulate_transposed(x, dy, check)
         for kind, fn, ref in (
             ("forward", lambda: gemm.f32_store(x, w, buf.y[o], transposed_b=True),
-             lambda: torch.mm(x, w, out_dtype=f32)),
+             lambda: cublas(M_TOKENS, o, i, x, w, False, True, buf.y[o], fl)),
             ("input_grad", lambda: gemm.f32_store(dy, w, buf.y[i]),
-             lambda: torch.mm(dy, w.t(), out_dtype=f32)),
+             lambda: cublas(M_TOKENS, i, o, dy, w, False, False, buf.y[i], fl)),
             ("weight_grad", lambda: gemm.f32_accumulate_transposed(x, dy, dw),
-             lambda: torch.mm(x.t(), dy, out_dtype=f32)),     # overwrite: cuBLASLt's cheaper case
+             lambda: cublas(i, o, M_TOKENS, x, dy, True, True, check, fl, accumulate=True)),   # beta = 1, like the kernel
         ):
             ms, tf = timed(fn, fl)
+            ctf, ok = ref()
             rows.append({"gemm": f"{name}.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1),
-                         "cublaslt_tflops": cublas(ref, fl)})
+                         "cublaslt_tflops": ctf, "cublaslt_agrees": ok})
+        del check
     fl = 2.0 * M_TOKENS * D_MODEL * VOCAB_PAD
     lse = head.forward(buf.x[D_MODEL], buf.head_w, buf.targets)[1]
     h = buf.x[D_MODEL]
 
-    def two_products():
-        torch.mm(buf.dlogits, buf.head_w.t(), out_dtype=f32)
-        torch.mm(h.t(), buf.dlogits, out_dtype=f32)
+    ms, tf = timed(lambda: head.forward(h, buf.head_w, buf.targets), fl)
+    # comparator: the logits product alone (bf16 logits written to HBM, no classifier)
+    ctf, _ = cublas(M_TOKENS, VOCAB_PAD, D_MODEL, h, buf.head_w, False, True, None, fl, out_dtype=torch.bfloat16)
+    rows.append({"gemm": "lm_head.fused_forward", "ms": round(ms, 4), "tflops": round(tf, 1),
+                 "cublaslt_tflops": ctf, "cublaslt_agrees": None})
+    # recompute + two gradient products; only the two products are credited.
+    # comparator: the two products alone, on dlogits already in HBM (d_weight with beta = 1)
+    ms, tf = timed(lambda: head.backward(h, buf.head_w, buf.targets, lse, dlogits=buf.dlogits, d_hidden=buf.dh,
+                                         d_weight=buf.head_dw, accumulate_dw=True), 2 * fl)
+    p1 = cmp.plan(M_TOKENS, D_MODEL, VOCAB_PAD, False, False, False, False)
+    p2 = cmp.plan(D_MODEL, VOCAB_PAD, M_TOKENS, True, True, False, True)
+    ctf = ok = None
+    if p1 is not None and p2 is not None:
+        cdh = torch.zeros_like(buf.dh)
+        cdw = torch.zeros_like(buf.head_dw)
 
-    for kind, fn, credit, ref in (
-        # comparator: the logits product alone (bf16 logits written to HBM, no classifier)
-        ("fused_forward", lambda: head.forward(h, buf.head_w, buf.targets), fl,
-         lambda: torch.mm(h, buf.head_w)),
-        # recompute + two gradient products; only the two products are credited.
-        # comparator: the two products alone, on dlogits already in HBM
-        ("fused_backward", lambda: head.backward(h, buf.head_w, buf.targets, lse,
-                                                 dlogits=buf.dlogits, d_hidden=buf.dh,
-                                                 d_weight=buf.head_dw, accumulate_dw=True), 2 * fl,
-         two_products),
-    ):
-        ms, tf = timed(fn, credit)
-        rows.append({"gemm": f"lm_head.{kind}", "ms": round(ms, 4), "tflops": round(tf, 1),
-                     "cublaslt_tflops": cublas(ref, credit)})
+        def two_products():
+            cmp.run(p1, torch, buf.dlogits, buf.head_w, cdh)
+            cmp.run(p2, torch, h, buf.dlogits, cdw)
+
+        two_products()
+        ok = cmp.agrees(torch, cdh, buf.dh)
+        ctf = round(timed(two_products, 2 * fl)[1], 1)
+        del cdh, cdw
+    rows.append({"gemm": "lm_head.fused_backward", "ms": round(ms, 4), "tflops": round(tf, 1),
+                 "cublaslt_tflops": ctf, "cublaslt_agrees": ok})
+    cmp.close()
     return rows
 
 
 
-# ---- the sharded workloads (BASELINE configs[2], [3], [4]) ------------------------
+# ---- the sharded workloads: fused head, expert-parallel MoE, tensor-parallel MLP --------------
 
-def run_sharded(args):
-    """`--workload lmhead | moe | tp_mlp`: the paths that shard over the GPUs of one box.
+SHARDED = ("lmhead", "tp_mlp", "moe")
+MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 
-    Strong scaling: the problem is the BASELINE configuration whatever N is; each
-    rank holds its shard.  Prints one JSON line (rank 0)."""
-    import torch
-    import torch.distributed as dist
-    import __graft_entry__ as entry
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if not dist.is_initialized():
-        if world == 1:
-            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            os.environ.setdefault("MASTER_PORT", "29517")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    pkg = entry.load_package()
+class Sharded:
+    """One of the three configurations that shard over the GPUs of one box, ready to step."""
+
+
+def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
     par = pkg.parallel
-    gemm = pkg.Tcgen05Gemm(local)
-    gemm.set_scheduler(args.scheduler == "dynamic")
-    ops = par.DeviceOps(gemm)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1)                                    # replicated operands: same seed on every rank
     bf, f32 = torch.bfloat16, torch.float32
+    w = Sharded()
+    w.result, w.extra = {}, None
 
     def rnd(shape, std, g=gen):
         return (torch.randn(shape, generator=g, device=dev, dtype=f32) * std).to(bf)
 
-    if args.workload == "lmhead":
+    if workload == "lmhead":
         m, k, v, classes = M_TOKENS, D_MODEL, VOCAB_PAD, VOCAB
         # Several GPUs: the weight-gradient GEMM leaves 16-32 SMs to d_hidden's all-reduce, which
         # runs in a group limited to as many thread blocks, so the two overlap.
@@ -334,21 +399,23 @@ def run_sharded(args):
         w_shard = rnd((k, head.c1 - head.c0), 0.02)
         targets = torch.randint(0, classes, (m,), generator=gen, device=dev, dtype=torch.int32)
         dw = torch.zeros((k, head.c1 - head.c0), device=dev, dtype=f32)
-        result = {}
 
         def step():
             loss, lse, _ = head.forward(hidden, w_shard, targets)
             head.backward(hidden, w_shard, targets, lse, d_weight=dw, accumulate_dw=True)
-            result["loss"] = loss
-            return 5
+            w.result["loss"] = loss
+            return 8                     # forward GEMM + two merge kernels + mean; recompute, two products, widen
 
-        flops = 3 * 2.0 * m * k * v
-        name = ("fused lm-head + softmax cross-entropy (BASELINE configs[2]): M=32768 K=1536 V=50432 "
-                "(50257 classes), forward + backward; the backward's logit recompute is not credited")
-        par_text = (f"vocabulary split over {world} GPU(s); all-reduce of row max / sum-exp and of d_hidden "
-                    f"(the latter under the weight-gradient GEMM, {reserve} SMs reserved for it)")
-        host_in = (hidden, None)
-    elif args.workload == "moe":
+        w.flops = 3 * 2.0 * m * k * v
+        w.title = ("fused lm-head + softmax cross-entropy: M=32768 K=1536 V=50432 (50257 classes), forward + "
+                   "backward; the backward's logit recompute is not credited")
+        w.par_text = (f"vocabulary split over {world} GPU(s); one all-gather of the shards' row max / sum-exp / "
+                      f"target logit, all-reduce of d_hidden under the weight-gradient GEMM ({reserve} SMs "
+                      "reserved for it)")
+        w.host_in, w.scaling = hidden, "strong"
+        w.compute_ops = ("head_forward_shard", "head_merge_shards", "head_dlogits", "head_dhidden_partial",
+                         "head_dweight", "widen")
+    elif workload == "moe":
         # 32768 tokens PER GPU (weak scaling): expert parallelism serves data-parallel
         # token batches; the experts, not the tokens, are what is divided.
         n_tok, d, ff, experts, top_k = 32768 * world, 1536, 768, 64, 8
@@ -370,122 +437,282 @@ def run_sharded(args):
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=2, exchange="device")
-        result = {}
 
         def step():
-            result["out"] = ep.forward(x, logits, scores_are_logits=True)
+            w.result["out"] = ep.forward(x, logits, scores_are_logits=True)
             return 9
 
-
-        flops = 2.0 * n_tok * top_k * d * ff * 2
-        name = ("MoE grouped expert GEMM (BASELINE configs[3]): 32768 tokens per GPU, D=1536, E=64, top-8, "
-                "expert FF=768, up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
-        par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch by peer stores and combine by "
-                    "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
-                    "counts and the two barriers; two token slices on two streams")
-        host_in = (x, None)
+        w.flops = 2.0 * n_tok * top_k * d * ff * 2
+        w.title = ("MoE grouped expert GEMM: 32768 tokens per GPU, D=1536, E=64, top-8, expert FF=768, "
+                   "up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
+        w.par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch by peer stores and combine by "
+                      "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
+                      "counts and the two barriers; two token slices on two streams")
+        w.host_in, w.scaling, w.extra = x, "weak", ep
+        w.compute_ops = ("route", "scatter", "combine", "grouped_indexed", "grouped_indexed_into", "ep_plan")
+        w.exchange_ops = ("ep_push", "ep_pull_combine")
     else:
         m, d, ff = 65536, 4096, 16384
         cols = ff // world
         x = rnd((m, d), 1.0)
         w1 = rnd((d, cols), 0.015)
         w2 = rnd((cols, d), 0.015)
-        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=4, partial_dtype=bf)
+        # several GPUs: the row exchanges go by copy-engine pushes into peer memory (no SM taken
+        # from the GEMMs), the parts are summed locally; `--mlp-exchange nccl` runs NCCL's instead
+        how = MLP_EXCHANGE if world > 1 else "nccl"
+        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=4, partial_dtype=bf, exchange=how)
         dy_local = rnd((m // world, d), 0.01)
         dw1 = torch.zeros((d, cols), device=dev, dtype=f32)
         dw2 = torch.zeros((cols, d), device=dev, dtype=f32)
-        result = {}
 
         def step():
-            result["out"] = mlp.forward(x)
-            result["dx"] = mlp.backward(x, dy_local, dw1, dw2)
+            w.result["out"] = mlp.forward(x)
+            w.result["dx"] = mlp.backward(x, dy_local, dw1, dw2)
             return 6 * 4
 
-        flops = 6 * 2.0 * m * d * ff
-        name = ("tensor-parallel MLP block (BASELINE configs[4]): M=65536 D=4096 FF=16384, column-parallel up, "
-                "row-parallel down, forward + input and weight gradients (K=65536 split-K)")
-        par_text = f"FF split over {world} GPU(s); reduce-scatter of the partial outputs, all-reduce of dx"
-        host_in = (x, None)
+        w.flops = 6 * 2.0 * m * d * ff
+        w.title = ("tensor-parallel MLP block: M=65536 D=4096 FF=16384, column-parallel up, row-parallel down, "
+                   "forward + input and weight gradients (K=65536 split-K)")
+        w.par_text = (f"FF split over {world} GPU(s); reduce-scatter of the partial outputs, all-gather of dy and "
+                      f"reduce-scatter of dx in the backward, each under the next row piece's GEMMs; exchange: {how}"
+                      + (" (copy-engine pushes into peer memory + local sum)" if how == "copy" else ""))
+        w.host_in, w.scaling = x, "strong"
+        w.compute_ops = ("linear", "linear_weight_grad", "linear_input_grad", "linear_input_grad_into")
+        w.exchange_ops = ("sum_parts",)
+    w.step = step
+    if not hasattr(w, "exchange_ops"):
+        w.exchange_ops = ()
+    return w
 
+
+def time_steps(torch, dist, step, steps, local, sample_clocks=True):
+    """CUDA-event time of `steps` steps between barriers (ms per step, clocks)."""
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
+
+    barrier()
+    sampler = ClockSampler(local) if sample_clocks else None
+    if sampler:
+        sampler.start()
+    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s0.record()
+    for _ in range(steps):
+        step()
+    e0.record()
+    barrier()
+    return s0.elapsed_time(e0) / steps, (sampler.stop() if sampler else None)
+
+
+def exchange_timeline(torch, dist, ops, w):
+    """One more step with CUDA events around every collective and every compute call (this
+    rank): how long each collective took and how much of that no GEMM of this rank covered.
+    The events sit on whichever stream the call was issued on; an exposed millisecond is one
+    during which a collective (or the expert exchange's push / pull kernels) ran and none of the
+    compute calls did."""
+    marks = []
+    restore = []
+
+    def wrap(obj, name, kind):
+        fn = getattr(obj, name, None)
+        if fn is None:
+            return
+
+        def wrapped(*a, **k):
+            s, t = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            r = fn(*a, **k)
+            t.record()
+            nbytes = 0
+            if kind == "collective":
+                big = max((x for x in a if hasattr(x, "numel")), key=lambda x: x.numel(), default=None)
+                nbytes = big.numel() * big.element_size() if big is not None else 0
+            marks.append((name, kind, s, t, nbytes))
+            return r
+
+        restore.append((obj, name, fn))
+        setattr(obj, name, wrapped)
+
+    for name in w.compute_ops:
+        wrap(ops, name, "compute")
+    for name in w.exchange_ops:
+        wrap(ops, name, "collective")
+    for name in ("all_reduce", "reduce_scatter_tensor", "all_gather_into_tensor", "all_to_all_single"):
+        wrap(dist, name, "collective")
+    try:
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        w.step()
+        t1.record()
+        torch.cuda.synchronize()
+    finally:
+        for obj, name, fn in restore:
+            setattr(obj, name, fn)
+    spans = [(name, kind, t0.elapsed_time(s), t0.elapsed_time(t), nb) for name, kind, s, t, nb in marks]
+    busy = sorted((a, b) for _, kind, a, b, _ in spans if kind == "compute")
+    merged = []
+    for a, b in busy:
+        if merged and a <= merged[-1][1]:
+            merged[-1][1] = max(merged[-1][1], b)
+        else:
+            merged.append([a, b])
+
+    def covered(a, b):
+        return sum(max(0.0, min(b, y) - max(a, x)) for x, y in merged)
+
+    per_op = {}
+    longest = None
+    for name, kind, a, b, nb in spans:
+        if kind != "collective":
+            continue
+        exposed = max(0.0, (b - a) - covered(a, b))
+        d = per_op.setdefault(name, {"calls": 0, "ms": 0.0, "exposed_ms": 0.0, "bytes": 0})
+        d["calls"] += 1
+        d["ms"] += b - a
+        d["exposed_ms"] += exposed
+        d["bytes"] += nb
+        if longest is None or exposed > longest["exposed_ms"]:
+            longest = {"op": name, "ms": round(b - a, 4), "exposed_ms": round(exposed, 4), "bytes": nb}
+    for d in per_op.values():
+        d["ms"], d["exposed_ms"] = round(d["ms"], 4), round(d["exposed_ms"], 4)
+    return {"step_ms": round(t0.elapsed_time(t1), 4), "compute_busy_ms": round(sum(b - a for a, b in merged), 4),
+            "collectives": per_op, "longest_exposed_collective": longest}
+
+
+def sharded_line(torch, dist, w, workload, world, ms, clocks, peaks, extra_e2e=None):
+    value = w.flops / (ms * 1e-3) / 1e12
+    out = {"ms_per_step": ms, "tflops": value, "tflops_per_gpu": value / world,
+           "frac_of_sustained_peak": value / world / peaks["tflops"], "scaling": w.scaling,
+           "algorithmic_flops_per_step": w.flops, "workload": w.title, "parallelism": w.par_text}
+    if clocks is not None:
+        out["clocks"] = clocks
+    if workload == "moe":
+        ep = w.extra
+        dev = w.host_in.device
+        recv = torch.tensor([float(ep.rows_received()), float(ep.last.get("rows_sent", 0)),
+                             float(ep.last.get("rows_sent_remote", -1))], device=dev)
+        allr = [torch.zeros_like(recv) for _ in range(world)]
+        dist.all_gather(allr, recv)
+        rows = [float(t[0].item()) for t in allr]
+        out["moe_rows_received_per_rank"] = rows
+        out["moe_rows_routed_per_rank"] = [float(t[1].item()) for t in allr]
+        out["moe_load_imbalance_max_over_mean"] = max(rows) / (sum(rows) / len(rows))
+    return out
+
+
+def init_group(torch, dist, rank, world, dev):
+    if not dist.is_initialized():
+        if world == 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29517")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+
+def run_sharded(args):
+    """`--workload lmhead | moe | tp_mlp`: one of the paths that shard over the GPUs of one box,
+    with the end-to-end leg.  Prints one JSON line (rank 0).  The default run reports all
+    three, device-timed, inside its own line (`sharded`)."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    init_group(torch, dist, rank, world, dev)
+    pkg = entry.load_package()
+    gemm = pkg.Tcgen05Gemm(local)
+    gemm.set_scheduler(args.scheduler == "dynamic")
+    ops = pkg.parallel.DeviceOps(gemm)
+    f32 = torch.float32
+    w = build_sharded(args.workload, torch, pkg, gemm, ops, dev, rank, world)
 
     # The expert-parallel exchange sets up peer mappings, side streams and their scheduler
     # counters during its first steps; a few more untimed steps keep that out of the clock.
     warmup = max(args.warmup, 10 if args.workload == "moe" else 3)
     for _ in range(warmup):
-        launches = step()
-    barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
-    s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    s0.record()
-    for _ in range(args.steps):
-        step()
-    e0.record()
-    barrier()
-    clocks = sampler.stop()
-    ms = s0.elapsed_time(e0) / args.steps
+        launches = w.step()
+    ms, clocks = time_steps(torch, dist, w.step, args.steps, local)
     # end to end: this step's activations from pinned host memory, one result word back
-    src = host_in[0]
+    src = w.host_in
     host_x = torch.empty(src.shape, dtype=src.dtype).pin_memory()
     host_x.copy_(src.cpu())
     host_out = torch.empty(1, dtype=f32).pin_memory()
 
     def e2e_step():
         src.copy_(host_x, non_blocking=True)
-        step()
-        word = result.get("loss")
+        w.step()
+        word = w.result.get("loss")
         if word is None:
-            word = next(iter(result.values())).reshape(-1)[:1].float()
+            word = next(iter(w.result.values())).reshape(-1)[:1].float()
         host_out.copy_(word, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     e2e_step()
-    barrier()
-    s1, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s1.record()
-    n_e2e = max(1, min(args.steps, 5))
-    for _ in range(n_e2e):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = s1.elapsed_time(e1) / n_e2e
+    e2e_ms, _ = time_steps(torch, dist, e2e_step, args.steps, local, sample_clocks=False)
     tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     ms, e2e_ms = tt.tolist()
+    timeline = exchange_timeline(torch, dist, ops, w)
     status = gemm.device_status()
     peaks = measured_peaks()
-    value = flops / (ms * 1e-3) / 1e12
+    sub = sharded_line(torch, dist, w, args.workload, world, ms, None, peaks)
+    value = sub["tflops"]
     line = {
         "metric": f"bf16_gemm_tflops_{args.workload}", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak" if args.workload == "moe" else "strong", "vs_baseline": None, "dtype": "bf16",
+        "scaling": w.scaling, "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": name, "parallelism": par_text,
+        "config": {"workload": w.title, "parallelism": w.par_text,
                    "l2": "operands exceed the 126 MB L2"},
         "pct_of_nominal_dense_peak": 100.0 * value / world / 2250.0,
         "gpu_launches": launches * args.steps, "device_status": status, "clocks": clocks,
-        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": w.flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": host_x.numel() * host_x.element_size(), "d2h_bytes_per_step": 4},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": value / world / peaks["tflops"], "traffic": None,
                      "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
-                     "algorithmic_flops_per_step": flops},
+                     "algorithmic_flops_per_step": w.flops},
+        "exchange_timeline": timeline,
     }
-    if args.workload == "moe":
-        recv = torch.tensor([float(ep.rows_received())], device=dev)
-        allr = [torch.zeros_like(recv) for _ in range(world)]
-        dist.all_gather(allr, recv)
-        rows = [float(t.item()) for t in allr]
-        line["moe_rows_received_per_rank"] = rows
-        line["moe_load_imbalance_max_over_mean"] = max(rows) / (sum(rows) / len(rows))
+    for key in ("moe_rows_received_per_rank", "moe_rows_routed_per_rank", "moe_load_imbalance_max_over_mean"):
+        if key in sub:
+            line[key] = sub[key]
     if rank == 0:
         print(json.dumps(line), flush=True)
     gemm.close()
     dist.destroy_process_group()
+
+
+def sharded_block(args, torch, dist, pkg, gemm, dev, rank, world, local):
+    """The three sharded configurations at this run's N, device-timed (10 steps each), each
+    with its exchange timeline: what the default line carries as `sharded`."""
+    ops = pkg.parallel.DeviceOps(gemm)
+    peaks = measured_peaks()
+    steps = max(3, min(args.steps, 10))
+    block = {}
+    for workload in SHARDED:
+        w = build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world)
+        for _ in range(10 if workload == "moe" else 3):
+            w.step()
+        ms, clocks = time_steps(torch, dist, w.step, steps, local)
+        tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        sub = sharded_line(torch, dist, w, workload, world, float(tt.item()), clocks, peaks)
+        sub["steps"] = steps
+        sub["exchange_timeline"] = exchange_timeline(torch, dist, ops, w)
+        sub["device_status"] = gemm.device_status()
+        block[workload] = sub
+        del w
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+    return block
+
 
 def run_only(args):
     """Profiling aid: launch ONE named GEMM of the step (e.g. qkv.forward) a few times.
@@ -650,8 +877,7 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+    init_group(torch, dist, rank, world, device)             # one rank too: the sharded block below needs a group
     pkg = entry.load_package()
     gemm = pkg.Tcgen05Gemm(local)
     gemm.set_scheduler(args.scheduler == "dynamic")
@@ -659,8 +885,7 @@ def run_gpu(args):
     buf = StepBuffers(torch, device, seed=rank)
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        dist.barrier()
         torch.cuda.synchronize()
 
     # ---- device-resident timing -------------------------------------------------
@@ -684,7 +909,7 @@ def run_gpu(args):
     host_x = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
     host_x.copy_(buf.x[D_MODEL].cpu())
     host_out = torch.empty(1, dtype=torch.float32).pin_memory()
-    e2e_steps = max(1, min(args.steps, 5))
+    e2e_steps = args.steps                                       # as many as the device-timed region
 
     def e2e_step():
         buf.x[D_MODEL].copy_(host_x, non_blocking=True)         # this step's token activations
@@ -702,11 +927,15 @@ def run_gpu(args):
     barrier()
     e2e_ms = s2.elapsed_time(e2) / e2e_steps
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
+    t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
 
+    traffic = {}
+    tpath = os.path.join(ROOT, "profiles", "gemm_tcgen05_qkv_forward_ncu.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f)
     flops = step_flops()
     value = flops * world / (ms * 1e-3) / 1e12
     e2e_value = flops * world / (e2e_ms * 1e-3) / 1e12
@@ -725,23 +954,31 @@ def run_gpu(args):
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / peaks["tflops"],
                      # dram__bytes_read + write of ONE launch of the dominant instantiation (the QKV
-                     # forward, 718.8 MB algorithmic), from the ncu capture summarised under profiles/
-                     "traffic": 706.7e6, "traffic_launch": "gemm_tcgen05_kernel<2,0,0> qkv.forward",
+                     # forward, 718.8 MB algorithmic), as recorded beside the ncu summary under profiles/
+                     "traffic": traffic.get("dram_bytes_per_launch"), "traffic_launch": traffic.get("launch"),
+                     "traffic_source": traffic.get("source"),
                      "kernel": "gemm_tcgen05_kernel (every launch of the timed region)",
                      "peak_source": f"{peaks['source']} cuBLAS bf16 sustained; burst {peaks['burst']}",
                      "algorithmic_flops_per_step": flops},
     }
+    if rank == 0 and not args.no_table:
+        line["per_shape"] = per_shape_table(torch, gemm, head, buf)
+    # ---- the configurations that shard over the box, at this N (every rank takes part)
+    del buf, head
+    torch.cuda.empty_cache()
+    if not args.no_sharded:
+        try:
+            line["sharded"] = sharded_block(args, torch, dist, pkg, gemm, device, rank, world, local)
+        except Exception as exc:                              # the headline stands on its own
+            line["sharded"] = {"error": f"{type(exc).__name__}: {exc}"}
     if rank == 0:
-        if not args.no_table:
-            line["per_shape"] = per_shape_table(torch, gemm, head, buf)
         if world == 1 and not args.no_cpu:
             secs, fl, text = cpu_sample(1)
             line["cpu_baseline"] = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
                                     "sample": text + f"; {secs:.1f} s on one host core of {os.cpu_count()}"}
         print(json.dumps(line), flush=True)
     gemm.close()
-    if world > 1:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
 
 
 def main():
@@ -752,6 +989,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-table", action="store_true", help="skip the per-shape table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sharded configurations' block")
     ap.add_argument("--only", default=None,
                     help="profiling aid: run one piece, e.g. qkv.forward, mlp_up.weight_grad, lm_head.fused_forward, "
                          "lm_head.fused_backward, moe.forward, moe.gated_forward, "
@@ -761,7 +999,11 @@ def main():
                     help="how the persistent kernels hand out tiles (see b200gemm_set_scheduler)")
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
                     help="dense_step (default) is the headline; the others are the sharded configurations")
+    ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
+                    help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
+    global MLP_EXCHANGE
+    MLP_EXCHANGE = args.mlp_exchange
     if args.impl == "reference":
         run_reference(args)
     elif args.only:

@@ -549,6 +549,17 @@ B200GEMM_API int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream,
                                               int64_t tokens, int32_t top_k, int64_t d, void* out,
                                               int32_t out_type);
 
+/*
+ * dst[i] = sum over p in [0, parts), ascending, of src[p * part_stride + i], i in [0, count):
+ * the last step of a reduce-scatter whose parts were delivered by copies (one part per rank,
+ * e.g. by the copy engines over NVLink while the SMs keep multiplying).  Element types:
+ * b200gemm_out_t, sums in fp32; count % 8 == 0.  max_blocks > 0 caps the grid, so that the
+ * pass fits beside a persistent GEMM instead of waiting for it.  New: the reference is single-GPU.
+ */
+B200GEMM_API int b200gemm_sum_parts(b200gemm_handle_t h, void* stream, const void* src, int32_t src_type,
+                                    int64_t part_stride, int32_t parts, int64_t count, void* dst,
+                                    int32_t dst_type, int32_t max_blocks);
+
 /* Synchronises `stream`, reads and clears the device status word; returns
  * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
  * *device_code (may be NULL).  The reference has no counterpart: its kernels

@@ -283,6 +283,12 @@ class Tcgen05Gemm {
     return b200gemm_transpose_bf16(h_, stream, src, dst, rows, cols);
   }
 
+  /// dst = sum of `parts` equally long arrays `part_stride` apart (the tail of a copy-delivered reduce-scatter).
+  int sum_parts(void* stream, const void* src, b200gemm_out_t src_type, int64_t part_stride, int32_t parts,
+                int64_t count, void* dst, b200gemm_out_t dst_type, int32_t max_blocks = 0) const {
+    return b200gemm_sum_parts(h_, stream, src, src_type, part_stride, parts, count, dst, dst_type, max_blocks);
+  }
+
   // ---- launch geometry, host buffers, device status ------------------------------
   /// tcgen05_launch_config (host.rs:47-94) for the GEMM `store`/`f32_store`/... would launch.
   int launch_config(const Operand& a, const Operand& b, void* out, b200gemm_out_t out_type, b200gemm_mode_t mode,

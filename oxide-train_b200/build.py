@@ -51,5 +51,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+COMPARATOR_SRC = os.path.join(HERE, "comparator", "cublaslt_compare.cpp")
+COMPARATOR_LIB = os.path.join(HERE, "comparator", "libcublaslt_compare.so")
+
+
+def build_comparator(force: bool = False) -> str | None:
+    """The benchmark's cuBLASLt column (never loaded by the package).  Returns None where the
+    toolkit has no cuBLASLt to link against."""
+    cuda = os.path.dirname(os.path.dirname(_nvcc()))
+    if not os.path.exists(os.path.join(cuda, "include", "cublasLt.h")):
+        return None
+    if (not force and os.path.exists(COMPARATOR_LIB)
+            and os.path.getmtime(COMPARATOR_LIB) >= os.path.getmtime(COMPARATOR_SRC)):
+        return COMPARATOR_LIB
+    env = dict(os.environ)
+    for var in ("CC", "CXX"):
+        env.pop(var, None)
+    lib_dir = os.path.join(cuda, "lib64")
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else (shutil.which("g++") or "g++")
+    subprocess.check_call([gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+                           "-I" + os.path.join(cuda, "include"), "-o", COMPARATOR_LIB, COMPARATOR_SRC,
+                           "-L" + lib_dir, "-lcublasLt", "-lcudart", "-Wl,-rpath," + lib_dir], env=env)
+    return COMPARATOR_LIB
+
+
 if __name__ == "__main__":
     print(build(force=True, verbose=True))

@@ -217,4 +217,59 @@ __global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
   __syncthreads();
 }
 
+// ------------------------------------------------------------------ sum of parts
+// dst[i] = sum over p (ascending) of src[p * part_stride + i], added in fp32; the tail of a
+// reduce-scatter whose parts were delivered by copies (one part per rank).  bf16 or fp32 in
+// and out; eight elements per thread per step, count a multiple of 8.
+template <bool kInBf16, bool kOutBf16>
+__global__ void __launch_bounds__(256) sum_parts_kernel(const void* __restrict__ src, long long part_stride,
+                                                        int parts, long long count, void* __restrict__ dst) {
+  const long long vecs = count / 8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += stride) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int p = 0; p < parts; ++p) {
+      if (kInBf16) {
+        const uint4 w = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(src) + p * part_stride)[v];
+        const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] = __fadd_rn(acc[2 * j], __uint_as_float(u[j] << 16));
+          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __uint_as_float(u[j] & 0xffff0000u));
+        }
+      } else {
+        const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(src) + p * part_stride) + 2 * v;
+        const float4 lo = s4[0], hi = s4[1];
+        acc[0] = __fadd_rn(acc[0], lo.x); acc[1] = __fadd_rn(acc[1], lo.y);
+        acc[2] = __fadd_rn(acc[2], lo.z); acc[3] = __fadd_rn(acc[3], lo.w);
+        acc[4] = __fadd_rn(acc[4], hi.x); acc[5] = __fadd_rn(acc[5], hi.y);
+        acc[6] = __fadd_rn(acc[6], hi.z); acc[7] = __fadd_rn(acc[7], hi.w);
+      }
+    }
+    if (kOutBf16) {
+      uint4 o;
+      o.x = f32x2_to_bf16x2(acc[0], acc[1]);
+      o.y = f32x2_to_bf16x2(acc[2], acc[3]);
+      o.z = f32x2_to_bf16x2(acc[4], acc[5]);
+      o.w = f32x2_to_bf16x2(acc[6], acc[7]);
+      reinterpret_cast<uint4*>(dst)[v] = o;
+    } else {
+      float4* o = reinterpret_cast<float4*>(dst) + 2 * v;
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+
+inline cudaError_t launch_sum_parts(cudaStream_t stream, const void* src, long long part_stride, int parts,
+                                    long long count, void* dst, bool in_bf16, bool out_bf16, int blocks) {
+  if (in_bf16 && out_bf16) sum_parts_kernel<true, true><<<blocks, 256, 0, stream>>>(src, part_stride, parts, count, dst);
+  else if (in_bf16) sum_parts_kernel<true, false><<<blocks, 256, 0, stream>>>(src, part_stride, parts, count, dst);
+  else if (out_bf16) sum_parts_kernel<false, true><<<blocks, 256, 0, stream>>>(src, part_stride, parts, count, dst);
+  else sum_parts_kernel<false, false><<<blocks, 256, 0, stream>>>(src, part_stride, parts, count, dst);
+  return cudaGetLastError();
+}
+
 }  // namespace b200

@@ -1281,6 +1281,23 @@ int b200gemm_lmhead_ce_merge_shards(b200gemm_handle_t h, void* stream, const flo
   return B200GEMM_OK;
 }
 
+int b200gemm_sum_parts(b200gemm_handle_t h, void* stream, const void* src, int32_t src_type, int64_t part_stride,
+                       int32_t parts, int64_t count, void* dst, int32_t dst_type, int32_t max_blocks) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!src || !dst) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (src_type < 0 || src_type > 1 || dst_type < 0 || dst_type > 1) return fail(B200GEMM_ERR_INVALID, "bad element type");
+  if (parts < 1 || parts > 64 || count <= 0 || (count % 8) != 0 || part_stride < count || (part_stride % 8) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "need 1..64 parts, count a positive multiple of 8, part_stride >= count and a multiple of 8");
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "buffers must be 16-byte aligned");
+  int blocks = stream_grid(count / 8, h->sm_total);
+  if (max_blocks > 0 && blocks > max_blocks) blocks = max_blocks;
+  CUDA_TRY(launch_sum_parts(static_cast<cudaStream_t>(stream), src, part_stride, parts, count, dst,
+                            src_type == B200GEMM_OUT_BF16, dst_type == B200GEMM_OUT_BF16, blocks));
+  return B200GEMM_OK;
+}
+
 int b200gemm_gemm_host(b200gemm_handle_t h, void* stream_, const b200gemm_desc_t* desc) {
   int rc = check_handle(h);
   if (rc) return rc;

@@ -189,6 +189,16 @@ class DeviceOps:
     def linear_weight_grad(self, x, dy, dw):
         self.gemm.f32_accumulate_transposed(x, dy, dw)
 
+    def sum_parts(self, parts, out):
+        """``out = sum_p parts[p]`` (``parts`` is ``[p, ...]``, contiguous), added in fp32 in order."""
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        code = lambda t: L.OUT_F32 if t.dtype == torch.float32 else L.OUT_BF16
+        L.check(self.gemm._lib.b200gemm_sum_parts(
+            self.gemm._h, _stream_ptr(), parts.data_ptr(), code(parts), parts.stride(0), parts.shape[0],
+            out.numel(), out.data_ptr(), code(out), 0))
+        return out
+
 
 def _world(group):
     return dist.get_world_size(group), dist.get_rank(group)
@@ -699,6 +709,61 @@ def exchange_plan(counts_all, rank, world):
     return send_off, [int(v) for v in send_rows], inbox_off, back_off, per_dest
 
 
+class PeerRowExchange:
+    """Reduce-scatter and all-gather of row blocks by copy-engine pushes into peer memory.
+
+    A reduce-scatter made of NCCL kernels needs SMs, and next to a persistent GEMM that holds
+    every SM it gets few of them, late (measured at 8 GPUs: 0.45 ms per 134 MB piece, a third of
+    the link rate, while the GEMMs it ran beside slowed down too).  Here every rank instead
+    *copies* the row block each peer owns straight into that peer's inbox (``cudaMemcpyAsync``
+    between peer-mapped buffers: the copy engines move the bytes over NVLink, no SM is
+    involved), a one-element all-reduce orders the ranks, and a small kernel of this library
+    adds the ``world`` parts that arrived (fp32 adds, rank order).  The all-gather is the same
+    without the sum.  Buffers are ``torch.distributed`` symmetric memory; no kernel here reads
+    or writes a peer's memory and nothing spins on a peer's flag."""
+
+    def __init__(self, ops, group, device, slots, share_rows, width, dtype=torch.bfloat16):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.ops = ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.slots, self.share, self.width = slots, share_rows, width
+        shape = (slots, self.world, share_rows, width)
+        self.inbox = symm_mem.empty(shape, dtype=dtype, device=device)        # parts of the rows I own
+        self.gathered = symm_mem.empty(shape, dtype=dtype, device=device)     # every rank's rows, in rank order
+        name = self.group.group_name
+        self._h_in = symm_mem.rendezvous(self.inbox, name)
+        self._h_all = symm_mem.rendezvous(self.gathered, name)
+        self.peer_inbox = [self._h_in.get_buffer(r, shape, dtype) for r in range(self.world)]
+        self.peer_gathered = [self._h_all.get_buffer(r, shape, dtype) for r in range(self.world)]
+        self._token = torch.zeros(1, device=device)
+
+    def barrier(self):
+        """Stream-ordered: what follows on this stream starts after every rank got here."""
+        dist.all_reduce(self._token, group=self.group)
+
+    def reduce_scatter(self, slot, partial, out):
+        """``out [share, width] = sum over ranks of their partial[rank_rows]``; ``partial`` is
+        ``[world * share, width]``.  Runs on the current stream."""
+        sh = self.share
+        # ring order starting after this rank: at any moment every GPU receives from one sender
+        for hop in range(self.world):
+            j = (self.rank + 1 + hop) % self.world
+            self.peer_inbox[j][slot, self.rank].copy_(partial[j * sh:(j + 1) * sh], non_blocking=True)
+        self.barrier()
+        self.ops.sum_parts(self.inbox[slot], out)
+        return out
+
+    def all_gather(self, slot, mine):
+        """Every rank's ``mine [share, width]`` in rank order: returns a ``[world * share, width]``
+        view of this rank's buffer, valid until ``slot`` is used again."""
+        for hop in range(self.world):
+            j = (self.rank + 1 + hop) % self.world
+            self.peer_gathered[j][slot, self.rank].copy_(mine, non_blocking=True)
+        self.barrier()
+        return self.gathered[slot].view(self.world * self.share, self.width)
+
+
 # --------------------------------------------------------------------------- tensor-parallel MLP
 
 class TensorParallelMlp:
@@ -711,13 +776,29 @@ class TensorParallelMlp:
     ``[c * m/chunks + r * m/(chunks*world), ...)`` of every piece ``c``."""
 
     def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks: int = 4,
-                 partial_dtype=torch.bfloat16, reserve_sms: int = 0):
+                 partial_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl"):
         self.ops, self.group, self.chunks = ops, group, chunks
         self.reserve_sms = reserve_sms      # SMs every GEMM leaves to the collectives on the side stream
         self.world, self.rank = _world(group)
         self.w_up, self.w_down = w_up_shard, w_down_shard
         self.partial_dtype = partial_dtype
         self._comm_stream = None
+        # "nccl": reduce_scatter_tensor / all_gather_into_tensor; "copy": copy-engine pushes into
+        # peer memory + a local sum (PeerRowExchange), CUDA tensors and more than one rank only
+        self.exchange, self._px = exchange, None
+
+    def _peer(self, x, piece, share):
+        """The copy-engine exchange for this problem size, or None (NCCL / gloo path)."""
+        if self.exchange != "copy" or x.device.type != "cuda" or self.world == 1:
+            return None
+        key = (piece, share, x.shape[1], self.partial_dtype)
+        if self._px is None or self._px_key != key:
+            if self.w_down.shape[1] != x.shape[1]:
+                raise ValueError("the copy exchange needs the MLP's input and output widths to match")
+            self._px = PeerRowExchange(self.ops, self.group, x.device, self.chunks, share, x.shape[1],
+                                       self.partial_dtype)
+            self._px_key = key
+        return self._px
 
     def _side_stream(self, device):
         if device.type != "cuda":
@@ -757,6 +838,7 @@ class TensorParallelMlp:
         piece, share = m // self.chunks, m // (self.chunks * self.world)
         out = torch.empty((self.chunks * share, d), dtype=self.partial_dtype, device=x.device)
         side = self._side_stream(x.device)
+        px = self._peer(x, piece, share)
         self._hidden = []
         partials = []
         for c in range(self.chunks):
@@ -771,7 +853,10 @@ class TensorParallelMlp:
             else:
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
-                    dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
+                    if px is not None:
+                        px.reduce_scatter(c, y, dst)
+                    else:
+                        dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
                 y.record_stream(side)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
@@ -788,9 +873,17 @@ class TensorParallelMlp:
             dx.record_stream(side)
             dx_local.record_stream(side)
 
+        px = self._peer(x, piece, share) if dy_local.dtype == self.partial_dtype else None
+
         def gather(c):
-            dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
             src = dy_local[c * share:(c + 1) * share].contiguous()
+            if px is not None:
+                with torch.cuda.stream(side):
+                    dy = px.all_gather(c, src)
+                    done = torch.cuda.Event()
+                    done.record(side)
+                return dy, done
+            dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
             if side is None:
                 dist.all_gather_into_tensor(dy, src, group=self.group)
                 return dy, None
@@ -825,7 +918,10 @@ class TensorParallelMlp:
                 produced.record(main)
                 with torch.cuda.stream(side):
                     side.wait_event(produced)
-                    dist.reduce_scatter_tensor(mine, dxs, op=dist.ReduceOp.SUM, group=self.group)
+                    if px is not None:
+                        px.reduce_scatter(c, dxs, mine)
+                    else:
+                        dist.reduce_scatter_tensor(mine, dxs, op=dist.ReduceOp.SUM, group=self.group)
         if side is not None:
             main.wait_stream(side)
         return dx_local

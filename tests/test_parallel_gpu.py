@@ -141,6 +141,28 @@ def _worker(rank, port, failures):
         assert np.max(np.abs(got - full) / (1.0 + np.abs(full))) <= 2e-2
         assert np.linalg.norm(got - full) / np.linalg.norm(full) <= 1e-2
         assert gemm.device_status() == 0
+        # the same block with the exchanges done by copy-engine pushes into peer memory and a
+        # local sum, forward and backward, twice in a row (the second step reuses every buffer)
+        shard = (w1[:, cols].contiguous(), w2[cols].contiguous())
+        mlp_nccl = par.TensorParallelMlp(ops, *shard, chunks=2, partial_dtype=bf)
+        mlp_copy = par.TensorParallelMlp(ops, *shard, chunks=2, partial_dtype=bf, exchange="copy")
+        dy_local = (torch.randn((m // WORLD, d), generator=gen, device=dev) * 0.1).to(bf)
+        outs = []
+        for blk in (mlp_nccl, mlp_copy, mlp_copy):
+            dw1 = torch.zeros((d, ff // WORLD), device=dev, dtype=torch.float32)
+            dw2 = torch.zeros((ff // WORLD, d), device=dev, dtype=torch.float32)
+            yb = blk.forward(x2)
+            dxb = blk.backward(x2, dy_local, dw1, dw2)
+            torch.cuda.synchronize()
+            outs.append((yb.float(), dxb.float(), dw1, dw2))
+        assert mlp_copy._px is not None
+        got = outs[1][0][[0, 1, len(rows) // 2, len(rows) - 1]].cpu().numpy()
+        assert np.linalg.norm(got - full) / np.linalg.norm(full) <= 1e-2         # against the oracle rows above
+        for a, b in ((outs[0], outs[1]), (outs[1], outs[2])):
+            for u, v2, what in zip(a, b, ("y", "dx", "dw_up", "dw_down")):
+                rel = float((u - v2).norm() / u.norm())
+                assert rel <= (1e-2 if a is outs[0] else 1e-6), (what, rel)
+        assert gemm.device_status() == 0
         dist.barrier()
         torch.cuda.synchronize()
         gemm.close()
