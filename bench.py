@@ -370,6 +370,7 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
 
 SHARDED = ("lmhead", "tp_mlp", "moe")
 MLP_EXCHANGE = "copy"          # set from --mlp-exchange
+HEAD_EXCHANGE = "copy"         # set from --head-exchange
 
 
 class Sharded:
@@ -392,9 +393,15 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         # Several GPUs: the weight-gradient GEMM leaves 16-32 SMs to d_hidden's all-reduce, which
         # runs in a group limited to as many thread blocks, so the two overlap.
         # (the all-reduce takes about the same time whatever N is while the GEMM shrinks with N)
-        reserve = 0 if world == 1 else (32 if world >= 8 else 16)
-        head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve,
-                                     group=par.nccl_group_with_cta_limit(reserve) if reserve else None)
+        if HEAD_EXCHANGE == "copy" or world == 1:
+            # d_hidden's sum goes by copy-engine pushes into peer memory and a local sum: no SMs to
+            # set aside for a collective's kernels beyond the few its one-element barriers run on
+            reserve = 0 if world == 1 else 4
+            head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve, exchange="copy")
+        else:
+            reserve = 32 if world >= 8 else 16
+            head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve,
+                                         group=par.nccl_group_with_cta_limit(reserve))
         hidden = rnd((m, k), 1.0)
         w_shard = rnd((k, head.c1 - head.c0), 0.02)
         targets = torch.randint(0, classes, (m,), generator=gen, device=dev, dtype=torch.int32)
@@ -410,11 +417,12 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         w.title = ("fused lm-head + softmax cross-entropy: M=32768 K=1536 V=50432 (50257 classes), forward + "
                    "backward; the backward's logit recompute is not credited")
         w.par_text = (f"vocabulary split over {world} GPU(s); one all-gather of the shards' row max / sum-exp / "
-                      f"target logit, all-reduce of d_hidden under the weight-gradient GEMM ({reserve} SMs "
-                      "reserved for it)")
+                      f"target logit; d_hidden summed over the shards under the weight-gradient GEMM ({reserve} "
+                      f"SMs left free), exchange: {HEAD_EXCHANGE if world > 1 else 'none'}")
         w.host_in, w.scaling = hidden, "strong"
         w.compute_ops = ("head_forward_shard", "head_merge_shards", "head_dlogits", "head_dhidden_partial",
                          "head_dweight", "widen")
+        w.exchange_ops = ("sum_parts",)
     elif workload == "moe":
         # 32768 tokens PER GPU (weak scaling): expert parallelism serves data-parallel
         # token batches; the experts, not the tokens, are what is divided.
@@ -999,11 +1007,13 @@ def main():
                     help="how the persistent kernels hand out tiles (see b200gemm_set_scheduler)")
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
                     help="dense_step (default) is the headline; the others are the sharded configurations")
+    ap.add_argument("--head-exchange", default="copy", choices=["copy", "nccl"],
+                    help="vocabulary-parallel head on several GPUs: how d_hidden is summed over the shards")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
-    global MLP_EXCHANGE
-    MLP_EXCHANGE = args.mlp_exchange
+    global MLP_EXCHANGE, HEAD_EXCHANGE
+    MLP_EXCHANGE, HEAD_EXCHANGE = args.mlp_exchange, args.head_exchange
     if args.impl == "reference":
         run_reference(args)
     elif args.only:

@@ -364,9 +364,18 @@ __global__ void __launch_bounds__(256) moe_combine_backward_kernel(
   for (long long token = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; token < tokens; token += warps) {
     const uint32_t my_row = lane < top_k ? dest_row[token * top_k + lane] : kMoeDropped;
     const float my_gate = lane < top_k ? gates[token * top_k + lane] : 0.f;
+    // Every lane gets every rank's (row, gate) BEFORE the column loop: lanes leave that loop at
+    // different trip counts when d / 8 is not a multiple of 32, and a warp shuffle is only
+    // defined while all the lanes its mask names are executing it.
+    uint32_t rows[kMoeMaxTopK];
+    float gs[kMoeMaxTopK];
     float dots[kMoeMaxTopK];
 #pragma unroll
-    for (int r = 0; r < kMoeMaxTopK; ++r) dots[r] = 0.f;
+    for (int r = 0; r < kMoeMaxTopK; ++r) {
+      rows[r] = __shfl_sync(0xffffffffu, my_row, r);
+      gs[r] = __shfl_sync(0xffffffffu, my_gate, r);
+      dots[r] = 0.f;
+    }
     for (long long v = lane; v < vecs; v += 32) {
       float g[8];
       if (kDyBf16) {
@@ -380,8 +389,8 @@ __global__ void __launch_bounds__(256) moe_combine_backward_kernel(
 #pragma unroll
       for (int r = 0; r < kMoeMaxTopK; ++r) {
         if (r >= top_k) break;
-        const uint32_t row = __shfl_sync(0xffffffffu, my_row, r);
-        const float gate = __shfl_sync(0xffffffffu, my_gate, r);
+        const uint32_t row = rows[r];
+        const float gate = gs[r];
         if (row == kMoeDropped) continue;
         float scaled[8];
 #pragma unroll

@@ -274,9 +274,15 @@ def merge_softmax_stats(row_max, row_sum, row_target_logit, group=None):
 
 class VocabParallelHead:
     def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out",
-                 reduce_dtype=torch.bfloat16, reserve_sms: int = 0):
+                 reduce_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl",
+                 d_hidden: str = "all"):
         self.ops, self.group, self.w_layout, self.reduce_dtype = ops, group, w_layout, reduce_dtype
-        self.reserve_sms = reserve_sms      # SMs the weight-gradient GEMM leaves to d_hidden's all-reduce
+        self.reserve_sms = reserve_sms      # SMs the weight-gradient GEMM leaves to d_hidden's exchange
+        # d_hidden's sum over the shards: "nccl" = all_reduce; "copy" = copy-engine reduce-scatter
+        # (+ all-gather) through peer memory, see PeerRowExchange.  d_hidden = "all": every rank
+        # gets all rows; "scatter": rank r gets rows [r * m / world, (r + 1) * m / world) only --
+        # half the bytes, and what a row-parallel layer below the head wants anyway.
+        self.exchange, self.d_hidden, self._px, self._px_key = exchange, d_hidden, None, None
         self.world, self.rank = _world(group)
         self.c0, self.c1 = vocab_shards(vocab_padded, self.world)[self.rank]
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
@@ -332,9 +338,28 @@ class VocabParallelHead:
         if self._side is None:
             self._side = torch.cuda.Stream(device=hidden.device)
         self._side.wait_stream(torch.cuda.current_stream())
+        m, k = dh.shape
+        use_copy = self.exchange == "copy" and self.world > 1 and m % self.world == 0
+        scatter = self.d_hidden == "scatter" and m % self.world == 0
+        if use_copy and (self._px is None or self._px_key != (m, k, dh.dtype)):
+            self._px = PeerRowExchange(self.ops, self.group, dh.device, 1, m // self.world, k, dh.dtype)
+            self._px_key = (m, k, dh.dtype)
+        mine = None
+        if use_copy or scatter:
+            mine = torch.empty((m // self.world, k), dtype=dh.dtype, device=dh.device)
+            mine.record_stream(self._side)
         with torch.cuda.stream(self._side):
-            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+            if use_copy:
+                self._px.reduce_scatter(0, dh, mine)
+                summed = mine if scatter else self._px.all_gather(0, mine)
+            elif scatter:
+                dist.reduce_scatter_tensor(mine, dh, op=dist.ReduceOp.SUM, group=self.group)
+                summed = mine
+            else:
+                dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
+                summed = dh
         dh.record_stream(self._side)
+        dh = summed
         with _ReservedSms(self.ops, self.reserve_sms):
             dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
         torch.cuda.current_stream().wait_stream(self._side)

@@ -63,6 +63,13 @@ def _worker(rank, port, failures):
         _, dh3, _ = head32.backward(h, ws, t, lse2)
         assert torch.allclose(dh1, dh3, atol=2e-5, rtol=2e-2), float((dh1 - dh3).abs().max())
         assert torch.allclose(dw1[:, head.c0:head.c1], dw2, atol=2e-5, rtol=2e-2)
+        # d_hidden summed by copy-engine pushes + a local sum, all rows and this rank's rows only, twice
+        for mode in ("all", "scatter", "all"):
+            headc = par.VocabParallelHead(ops, classes, v, exchange="copy", d_hidden=mode, reserve_sms=4)
+            _, dhc, dwc = headc.backward(h, ws, t, lse2)
+            want_rows = dh1 if mode == "all" else dh1[rank * m // WORLD:(rank + 1) * m // WORLD]
+            assert float((want_rows - dhc).norm() / want_rows.norm()) < 1e-2, mode
+            assert torch.equal(dwc, dw2)
         # ... and against the oracle: Linear::forward + SoftmaxCrossEntropy + Linear::backward on the CPU
         hv, wv, tv = h.float().cpu().numpy(), w.float().cpu().numpy(), t.cpu().numpy()
         o_logits = orc.matmul(hv, wv, 8)
