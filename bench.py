@@ -549,8 +549,10 @@ def exchange_timeline(torch, dist, ops, w):
     for name in ("all_reduce", "reduce_scatter_tensor", "all_gather_into_tensor", "all_to_all_single"):
         wrap(dist, name, "collective")
     try:
+        w.step()                      # once with the recorders in place, untimed (first-use costs of the events)
         torch.cuda.synchronize()
         dist.barrier()
+        marks.clear()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         w.step()

@@ -80,7 +80,7 @@ def test_fused_head_full_size_properties(pkg, oracle, gemm):
     w_bits[:, classes:] = 0
     from _util import to_dev_bf16
     w = to_dev_bf16(w_bits)
-    tv_all = np.minimum((oracle.uniform(m, 3) * classes).astype(np.int32), classes - 1)
+    tv_all = np.clip(((oracle.uniform(m, 3) * 0.5 + 0.5) * classes).astype(np.int32), 0, classes - 1)   # uniform is in [-1, 1)
     t = torch.from_numpy(tv_all).cuda()
     head = pkg.FusedLmHead(gemm, classes, "in_out")
     loss, lse, row_loss = head.forward(h, w, t)
@@ -157,7 +157,7 @@ def test_vocabulary_shards_emulated_on_one_gpu(pkg, oracle, gemm, world):
     w, wv = bf16_operand(oracle, (k, v), 29, std=0.3)
     wv[:, classes:] = 0
     w[:, classes:] = 0
-    targets = np.minimum((oracle.uniform(m, 30) * classes).astype(np.int32), classes - 1)
+    targets = np.clip(((oracle.uniform(m, 30) * 0.5 + 0.5) * classes).astype(np.int32), 0, classes - 1)
     targets[:4] = [0, classes - 1, 255, 256]                      # shard and tile edges
     logits, loss, row_loss, lse, dlogits = _oracle_head(oracle, hv, wv, targets, classes)
     ops = par.DeviceOps(gemm)
