@@ -468,7 +468,10 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         # several GPUs: the row exchanges go by copy-engine pushes into peer memory (no SM taken
         # from the GEMMs), the parts are summed locally; `--mlp-exchange nccl` runs NCCL's instead
         how = MLP_EXCHANGE if world > 1 else "nccl"
-        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=4, partial_dtype=bf, exchange=how)
+        # rows go through in pieces; on several GPUs short pieces at both ends, because what no GEMM
+        # covers is the exchange of the last piece (forward and backward) and the gather of the first
+        pieces = 4 if world == 1 else [1, 3, 4, 4, 3, 1]
+        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=pieces, partial_dtype=bf, exchange=how)
         dy_local = rnd((m // world, d), 0.01)
         dw1 = torch.zeros((d, cols), device=dev, dtype=f32)
         dw2 = torch.zeros((cols, d), device=dev, dtype=f32)
@@ -476,13 +479,14 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         def step():
             w.result["out"] = mlp.forward(x)
             w.result["dx"] = mlp.backward(x, dy_local, dw1, dw2)
-            return 6 * 4
+            return 6 * len(mlp.pieces(m))
 
         w.flops = 6 * 2.0 * m * d * ff
         w.title = ("tensor-parallel MLP block: M=65536 D=4096 FF=16384, column-parallel up, row-parallel down, "
                    "forward + input and weight gradients (K=65536 split-K)")
         w.par_text = (f"FF split over {world} GPU(s); reduce-scatter of the partial outputs, all-gather of dy and "
-                      f"reduce-scatter of dx in the backward, each under the next row piece's GEMMs; exchange: {how}"
+                      f"reduce-scatter of dx in the backward, each under the next row piece's GEMMs ({len(mlp.pieces(m))} pieces); "
+                      f"exchange: {how}"
                       + (" (copy-engine pushes into peer memory + local sum)" if how == "copy" else ""))
         w.host_in, w.scaling = x, "strong"
         w.compute_ops = ("linear", "linear_weight_grad", "linear_input_grad", "linear_input_grad_into")
@@ -772,15 +776,28 @@ def run_only(args):
         x = torch.randn((n_tok, d), device=dev).to(bf)
         bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
         logits = (torch.randn((n_tok, experts), device=dev) + bias).contiguous()
-        if kind == "gated_forward":        # the reference's own expert: SwiGLU over a fused gate/up projection
+        gated = kind.startswith("gated")
+        if gated:                          # the reference's own expert: SwiGLU over a fused gate/up projection
             ffn = pkg.GatedExpertFfn(gemm, (torch.randn((experts, d, 2, ff), device=dev) * 0.02).to(bf),
                                      (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
             flops = 2.0 * n_tok * top_k * d * ff * 3
+            d_up = torch.zeros((experts, d, 2, ff), device=dev, dtype=f32)
         else:
             ffn = pkg.GroupedExpertFfn(gemm, (torch.randn((experts, d, ff), device=dev) * 0.02).to(bf),
                                        (torch.randn((experts, ff, d), device=dev) * 0.02).to(bf))
             flops = 2.0 * n_tok * top_k * d * ff * 2
-        fn = lambda: ffn.forward(x, logits, top_k, scores_are_logits=True)
+            d_up = torch.zeros((experts, d, ff), device=dev, dtype=f32)
+        if kind.endswith("backward"):      # forward keeping its activations + the whole backward
+            d_dn = torch.zeros((experts, ff, d), device=dev, dtype=f32)
+            dy = (torch.randn((n_tok, d), device=dev) * 0.01).to(bf)
+            keep = {"keep_gate_up": True} if gated else {"keep_for_backward": True}
+
+            def fn():
+                ffn.forward(x, logits, top_k, scores_are_logits=True, **keep)
+                ffn.backward(dy, d_up, d_dn)
+            flops *= 3
+        else:
+            fn = lambda: ffn.forward(x, logits, top_k, scores_are_logits=True)
         for _ in range(args.warmup):
             fn()
         torch.cuda.synchronize()
@@ -1002,7 +1019,7 @@ def main():
     ap.add_argument("--no-sharded", action="store_true", help="skip the sharded configurations' block")
     ap.add_argument("--only", default=None,
                     help="profiling aid: run one piece, e.g. qkv.forward, mlp_up.weight_grad, lm_head.fused_forward, "
-                         "lm_head.fused_backward, moe.forward, moe.gated_forward, "
+                         "lm_head.fused_backward, moe.forward, moe.gated_forward, moe.backward, moe.gated_backward, "
                          "mlp_gate_up.{swiglu,swiglu_no_panel,plain_gemm_only,unfused}")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
     ap.add_argument("--scheduler", default="dynamic", choices=["static", "dynamic"],

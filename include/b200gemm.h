@@ -377,6 +377,27 @@ B200GEMM_API int b200gemm_grouped_gemm_silu(b200gemm_handle_t h, void* stream, c
                                             int32_t groups, int64_t total_rows, int64_t n, int64_t k);
 
 /*
+ * The input-gradient GEMM of an expert linear with the backward of the activation in front of
+ * it fused into its epilogue: replaces `f32_store_batched` + `swiglu_backward_interleaved_packed`
+ * (gpu/model/src/lib.rs:2335-2400), i.e. b200gemm_grouped_gemm + b200gemm_activation_backward,
+ * without the [rows, n] intermediate and with one rounding instead of two.
+ *   d_y[rows, n] = A[rows, k] . B[g]^T                          (fp32, never stored)
+ *   activation 1 (SiLU):   d_saved[rows, n]    = d_y * silu'(saved),      saved [rows, n]
+ *   activation 2 (SwiGLU): d_saved[rows, 2, n] = {d_y * up * silu'(gate), d_y * silu(gate)},
+ *                          saved = the [rows, 2, n] gate/up panel; n % 64 == 0
+ * Row strides in elements (0 = packed); n % 8 == 0.  Groups, B and `group_b_index` as in
+ * b200gemm_grouped_gemm_indexed (NULL = group g uses B[g]).
+ */
+B200GEMM_API int b200gemm_grouped_gemm_act_backward(b200gemm_handle_t h, void* stream, const void* a,
+                                                    int64_t lda, const void* b, int32_t b_layout,
+                                                    int64_t ldb, int64_t batch_stride_b, int32_t b_count,
+                                                    const int32_t* group_b_index, int32_t activation,
+                                                    const void* saved, int64_t ld_saved, void* d_saved,
+                                                    int64_t ld_dsaved, const int32_t* offsets,
+                                                    int32_t groups, int64_t total_rows, int64_t n,
+                                                    int64_t k);
+
+/*
  * Weight gradients of the expert linears over the routed permutation: the row groups are
  * the REDUCTION axis.
  *

@@ -206,6 +206,15 @@ class Tcgen05Gemm {
     return b200gemm_grouped_gemm_silu(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, b_count,
                                       group_b_index, y, ldy, before, ld_before, offsets, groups, a.rows, b.rows, a.k);
   }
+  /// Input gradient of an expert linear with the activation's backward in its epilogue
+  /// (activation 1 = SiLU, 2 = SwiGLU; `saved` = what the forward kept).
+  int grouped_gemm_act_backward(void* stream, const Operand& a, const Operand& b, int32_t b_count,
+                                const int32_t* group_b_index, int activation, const void* saved, int64_t ld_saved,
+                                void* d_saved, int64_t ld_dsaved, const int32_t* offsets, int32_t groups) const {
+    return b200gemm_grouped_gemm_act_backward(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, b_count,
+                                              group_b_index, activation, saved, ld_saved, d_saved, ld_dsaved, offsets,
+                                              groups, a.rows, b.rows, a.k);
+  }
   /// dW[g] (=|+=) A[rows_g]^T . B[rows_g]: the row groups are the reduction axis
   /// (f32_accumulate_transposed_batched over exact groups instead of capacity bins).
   int grouped_wgrad(void* stream, const void* a, int64_t lda, const void* b, int64_t ldb, float* c, int64_t ldc,

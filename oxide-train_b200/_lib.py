@@ -91,6 +91,10 @@ SIGNATURES = {
                                              C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
                                              C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "b200gemm_grouped_gemm_act_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                                     C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p,
+                                                     C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                                     C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
     "b200gemm_grouped_wgrad": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                          C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32]),

@@ -61,7 +61,7 @@ struct b200gemm_context {
   // staging for b200gemm_gemm_host
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
-  bool smem_opt_in[2][8][4] = {};   // [cta_group - 1][epilogue kind][schedule kind]: one per kernel instantiation
+  bool smem_opt_in[2][12][4] = {};   // [cta_group - 1][epilogue kind][schedule kind]: one per kernel instantiation
   // per-segment expert counts of b200gemm_moe_route: one buffer per stream, so that routing
   // calls issued on different streams can overlap on the GPU without sharing scratch
   struct Scratch {
@@ -539,14 +539,27 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
                  const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b, void* c,
                  int64_t ldc, const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
                  int64_t k, int32_t activation, const int32_t* group_b_index = nullptr,
-                 int32_t b_count = 0, void* panel = nullptr, int64_t ld_panel = 0) {
+                 int32_t b_count = 0, void* panel = nullptr, int64_t ld_panel = 0,
+                 const void* saved = nullptr, int64_t ld_saved = 0) {
   // activation 2 (SwiGLU): B is [gate | up], 2 * n columns; C = silu(gate) * up has n.
+  // activation 3 / 4: the backward of SiLU / SwiGLU applied to the product (an input gradient)
+  // from `saved`; with 4, C is the [rows, 2, n] gradient panel.
   const bool glu = activation == 2;
+  const bool act_bwd = activation == 3 || activation == 4;
   const int64_t bn = glu ? 2 * n : n;                      // B's extent along N
+  const int64_t c_cols = activation == 4 ? 2 * n : n;      // C's row length
+  if (act_bwd) {
+    if (!saved) return fail(B200GEMM_ERR_INVALID, "null saved activations");
+    if ((n % 8) != 0 || (activation == 4 && (n % 64) != 0))
+      return fail(B200GEMM_ERR_SHAPE, "the fused activation backward needs n %% 8 == 0 (SiLU) / n %% 64 == 0 (SwiGLU)");
+    ld_saved = ld_saved ? ld_saved : c_cols;
+    if (ld_saved < c_cols || (ld_saved % 8) != 0 || (reinterpret_cast<uintptr_t>(saved) & 15u) != 0)
+      return fail(B200GEMM_ERR_SHAPE, "saved activations: row stride must cover the row and be a multiple of 8, base 16-byte aligned");
+  }
   if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
   if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
   const int32_t b_mats = group_b_index ? b_count : groups;
-  if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 2)
+  if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 4)
     return fail(B200GEMM_ERR_INVALID, "bad layout or activation");
   if (panel && activation == 0) return fail(B200GEMM_ERR_INVALID, "a second output is written only with an activation");
   if (glu && (n % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "SwiGLU needs ff to be a multiple of 8");
@@ -557,10 +570,10 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const bool b_mn = b_layout == B200GEMM_MN_MAJOR;
   lda = lda ? lda : k;
   ldb = ldb ? ldb : (b_mn ? bn : k);
-  ldc = ldc ? ldc : n;
+  ldc = ldc ? ldc : c_cols;
   const int64_t panel_cols = glu ? 2 * n : n;            // SiLU keeps the [rows, n] values before the activation
   ld_panel = ld_panel ? ld_panel : panel_cols;
-  if (lda < k || ldb < (b_mn ? bn : k) || ldc < n) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
+  if (lda < k || ldb < (b_mn ? bn : k) || ldc < c_cols) return fail(B200GEMM_ERR_SHAPE, "leading dimension too small");
   if ((ldc % 8) != 0) return fail(B200GEMM_ERR_SHAPE, "ldc must be a multiple of 8");
   if (panel && (ld_panel < panel_cols || (ld_panel % 8) != 0))
     return fail(B200GEMM_ERR_SHAPE, "second output's row stride must cover its row and be a multiple of 8");
@@ -573,7 +586,7 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, bn, b_mats, ldb, bsb, 64, kTileN / 2, "B");
   else rc = encode_map(ctx, &params.map_b, bf16, 2, b, bn, k, b_mats, ldb, bsb, 64, 64, "B");
   if (rc) return rc;
-  rc = encode_map(ctx, &params.map_c, bf16, 2, c, n, total_rows, 1, ldc, 0, 64, 32, "C");
+  rc = encode_map(ctx, &params.map_c, bf16, 2, c, c_cols, total_rows, 1, ldc, 0, 64, 32, "C");
   if (rc) return rc;
   if (panel) {
     rc = encode_map(ctx, &params.map_d, bf16, 2, panel, panel_cols, total_rows, 1, ld_panel, 0, 64, 32, "panel");
@@ -596,7 +609,9 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   params.group_offsets = offsets;
   params.group_b_index = group_b_index;
   params.groups = groups;
-  params.act_silu = activation == 1;
+  params.act_silu = activation == 1 ? 1 : (activation == 3 ? 2 : (activation == 4 ? 3 : 0));
+  params.saved = static_cast<const uint16_t*>(saved);
+  params.ld_saved = ld_saved;
   params.glu_cols = glu ? static_cast<int>(n) : 0;
   // The tile count depends on the device-side offsets; bound it from above
   // (each group wastes at most one partial tile) and let surplus clusters exit.
@@ -604,6 +619,7 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const int64_t max_items = (ceil_div(total_rows, 2 * kTileMCta) + static_cast<int64_t>(groups)) * params.tiles_n;
   const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
   if (glu) return launch_kernel<2, kEpiBf16GroupedGlu, kSchedGrouped>(ctx, params, grid, stream);
+  if (act_bwd) return launch_kernel<2, kEpiBf16GroupedActBwd, kSchedGrouped>(ctx, params, grid, stream);
   return launch_kernel<2, kEpiBf16Grouped, kSchedGrouped>(ctx, params, grid, stream);
 }
 
@@ -1140,6 +1156,21 @@ int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const*
                                                            tokens, top_k, d, result_rows, h->status, out);
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
+}
+
+int b200gemm_grouped_gemm_act_backward(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                       const void* b, int32_t b_layout, int64_t ldb, int64_t batch_stride_b,
+                                       int32_t b_count, const int32_t* group_b_index, int32_t activation,
+                                       const void* saved, int64_t ld_saved, void* d_saved, int64_t ld_dsaved,
+                                       const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
+                                       int64_t k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (activation != 1 && activation != 2) return fail(B200GEMM_ERR_INVALID, "activation is 1 (SiLU) or 2 (SwiGLU)");
+  if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, d_saved,
+                      ld_dsaved, offsets, groups, total_rows, n, k, activation + 2, group_b_index, b_count, nullptr,
+                      0, saved, ld_saved);
 }
 
 int b200gemm_grouped_wgrad(b200gemm_handle_t h, void* stream, const void* a, int64_t lda, const void* b,

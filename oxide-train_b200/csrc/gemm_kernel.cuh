@@ -71,10 +71,14 @@ enum EpilogueKind : int {
   // fp32 C through TMA store plus the same values rounded to bf16 into a second matrix
   // (the operand copy the next GEMM reads; replaces a separate fp32 -> bf16 convert pass).
   kEpiF32DualBf16 = 7,
+  // Ragged row groups, backward of the activation fused into the input-gradient GEMM:
+  // C = acc * silu'(saved) (p.act_silu == 2, saved [rows, n]) or, for SwiGLU (p.act_silu == 3,
+  // saved = the [rows, 2, n] gate/up panel), C [rows, 2, n] = {acc * up * silu'(gate), acc * silu(gate)}.
+  kEpiBf16GroupedActBwd = 8,
 };
 
 __host__ __device__ constexpr bool epi_is_grouped(int epi) {
-  return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu;
+  return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu || epi == kEpiBf16GroupedActBwd;
 }
 
 enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2, kSchedGroupedWgrad = 3 };
@@ -124,7 +128,10 @@ struct GemmParams {
   const int* group_offsets;  // [groups + 1] first row of each group
   const int* group_b_index;  // [groups] which B matrix group g multiplies; null = g itself
   int groups;
-  int act_silu;        // kEpiBf16Grouped: apply x * sigmoid(x) before rounding
+  int act_silu;        // kEpiBf16Grouped: 1 = apply x * sigmoid(x) before rounding;
+                       // kEpiBf16GroupedActBwd: 2 = SiLU backward, 3 = SwiGLU backward
+  const uint16_t* saved;   // kEpiBf16GroupedActBwd: what the forward kept ([rows, n] or [rows, 2, n])
+  long long ld_saved;
   // ---- kEpiBf16GroupedGlu (the reference's [rows, 2, ff] gate/up panel, gpu/ops/src/lib.rs:1149-1171)
   int glu_cols;        // ff: B's "up" block starts this many columns after its "gate" block; C is [rows, ff]
   CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1};
@@ -754,11 +761,51 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           // activation's backward reads.
           [[maybe_unused]] uint32_t before[32];
           const bool keep_before = kEpi == kEpiBf16Grouped && p.d_bf16 != nullptr;
+          // kEpiBf16GroupedActBwd: this row's 64 saved values (and, for SwiGLU, the 64 "up"
+          // values n columns further on), requested before the accumulator is read.
+          [[maybe_unused]] uint4 sg[8], su[8];
+          [[maybe_unused]] uint32_t packed_up[32];
+          if constexpr (kEpi == kEpiBf16GroupedActBwd) {
+            const uint16_t* srow = p.saved + static_cast<long long>(row) * p.ld_saved + col0 + c * 64;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const bool ok = row < t.m_end && col0 + c * 64 + 8 * q + 8 <= p.n;
+              sg[q] = ok ? *reinterpret_cast<const uint4*>(srow + 8 * q) : make_uint4(0u, 0u, 0u, 0u);
+              if (p.act_silu == 3)
+                su[q] = ok ? *reinterpret_cast<const uint4*>(srow + p.n + 8 * q) : make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * 64 + h * 32, r);
             tmem_ld_wait();
+            if constexpr (kEpi == kEpiBf16GroupedActBwd) {
+              const uint32_t* gw = reinterpret_cast<const uint32_t*>(sg) + h * 16;
+              const uint32_t* uw = reinterpret_cast<const uint32_t*>(su) + h * 16;
+              float up_grad[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const uint32_t gword = gw[j >> 1];
+                const float g = __uint_as_float((j & 1) ? (gword & 0xffff0000u) : (gword << 16));
+                // sigmoid(g) = (1 + tanh(g / 2)) / 2: one MUFU op; silu'(g) = s * (1 + g * (1 - s))
+                const float sgm = fmaf(0.5f, fast_tanh(0.5f * g), 0.5f);
+                const float dsilu = sgm * fmaf(g, 1.f - sgm, 1.f);
+                const float dy = __uint_as_float(r[j]);
+                if (p.act_silu == 3) {
+                  const uint32_t uword = uw[j >> 1];
+                  const float u = __uint_as_float((j & 1) ? (uword & 0xffff0000u) : (uword << 16));
+                  r[j] = __float_as_uint(dy * u * dsilu);
+                  up_grad[j] = dy * (g * sgm);
+                } else {
+                  r[j] = __float_as_uint(dy * dsilu);
+                }
+              }
+              if (p.act_silu == 3) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) packed_up[h * 16 + j] = pack_bf16x2(up_grad[2 * j], up_grad[2 * j + 1]);
+              }
+            }
             if constexpr (kEpi == kEpiBf16Grouped) {
               if (keep_before) {
 #pragma unroll
@@ -808,6 +855,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
           if constexpr (kEpi == kEpiBf16Grouped) {
             if (keep_before) put_chunk(&p.map_d, p.d_bf16, p.ldd, col0 + c * 64, p.n, before);
+          }
+          if constexpr (kEpi == kEpiBf16GroupedActBwd) {
+            // SwiGLU: the gradient of the "up" half goes n columns further on in the same panel
+            // (the host requires n % 64 == 0, so a chunk of gate columns never reaches into it).
+            if (p.act_silu == 3 && col0 + c * 64 < p.n)
+              put_chunk(&p.map_c, p.c_bf16, p.ldc, p.n + col0 + c * 64, 2 * p.n, packed_up);
           }
           }
         }

@@ -214,6 +214,28 @@ def activation_backward(gemm: Tcgen05Gemm, activation: str, saved, d_y, out=None
     return out
 
 
+def grouped_gemm_act_backward(gemm: Tcgen05Gemm, dy, w, offsets, activation: str, saved, out=None,
+                              group_b_index=None):
+    """``d_saved = act'(saved) * (dy . w^T)`` per row group in one launch: the input gradient of an
+    expert's down projection with the activation's backward in its epilogue.
+
+    ``w`` is ``[matrices, n, k]`` (the ``[IN, OUT]`` weight read K-major); ``saved`` / the result are
+    ``[rows, n]`` (``"silu"``) or ``[rows, 2, n]`` (``"swiglu"``)."""
+    rows, k = dy.shape
+    n = w.shape[1]
+    if w.shape[2] != k:
+        raise ValueError("reduction extents differ")
+    code = {"silu": 1, "swiglu": 2}[activation]
+    groups = offsets.numel() - 1
+    if out is None:
+        out = torch.empty_like(saved)
+    L.check(gemm._lib.b200gemm_grouped_gemm_act_backward(
+        gemm._h, _stream_ptr(), dy.data_ptr(), dy.stride(0), w.data_ptr(), L.K_MAJOR, w.stride(1), w.stride(0),
+        w.shape[0], None if group_b_index is None else group_b_index.data_ptr(), code, saved.data_ptr(),
+        saved.stride(0), out.data_ptr(), out.stride(0), offsets.data_ptr(), groups, rows, n, k))
+    return out
+
+
 def route_backward(gemm: Tcgen05Gemm, probs, routing: MoeRouting, gate_grad, aux_coefficient: float = 0.0):
     """Gradient of the router's logits from the gradients of the combine weights (moe.rs:397-445)."""
     tokens, experts = probs.shape
@@ -247,6 +269,7 @@ class _ExpertCtx:
 
 class _ExpertFfnBase:
     activation = "silu"
+    fuse_activation_backward = True
 
     def _up(self, xp, offsets, keep):
         raise NotImplementedError
@@ -275,8 +298,13 @@ class _ExpertFfnBase:
                                           rows=c.y_permuted.shape[0])
         # down projection: dW_down[e] += hidden_e^T dyp_e ; d_hidden = dyp . W_down^T
         grouped_wgrad(g, c.hidden, dyp, r.offsets, d_w_down, accumulate=True)
-        d_hidden = grouped_gemm(g, dyp, self.w_down, r.offsets, transposed_b=False)
-        d_saved = activation_backward(g, self.activation, c.saved, d_hidden)
+        ff = self.w_down.shape[1]
+        if self.fuse_activation_backward and ff % (64 if self.activation == "swiglu" else 8) == 0:
+            # d_hidden = dyp . W_down^T never leaves the SM: the activation's backward is the GEMM's epilogue
+            d_saved = grouped_gemm_act_backward(g, dyp, self.w_down, r.offsets, self.activation, c.saved)
+        else:
+            d_hidden = grouped_gemm(g, dyp, self.w_down, r.offsets, transposed_b=False)
+            d_saved = activation_backward(g, self.activation, c.saved, d_hidden)
         # up projection: dW_up[e] += x_e^T d_saved_e ; dx_permuted = d_saved . W_up^T
         flat = d_saved.reshape(d_saved.shape[0], -1)
         w_up = self.w_up.reshape(self.w_up.shape[0], self.w_up.shape[1], -1)

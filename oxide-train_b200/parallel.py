@@ -342,7 +342,7 @@ class VocabParallelHead:
         use_copy = self.exchange == "copy" and self.world > 1 and m % self.world == 0
         scatter = self.d_hidden == "scatter" and m % self.world == 0
         if use_copy and (self._px is None or self._px_key != (m, k, dh.dtype)):
-            self._px = PeerRowExchange(self.ops, self.group, dh.device, 1, m // self.world, k, dh.dtype)
+            self._px = PeerRowExchange(self.ops, self.group, dh.device, [m // self.world], k, dh.dtype)
             self._px_key = (m, k, dh.dtype)
         mine = None
         if use_copy or scatter:
@@ -747,21 +747,30 @@ class PeerRowExchange:
     without the sum.  Buffers are ``torch.distributed`` symmetric memory; no kernel here reads
     or writes a peer's memory and nothing spins on a peer's flag."""
 
-    def __init__(self, ops, group, device, slots, share_rows, width, dtype=torch.bfloat16):
+    def __init__(self, ops, group, device, shares, width, dtype=torch.bfloat16):
+        """``shares[s]`` = rows every rank owns in slot ``s`` (slots may differ in size)."""
         import torch.distributed._symmetric_memory as symm_mem
         self.ops = ops
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
-        self.slots, self.share, self.width = slots, share_rows, width
-        shape = (slots, self.world, share_rows, width)
-        self.inbox = symm_mem.empty(shape, dtype=dtype, device=device)        # parts of the rows I own
-        self.gathered = symm_mem.empty(shape, dtype=dtype, device=device)     # every rank's rows, in rank order
+        self.shares, self.width = list(shares), width
+        sizes = [self.world * sh * width for sh in self.shares]
+        self._off = [sum(sizes[:i]) for i in range(len(sizes))]
+        total = sum(sizes)
+        self._inbox = symm_mem.empty((total,), dtype=dtype, device=device)       # parts of the rows I own
+        self._gathered = symm_mem.empty((total,), dtype=dtype, device=device)    # every rank's rows, in rank order
         name = self.group.group_name
-        self._h_in = symm_mem.rendezvous(self.inbox, name)
-        self._h_all = symm_mem.rendezvous(self.gathered, name)
-        self.peer_inbox = [self._h_in.get_buffer(r, shape, dtype) for r in range(self.world)]
-        self.peer_gathered = [self._h_all.get_buffer(r, shape, dtype) for r in range(self.world)]
+        self._h_in = symm_mem.rendezvous(self._inbox, name)
+        self._h_all = symm_mem.rendezvous(self._gathered, name)
+        self._peer_inbox = [self._h_in.get_buffer(r, (total,), dtype) for r in range(self.world)]
+        self._peer_gathered = [self._h_all.get_buffer(r, (total,), dtype) for r in range(self.world)]
         self._token = torch.zeros(1, device=device)
+
+    def _slot(self, flat, slot):
+        """``[world, share, width]`` view of slot ``slot`` of a flat buffer."""
+        sh = self.shares[slot]
+        n = self.world * sh * self.width
+        return flat[self._off[slot]:self._off[slot] + n].view(self.world, sh, self.width)
 
     def barrier(self):
         """Stream-ordered: what follows on this stream starts after every rank got here."""
@@ -770,13 +779,13 @@ class PeerRowExchange:
     def reduce_scatter(self, slot, partial, out):
         """``out [share, width] = sum over ranks of their partial[rank_rows]``; ``partial`` is
         ``[world * share, width]``.  Runs on the current stream."""
-        sh = self.share
+        sh = self.shares[slot]
         # ring order starting after this rank: at any moment every GPU receives from one sender
         for hop in range(self.world):
             j = (self.rank + 1 + hop) % self.world
-            self.peer_inbox[j][slot, self.rank].copy_(partial[j * sh:(j + 1) * sh], non_blocking=True)
+            self._slot(self._peer_inbox[j], slot)[self.rank].copy_(partial[j * sh:(j + 1) * sh], non_blocking=True)
         self.barrier()
-        self.ops.sum_parts(self.inbox[slot], out)
+        self.ops.sum_parts(self._slot(self._inbox, slot), out)
         return out
 
     def all_gather(self, slot, mine):
@@ -784,9 +793,9 @@ class PeerRowExchange:
         view of this rank's buffer, valid until ``slot`` is used again."""
         for hop in range(self.world):
             j = (self.rank + 1 + hop) % self.world
-            self.peer_gathered[j][slot, self.rank].copy_(mine, non_blocking=True)
+            self._slot(self._peer_gathered[j], slot)[self.rank].copy_(mine, non_blocking=True)
         self.barrier()
-        return self.gathered[slot].view(self.world * self.share, self.width)
+        return self._slot(self._gathered, slot).view(self.world * self.shares[slot], self.width)
 
 
 # --------------------------------------------------------------------------- tensor-parallel MLP
@@ -795,12 +804,17 @@ class TensorParallelMlp:
     """Column-parallel ``up`` ([d, ff / world]) and row-parallel ``down`` ([ff / world, d]).
 
     ``forward`` takes the replicated ``x [m, d]`` and returns this rank's rows of
-    ``y = (x . W_up) . W_down`` after a reduce-scatter.  Rows are processed in
-    ``chunks`` pieces; the reduce-scatter of a piece runs on a side stream while
-    the next piece's GEMMs run, and rank ``r`` ends up owning rows
-    ``[c * m/chunks + r * m/(chunks*world), ...)`` of every piece ``c``."""
+    ``y = (x . W_up) . W_down`` after a reduce-scatter.  Rows are processed in pieces; the
+    reduce-scatter of a piece runs on a side stream while the next piece's GEMMs run, and of
+    every piece ``[start, start + rows)`` rank ``r`` ends up owning rows
+    ``[start + r * rows / world, start + (r + 1) * rows / world)``.
 
-    def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks: int = 4,
+    ``chunks`` is the number of equal pieces, or a list of row fractions (e.g.
+    ``[1, 3, 4, 4, 3, 1]``): what no GEMM can cover is the exchange of the LAST piece of the
+    forward and of the backward and the gather of the backward's FIRST piece, so short pieces
+    at both ends shorten exactly that, while the long ones in the middle keep the GEMMs large."""
+
+    def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks=4,
                  partial_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl"):
         self.ops, self.group, self.chunks = ops, group, chunks
         self.reserve_sms = reserve_sms      # SMs every GEMM leaves to the collectives on the side stream
@@ -810,18 +824,31 @@ class TensorParallelMlp:
         self._comm_stream = None
         # "nccl": reduce_scatter_tensor / all_gather_into_tensor; "copy": copy-engine pushes into
         # peer memory + a local sum (PeerRowExchange), CUDA tensors and more than one rank only
-        self.exchange, self._px = exchange, None
+        self.exchange, self._px, self._px_key = exchange, None, None
 
-    def _peer(self, x, piece, share):
+    def pieces(self, m: int):
+        """``[(first row, rows), ...]`` of the pieces ``m`` rows are processed in."""
+        if isinstance(self.chunks, int):
+            if m % (self.chunks * self.world):
+                raise ValueError("rows must divide by chunks * world")
+            return [(c * (m // self.chunks), m // self.chunks) for c in range(self.chunks)]
+        total = sum(self.chunks)
+        rows = [m * f // total for f in self.chunks]
+        if sum(rows) != m or any(r <= 0 or r % self.world for r in rows):
+            raise ValueError("every piece must be a positive multiple of the world size and the pieces must add up")
+        starts = [sum(rows[:i]) for i in range(len(rows))]
+        return list(zip(starts, rows))
+
+    def _peer(self, x, plan):
         """The copy-engine exchange for this problem size, or None (NCCL / gloo path)."""
         if self.exchange != "copy" or x.device.type != "cuda" or self.world == 1:
             return None
-        key = (piece, share, x.shape[1], self.partial_dtype)
+        key = (tuple(plan), x.shape[1], self.partial_dtype)
         if self._px is None or self._px_key != key:
             if self.w_down.shape[1] != x.shape[1]:
                 raise ValueError("the copy exchange needs the MLP's input and output widths to match")
-            self._px = PeerRowExchange(self.ops, self.group, x.device, self.chunks, share, x.shape[1],
-                                       self.partial_dtype)
+            self._px = PeerRowExchange(self.ops, self.group, x.device, [rows // self.world for _, rows in plan],
+                                       x.shape[1], self.partial_dtype)
             self._px_key = key
         return self._px
 
@@ -834,10 +861,10 @@ class TensorParallelMlp:
 
     def owned_rows(self, m: int):
         """Global row indices this rank holds after ``forward`` (in output order)."""
-        piece = m // self.chunks
-        share = piece // self.world
-        idx = [torch.arange(c * piece + self.rank * share, c * piece + (self.rank + 1) * share)
-               for c in range(self.chunks)]
+        idx = []
+        for start, rows in self.pieces(m):
+            share = rows // self.world
+            idx.append(torch.arange(start + self.rank * share, start + (self.rank + 1) * share))
         return torch.cat(idx)
 
     def forward(self, x):
@@ -858,21 +885,20 @@ class TensorParallelMlp:
 
     def _forward(self, x):
         m, d = x.shape[0], self.w_down.shape[1]
-        if m % (self.chunks * self.world):
-            raise ValueError("rows must divide by chunks * world")
-        piece, share = m // self.chunks, m // (self.chunks * self.world)
-        out = torch.empty((self.chunks * share, d), dtype=self.partial_dtype, device=x.device)
+        plan = self.pieces(m)
+        out = torch.empty((m // self.world, d), dtype=self.partial_dtype, device=x.device)
         side = self._side_stream(x.device)
-        px = self._peer(x, piece, share)
+        px = self._peer(x, plan)
         self._hidden = []
-        partials = []
-        for c in range(self.chunks):
-            xs = x[c * piece:(c + 1) * piece]
+        done = 0
+        for c, (start, rows) in enumerate(plan):
+            share = rows // self.world
+            xs = x[start:start + rows]
             h = self.ops.linear(xs, self.w_up, torch.bfloat16)
             y = self.ops.linear(h, self.w_down, self.partial_dtype)
             self._hidden.append(h)
-            partials.append(y)
-            dst = out[c * share:(c + 1) * share]
+            dst = out[done:done + share]
+            done += share
             if side is None:
                 dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
             else:
@@ -889,26 +915,28 @@ class TensorParallelMlp:
 
     def _backward(self, x, dy_local, dw_up, dw_down):
         m = x.shape[0]
-        piece, share = m // self.chunks, m // (self.chunks * self.world)
+        plan = self.pieces(m)
+        first = [sum(rows // self.world for _, rows in plan[:c]) for c in range(len(plan))]   # of my rows, per piece
         dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)
-        dx_local = torch.empty((self.chunks * share, x.shape[1]), dtype=self.partial_dtype, device=x.device)
+        dx_local = torch.empty((m // self.world, x.shape[1]), dtype=self.partial_dtype, device=x.device)
         side = self._side_stream(x.device)
         main = torch.cuda.current_stream() if side is not None else None
         if side is not None:
             dx.record_stream(side)
             dx_local.record_stream(side)
-
-        px = self._peer(x, piece, share) if dy_local.dtype == self.partial_dtype else None
+        px = self._peer(x, plan) if dy_local.dtype == self.partial_dtype else None
 
         def gather(c):
-            src = dy_local[c * share:(c + 1) * share].contiguous()
+            rows = plan[c][1]
+            share = rows // self.world
+            src = dy_local[first[c]:first[c] + share].contiguous()
             if px is not None:
                 with torch.cuda.stream(side):
                     dy = px.all_gather(c, src)
                     done = torch.cuda.Event()
                     done.record(side)
                 return dy, done
-            dy = torch.empty((piece, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
+            dy = torch.empty((rows, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
             if side is None:
                 dist.all_gather_into_tensor(dy, src, group=self.group)
                 return dy, None
@@ -922,20 +950,21 @@ class TensorParallelMlp:
         if side is not None:
             side.wait_stream(main)
         nxt = gather(0)
-        for c in range(self.chunks):
+        for c, (start, rows) in enumerate(plan):
+            share = rows // self.world
             dy, ready = nxt
-            if c + 1 < self.chunks:
+            if c + 1 < len(plan):
                 nxt = gather(c + 1)                                       # prefetch under this piece's GEMMs
             if ready is not None:
                 main.wait_event(ready)
             h = self._hidden[c]
             self.ops.linear_weight_grad(h, dy, dw_down)                   # dW_down += h^T dy
             dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16)   # dh = dy W_down^T
-            xs = x[c * piece:(c + 1) * piece]
+            xs = x[start:start + rows]
             self.ops.linear_weight_grad(xs, dh, dw_up)                    # dW_up += x^T dh
-            dxs = dx[c * piece:(c + 1) * piece]
+            dxs = dx[start:start + rows]
             self.ops.linear_input_grad_into(dh, self.w_up, dxs)           # dx piece (partial sum)
-            mine = dx_local[c * share:(c + 1) * share]
+            mine = dx_local[first[c]:first[c] + share]
             if side is None:
                 dist.reduce_scatter_tensor(mine, dxs, op=dist.ReduceOp.SUM, group=self.group)
             else:

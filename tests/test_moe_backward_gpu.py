@@ -136,6 +136,37 @@ def test_grouped_gemm_silu_keeps_the_values_before_the_activation(pkg, oracle, g
             assert_gemm_close(from_dev_bf16(before[off[g]:off[g + 1]]), ref, f"before {g}", rel_fro=4e-3, elem=8e-3)
 
 
+@pytest.mark.parametrize("activation,ff", [("silu", 200), ("swiglu", 128), ("swiglu", 320), ("silu", 768)])
+def test_activation_backward_fused_into_the_input_gradient(pkg, oracle, gemm, activation, ff):
+    """`d_saved = act'(saved) * (dy . W^T)` from one launch against the oracle's two steps (an
+    input gradient by `matmul_nt`, then `SwiGlu::backward`), and against the two-launch GPU form."""
+    counts = [130, 0, 517, 64, 33]
+    off, off_dev = _offsets(counts)
+    rows, d = int(off[-1]), 192
+    dy, dyv = bf16_operand(oracle, (rows, d), 25, std=0.1)
+    w, wv = bf16_operand(oracle, (len(counts), ff, d), 26, std=0.1)
+    shape = (rows, 2, ff) if activation == "swiglu" else (rows, ff)
+    saved, sv = bf16_operand(oracle, shape, 27)
+    fused = pkg.moe.grouped_gemm_act_backward(gemm, dy, w, off_dev, activation, saved)
+    assert gemm.device_status() == 0
+    d_hidden = pkg.moe.grouped_gemm(gemm, dy, w, off_dev, transposed_b=False)
+    two_pass = pkg.moe.activation_backward(gemm, activation, saved, d_hidden)
+    got, other = from_dev_bf16(fused), from_dev_bf16(two_pass)
+    for g in range(len(counts)):
+        if not counts[g]:
+            continue
+        a, b = off[g], off[g + 1]
+        dact = oracle.matmul_nt(dyv[a:b], wv[g], THREADS)
+        if activation == "swiglu":
+            dg, du = oracle.swiglu_backward(sv[a:b, 0], sv[a:b, 1], dact)
+            assert_gemm_close(got[a:b, 0], dg, f"d_gate {g}", rel_fro=4e-3, elem=8e-3)
+            assert_gemm_close(got[a:b, 1], du, f"d_up {g}", rel_fro=4e-3, elem=8e-3)
+        else:
+            assert_gemm_close(got[a:b], oracle.silu_backward(sv[a:b], dact), f"d_pre {g}", rel_fro=4e-3, elem=8e-3)
+    # the two-launch form rounds d_hidden to bf16 in between: the same values to a bf16 ulp or two
+    assert_gemm_close(got, other, "fused vs two launches", rel_fro=6e-3, elem=1.6e-2)
+
+
 def test_combine_and_scatter_backward(pkg, oracle, gemm):
     import torch
     N, E, K, D, cap = 600, 6, 3, 136, 250            # the capacity forces drops

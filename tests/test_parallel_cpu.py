@@ -193,7 +193,12 @@ def case_moe(rank, par, ops, orc):
 
 
 def case_tp_mlp(rank, par, ops, orc):
-    m, d, ff, chunks = 64, 16, 48, 2
+    for chunks in (2, [1, 3, 3, 1]):          # equal pieces; short pieces at both ends
+        _tp_mlp_case(orc, par, ops, rank, chunks)
+
+
+def _tp_mlp_case(orc, par, ops, rank, chunks):
+    m, d, ff = 64, 16, 48
     x = orc.normal(m * d, 21).reshape(m, d)
     w1 = orc.normal(d * ff, 22, 0.0, 0.2).reshape(d, ff)
     w2 = orc.normal(ff * d, 23, 0.0, 0.2).reshape(ff, d)

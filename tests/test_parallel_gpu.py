@@ -151,9 +151,13 @@ def _worker(rank, port, failures):
         # the same block with the exchanges done by copy-engine pushes into peer memory and a
         # local sum, forward and backward, twice in a row (the second step reuses every buffer)
         shard = (w1[:, cols].contiguous(), w2[cols].contiguous())
-        mlp_nccl = par.TensorParallelMlp(ops, *shard, chunks=2, partial_dtype=bf)
-        mlp_copy = par.TensorParallelMlp(ops, *shard, chunks=2, partial_dtype=bf, exchange="copy")
+        mlp_nccl = par.TensorParallelMlp(ops, *shard, chunks=[1, 2, 1], partial_dtype=bf)
+        mlp_copy = par.TensorParallelMlp(ops, *shard, chunks=[1, 2, 1], partial_dtype=bf, exchange="copy")
         dy_local = (torch.randn((m // WORLD, d), generator=gen, device=dev) * 0.1).to(bf)
+        rows = mlp_copy.owned_rows(m)                          # short pieces at both ends: another ownership
+        pick = rows[[0, 1, len(rows) // 2, len(rows) - 1]]
+        hid = orc.bf16_round(orc.matmul(x2[pick].float().cpu().numpy(), w1.float().cpu().numpy(), 4))
+        full = orc.matmul(hid, w2.float().cpu().numpy(), 4)
         outs = []
         for blk in (mlp_nccl, mlp_copy, mlp_copy):
             dw1 = torch.zeros((d, ff // WORLD), device=dev, dtype=torch.float32)
