@@ -397,7 +397,10 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
             # d_hidden's sum goes by copy-engine pushes into peer memory and a local sum: no SMs to
             # set aside for a collective's kernels beyond the few its one-element barriers run on
             reserve = 0 if world == 1 else 4
-            head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve, exchange="copy")
+            # each rank keeps its own m / N rows of the summed d_hidden (a reduce-scatter): what a
+            # row-parallel layer below the head consumes; `d_hidden="all"` would gather them again
+            head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve, exchange="copy",
+                                         d_hidden="scatter" if world > 1 else "all")
         else:
             reserve = 32 if world >= 8 else 16
             head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve,
@@ -418,7 +421,8 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
                    "backward; the backward's logit recompute is not credited")
         w.par_text = (f"vocabulary split over {world} GPU(s); one all-gather of the shards' row max / sum-exp / "
                       f"target logit; d_hidden summed over the shards under the weight-gradient GEMM ({reserve} "
-                      f"SMs left free), exchange: {HEAD_EXCHANGE if world > 1 else 'none'}")
+                      f"SMs left free), exchange: {HEAD_EXCHANGE if world > 1 else 'none'}"
+                      + ("; every rank keeps its m / N rows of d_hidden (reduce-scatter)" if world > 1 else ""))
         w.host_in, w.scaling = hidden, "strong"
         w.compute_ops = ("head_forward_shard", "head_merge_shards", "head_dlogits", "head_dhidden_partial",
                          "head_dweight", "widen")

@@ -852,15 +852,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               packed[h * 16 + j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
           }
           if (c == kChunks - 1) release_accumulator();
-          put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
+          if constexpr (kEpi == kEpiBf16GroupedActBwd) {
+            // SwiGLU: C is the [rows, 2, n] panel, so columns at or beyond n are NOT outside the
+            // tensor map (they are the "up" half): a chunk past the product's n columns must not be
+            // stored at all, and the gradient of the "up" half goes n columns further on (the host
+            // requires n % 64 == 0, so a chunk of gate columns never reaches into it).
+            if (col0 + c * 64 < p.n) {
+              put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
+              if (p.act_silu == 3) put_chunk(&p.map_c, p.c_bf16, p.ldc, p.n + col0 + c * 64, 2 * p.n, packed_up);
+            }
+          } else {
+            put_chunk(&p.map_c, p.c_bf16, p.ldc, col0 + c * 64, p.n, packed);
+          }
           if constexpr (kEpi == kEpiBf16Grouped) {
             if (keep_before) put_chunk(&p.map_d, p.d_bf16, p.ldd, col0 + c * 64, p.n, before);
-          }
-          if constexpr (kEpi == kEpiBf16GroupedActBwd) {
-            // SwiGLU: the gradient of the "up" half goes n columns further on in the same panel
-            // (the host requires n % 64 == 0, so a chunk of gate columns never reaches into it).
-            if (p.act_silu == 3 && col0 + c * 64 < p.n)
-              put_chunk(&p.map_c, p.c_bf16, p.ldc, p.n + col0 + c * 64, 2 * p.n, packed_up);
           }
           }
         }
