@@ -371,6 +371,7 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
 SHARDED = ("lmhead", "tp_mlp", "moe")
 MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
+MOE_PIECES = 2                 # set from --moe-pieces: token slices of the expert-parallel step
 
 
 class Sharded:
@@ -448,7 +449,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         logits = (torch.randn((n_local, experts), generator=grank, device=dev) + bias).contiguous()
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
-        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=2, exchange="device")
+        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=MOE_PIECES, exchange="device")
 
         def step():
             w.result["out"] = ep.forward(x, logits, scores_are_logits=True)
@@ -459,7 +460,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
                    "up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
         w.par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch by peer stores and combine by "
                       "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
-                      "counts and the two barriers; two token slices on two streams")
+                      f"counts and the two barriers; {MOE_PIECES} token slices on two streams")
         w.host_in, w.scaling, w.extra = x, "weak", ep
         w.compute_ops = ("route", "scatter", "combine", "grouped_indexed", "grouped_indexed_into", "ep_plan")
         w.exchange_ops = ("ep_push", "ep_pull_combine")
@@ -1032,11 +1033,13 @@ def main():
                     help="dense_step (default) is the headline; the others are the sharded configurations")
     ap.add_argument("--head-exchange", default="copy", choices=["copy", "nccl"],
                     help="vocabulary-parallel head on several GPUs: how d_hidden is summed over the shards")
+    ap.add_argument("--moe-pieces", type=int, default=2,
+                    help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
-    global MLP_EXCHANGE, HEAD_EXCHANGE
-    MLP_EXCHANGE, HEAD_EXCHANGE = args.mlp_exchange, args.head_exchange
+    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES
+    MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES = args.mlp_exchange, args.head_exchange, args.moe_pieces
     if args.impl == "reference":
         run_reference(args)
     elif args.only:

@@ -69,7 +69,7 @@ def test_fused_head_matches_oracle(pkg, oracle, gemm, m, k, v, classes, layout):
 
 
 def test_fused_head_full_size_properties(pkg, oracle, gemm):
-    """BASELINE size (32768 x 1536 x 50432, 50257 classes): sampled rows against the
+    """The 183M dense model's head at full size (32768 x 1536 x 50432, 50257 classes): sampled rows against the
     oracle and size-independent properties of the gradient."""
     import torch
     m, k, v, classes = 32768, 1536, 50432, 50257

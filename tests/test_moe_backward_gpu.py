@@ -240,12 +240,15 @@ def test_loss_mean_with_aux(pkg, oracle, gemm):
 
 # ---- the whole block -------------------------------------------------------------------------
 
-def _block(pkg, oracle, gemm, gated, N, D, FF, E, K, cap, seed):
+def _block(pkg, oracle, gemm, gated, N, D, FF, E, K, cap, seed, idle_expert=None):
     """Forward + backward of a whole expert block on the GPU and through MoeRef on the same bf16
     operands, MoeRef rounding its intermediates to bf16 where the GPU path stores them."""
     import torch
     x, xv = bf16_operand(oracle, (N, D), seed)
-    probs = oracle.softmax_rows(oracle.normal(N * E, seed + 1).reshape(N, E) * 1.5)
+    logits = oracle.normal(N * E, seed + 1).reshape(N, E) * 1.5
+    if idle_expert is not None:
+        logits[:, idle_expert] -= 60.0                     # never among the top-k: the expert gets no rows
+    probs = oracle.softmax_rows(logits)
     wd, wdv = bf16_operand(oracle, (E, FF, D), seed + 2, std=0.08)
     dy, dyv = bf16_operand(oracle, (N, D), seed + 3, std=0.1)
     if gated:
@@ -282,9 +285,10 @@ def _block(pkg, oracle, gemm, gated, N, D, FF, E, K, cap, seed):
 
 
 def test_gated_block_backward_with_drops_and_an_idle_expert(pkg, oracle, gemm):
-    # the reference's own expert (SwiGLU); capacity 150 forces drops; expert 5 gets nothing
-    ref = _block(pkg, oracle, gemm, True, N=700, D=192, FF=128, E=6, K=2, cap=300, seed=60)
+    # the reference's own expert (SwiGLU); the capacity forces drops; expert 4 gets nothing
+    ref = _block(pkg, oracle, gemm, True, N=700, D=192, FF=128, E=6, K=2, cap=200, seed=60, idle_expert=4)
     assert int((ref.r["slots"] == 0xFFFFFFFF).sum()) > 0
+    assert int(ref.r["accepted_counts"][4]) == 0
 
 
 def test_silu_block_backward(pkg, oracle, gemm):

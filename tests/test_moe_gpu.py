@@ -3,8 +3,8 @@
 Routing cases restate the reference's: the tie golden vector
 (crates/nn/tests/moe.rs:182-197, gpu/ops/src/main.rs:1260-1283), the bin-assign
 shape N=2500, E=5, K=2, C=720 with its formula routing (gpu/ops/src/main.rs:914-1036),
-forced drops (crates/nn/tests/moe.rs:148-151) and the BASELINE configuration
-(E=64, top-8, Zipf-skewed loads).
+forced drops (crates/nn/tests/moe.rs:148-151) and the 64-expert top-8 configuration
+with Zipf-skewed loads.
 """
 import numpy as np
 import pytest
@@ -237,7 +237,7 @@ def test_moe_forward_small_matches_oracle(pkg, oracle, gemm):
 
 
 def test_moe_full_size_properties(pkg, oracle, gemm):
-    """BASELINE MoE config: 32768 tokens, D=1536, E=64, top-8, FF=768."""
+    """The 64-expert configuration at full size: 32768 tokens, D=1536, E=64, top-8, FF=768."""
     import torch
     N, D, FF, E, K = 32768, 1536, 768, 64, 8
     gen = torch.Generator(device="cuda")
