@@ -1033,13 +1033,16 @@ def main():
                     help="dense_step (default) is the headline; the others are the sharded configurations")
     ap.add_argument("--head-exchange", default="copy", choices=["copy", "nccl"],
                     help="vocabulary-parallel head on several GPUs: how d_hidden is summed over the shards")
-    ap.add_argument("--moe-pieces", type=int, default=2,
-                    help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams")
+    ap.add_argument("--moe-pieces", default="2",
+                    help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams; "
+                         "a count, or comma-separated weights such as 1,3,3,1")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
     global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES
-    MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES = args.mlp_exchange, args.head_exchange, args.moe_pieces
+    MLP_EXCHANGE, HEAD_EXCHANGE = args.mlp_exchange, args.head_exchange
+    parts = [int(v) for v in str(args.moe_pieces).split(",")]
+    MOE_PIECES = parts[0] if len(parts) == 1 else parts
     if args.impl == "reference":
         run_reference(args)
     elif args.only:

@@ -497,17 +497,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           if constexpr (kSched == kSchedGroupedWgrad) {
             // The last K block of a group runs past the group's end: the copy engine clips
             // only at the end of the whole array, so rows k_tail..63 of this stage hold the
-            // NEXT group's rows.  A product is unaffected by garbage in one operand where the
-            // other is zero, so those rows of A alone are zeroed, in this CTA's stage and in
-            // the peer's, before the tensor cores read them.  An MN-major stage keeps one K row
-            // per 128-byte line of each 64-column subtile, so this is whole lines.
+            // NEXT group's rows -- or, behind the last group, whatever the buffer holds there,
+            // which need not even be finite (so zeroing one operand would not do: 0 x NaN).
+            // Those rows of A and of B are zeroed, in this CTA's stage and in the peer's, before
+            // the tensor cores read them.  An MN-major stage keeps one K row per 128-byte line of
+            // each 64-column subtile, and B's subtiles follow A's, so this is whole lines of
+            // consecutive subtiles.
             if (kb == t.kb_count - 1 && t.k_tail < kBlockK) {
+              constexpr int kSubtiles = (kTileMCta + Cfg::kBRowsCta) / 64;
               const uint32_t a_stage = ring + stage * Cfg::kStageBytes;
               const int lines = kBlockK - t.k_tail;                 // per subtile
               const int chunks = lines * 8;                          // 16-byte pieces per subtile
-              for (int c = lane; c < chunks * (kTileMCta / 64) * kCtaGroup; c += 32) {
-                const int cta = c / (chunks * (kTileMCta / 64));
-                const int rest = c - cta * chunks * (kTileMCta / 64);
+              for (int c = lane; c < chunks * kSubtiles * kCtaGroup; c += 32) {
+                const int cta = c / (chunks * kSubtiles);
+                const int rest = c - cta * chunks * kSubtiles;
                 const int sub = rest / chunks;
                 const uint32_t off = a_stage + sub * kSubtileBytes + t.k_tail * 128 + (rest - sub * chunks) * 16;
                 if (cta == 0) st_shared_zero16(off);

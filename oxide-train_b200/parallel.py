@@ -439,47 +439,63 @@ class ExpertParallelMoe:
         import ctypes as C
         n, d = x.shape
         ff, d_out = self.w_up.shape[2], self.w_down.shape[2]
-        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
-        step = n // pieces
-        cap = step * self.top_k * self.world                # worst case: every row of every rank lands here
-        key = (pieces, cap, d, ff, d_out)
+        slices = self._slices(n)
+        caps = [rows * self.top_k * self.world for _, rows in slices]   # worst case: every row of every rank lands here
+        first = [sum(caps[:i]) for i in range(len(caps))]               # first buffer row of every slice
+        total = sum(caps)
+        key = (tuple(slices), d, ff, d_out)
         if self._dev is None or self._dev["key"] != key:
             import torch.distributed._symmetric_memory as symm_mem
             grp = self.group if self.group is not None else dist.group.WORLD
-            inbox = symm_mem.empty((pieces * cap, d), dtype=torch.bfloat16, device=x.device)
-            results = symm_mem.empty((pieces * cap, d_out), dtype=torch.bfloat16, device=x.device)
+            inbox = symm_mem.empty((total, d), dtype=torch.bfloat16, device=x.device)
+            results = symm_mem.empty((total, d_out), dtype=torch.bfloat16, device=x.device)
             h_in = symm_mem.rendezvous(inbox, grp.group_name)
             h_res = symm_mem.rendezvous(results, grp.group_name)
             ptrs_in, ptrs_res = [], []
-            for p in range(pieces):
+            for p in range(len(slices)):
                 a_in = (C.c_void_p * self.world)()
                 a_res = (C.c_void_p * self.world)()
                 for r in range(self.world):
-                    a_in[r] = h_in.get_buffer(r, (pieces * cap, d), torch.bfloat16).data_ptr() + p * cap * d * 2
-                    a_res[r] = h_res.get_buffer(r, (pieces * cap, d_out), torch.bfloat16).data_ptr() + p * cap * d_out * 2
+                    a_in[r] = h_in.get_buffer(r, (total, d), torch.bfloat16).data_ptr() + first[p] * d * 2
+                    a_res[r] = h_res.get_buffer(r, (total, d_out), torch.bfloat16).data_ptr() + first[p] * d_out * 2
                 ptrs_in.append(a_in)
                 ptrs_res.append(a_res)
             self._dev = {"key": key, "inbox": inbox, "results": results, "handles": (h_in, h_res),
                          "ptrs_in": ptrs_in, "ptrs_res": ptrs_res,
-                         "hidden": torch.empty((pieces * cap, ff), dtype=torch.bfloat16, device=x.device),
+                         "hidden": torch.empty((total, ff), dtype=torch.bfloat16, device=x.device),
                          "token": torch.zeros(1, device=x.device)}
         dv = self._dev
         out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
         # The expert GEMMs leave a few SMs to the one-element all-reduces used as barriers
         # and to the other slice's small kernels.
         with _ReservedSms(self.ops, self.reserve_sms):
-            return self._forward_device_body(x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out)
+            return self._forward_device_body(x, scores, scores_are_logits, residual, out, dv, slices, caps, first)
 
-    def _forward_device_body(self, x, scores, scores_are_logits, residual, out, dv, pieces, step, cap, d_out):
+    def _slices(self, n):
+        """``[(first token, tokens), ...]``: ``pieces`` equal slices, or -- ``pieces`` a list of
+        weights -- slices in those proportions (a short first and last slice shorten what no GEMM
+        can cover: the first slice's dispatch and the last slice's combine)."""
+        if isinstance(self.pieces, int):
+            pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+            return [(p * (n // pieces), n // pieces) for p in range(pieces)]
+        total = sum(self.pieces)
+        rows = [n * w // total for w in self.pieces]
+        if sum(rows) != n or min(rows) < 256:
+            return [(0, n)]
+        return [(sum(rows[:i]), rows[i]) for i in range(len(rows))]
+
+    def _forward_device_body(self, x, scores, scores_are_logits, residual, out, dv, slices, caps, first):
         n = x.shape[0]
+        d_out = out.shape[1]
+        pieces = len(slices)
         streams = self._streams(x.device) if pieces > 1 else [torch.cuda.current_stream()]
         main = torch.cuda.current_stream()
         routed = []
         # Stage 1, every slice: route, plan, push, barrier.  Issued for all slices before
         # any GEMM so that the collectives (which NCCL runs in issue order) of a later
         # slice are not queued behind an earlier slice's post-GEMM barrier.
-        for p in range(pieces):
-            sl = slice(p * step, (p + 1) * step)
+        for p, (start, rows) in enumerate(slices):
+            sl = slice(start, start + rows)
             st = streams[p % len(streams)]
             if st is not main:
                 st.wait_stream(main)
@@ -488,7 +504,7 @@ class ExpertParallelMoe:
                 allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
                 dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
                 dst_base, offsets, index = self.ops.ep_plan(allc, self.world, self.rank, self.experts)
-                self.ops.ep_push(x[sl], r, dst_base, dv["ptrs_in"][p], cap, self.world, self.experts)
+                self.ops.ep_push(x[sl], r, dst_base, dv["ptrs_in"][p], caps[p], self.world, self.experts)
                 dist.all_reduce(dv["token"], group=self.group)        # every rank's rows have landed
                 if st is not main:
                     for tns in (allc, dst_base, offsets, index):
@@ -498,14 +514,14 @@ class ExpertParallelMoe:
         for p, (sl, r, dst_base, offsets, index) in enumerate(routed):
             st = streams[p % len(streams)]
             with torch.cuda.stream(st):
-                inbox = dv["inbox"][p * cap:(p + 1) * cap]
-                hidden = dv["hidden"][p * cap:(p + 1) * cap]
-                res = dv["results"][p * cap:(p + 1) * cap]
+                inbox = dv["inbox"][first[p]:first[p] + caps[p]]
+                hidden = dv["hidden"][first[p]:first[p] + caps[p]]
+                res = dv["results"][first[p]:first[p] + caps[p]]
                 self.ops.grouped_indexed_into(inbox, self.w_up, offsets, index, True, hidden)
                 self.ops.grouped_indexed_into(hidden, self.w_down, offsets, index, False, res)
                 dist.all_reduce(dv["token"], group=self.group)        # every rank's results are complete
                 self.ops.ep_pull_combine(dv["ptrs_res"][p], r, dst_base, residual[sl] if residual is not None else None,
-                                         cap, self.world, self.experts, d_out, out[sl])
+                                         caps[p], self.world, self.experts, d_out, out[sl])
                 if st is not main:
                     out.record_stream(st)
         for st in streams:
@@ -532,7 +548,8 @@ class ExpertParallelMoe:
         results are pushed back, so the pushes of one slice ride under the GEMMs of another."""
         n, d = x.shape
         d_out = self.w_down.shape[2]
-        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+        count = self.pieces if isinstance(self.pieces, int) else len(self.pieces)   # equal slices on this path
+        pieces = count if (n % count == 0 and n // count >= 256) else 1
         step = n // pieces
         pairs = step * self.top_k
         cap = pairs * min(self.world, 3)                      # inbox rows per slice (3x the even share)
@@ -619,7 +636,8 @@ class ExpertParallelMoe:
         streams, so that the all-to-alls of a slice overlap the GEMMs of its
         neighbour."""
         n = x.shape[0]
-        pieces = self.pieces if (n % self.pieces == 0 and n // self.pieces >= 256) else 1
+        count = self.pieces if isinstance(self.pieces, int) else len(self.pieces)   # equal slices on this path
+        pieces = count if (n % count == 0 and n // count >= 256) else 1
         step = n // pieces
         on_gpu = x.device.type == "cuda"
         plan = []

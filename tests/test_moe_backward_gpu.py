@@ -44,8 +44,10 @@ def test_grouped_wgrad_ragged_groups(pkg, oracle, gemm, m, n):
     import torch
     off, off_dev = _offsets(RAGGED)
     rows, G = int(off[-1]), len(RAGGED)
-    a, av = bf16_operand(oracle, (rows + 70, m), 11)               # rows past the last group exist and must not count
-    b, bv = bf16_operand(oracle, (rows + 70, n), 12, std=0.05)
+    a, av = bf16_operand(oracle, (rows + 70, m), 11)               # rows past the last group exist and must not count,
+    b, bv = bf16_operand(oracle, (rows + 70, n), 12, std=0.05)     # whatever they hold: uninitialised memory can be NaN
+    a[rows:] = float("nan")
+    b[rows:] = float("inf")
     ref = np.stack([oracle.matmul_tn(av[off[g]:off[g + 1]], bv[off[g]:off[g + 1]], THREADS)
                     if off[g + 1] > off[g] else np.zeros((m, n), np.float32) for g in range(G)])
     c = torch.full((G, m, n), 5.0, dtype=torch.float32, device="cuda")

@@ -86,7 +86,7 @@ def _worker(rank, port, failures):
         assert rel <= 1e-2, ("d_weight shard", rel)
 
         # ---- expert-parallel MoE vs the single-GPU grouped path on this rank's tokens
-        n_local, d, ff, experts, top_k = 512, 256, 384, 8, 2
+        n_local, d, ff, experts, top_k = 1024, 256, 384, 8, 2
         x = torch.randn((WORLD, n_local, d), generator=gen, device=dev).to(bf)
         up = (torch.randn((experts, d, ff), generator=gen, device=dev) * 0.1).to(bf)
         dn = (torch.randn((experts, ff, d), generator=gen, device=dev) * 0.1).to(bf)
@@ -128,6 +128,13 @@ def _worker(rank, port, failures):
             out3 = ep3.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
             assert ep3.last["exchange"] == "device"
             assert torch.allclose(out3, ref, atol=1e-5, rtol=1e-5), float((out3 - ref).abs().max())
+        # ... and with token slices of different sizes (a short first and last slice)
+        ep4 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=[1, 2, 1], exchange="device")
+        for _ in range(2):
+            out4 = ep4.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert ep4.last["pieces"] == 3
+            assert torch.allclose(out4, ref, atol=1e-5, rtol=1e-5), float((out4 - ref).abs().max())
         assert gemm.device_status() == 0
 
         # ---- tensor-parallel MLP vs the unsharded product of the same bf16 operands
