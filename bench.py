@@ -372,6 +372,7 @@ SHARDED = ("lmhead", "tp_mlp", "moe")
 MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
 MOE_PIECES = 2                 # set from --moe-pieces: token slices of the expert-parallel step
+MOE_RETURN = "pull"            # set from --moe-return
 
 
 class Sharded:
@@ -449,7 +450,8 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         logits = (torch.randn((n_local, experts), generator=grank, device=dev) + bias).contiguous()
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
-        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=MOE_PIECES, exchange="device")
+        ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=MOE_PIECES, exchange="device",
+                                   return_path=MOE_RETURN)
 
         def step():
             w.result["out"] = ep.forward(x, logits, scores_are_logits=True)
@@ -462,7 +464,8 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
                       "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
                       f"counts and the two barriers; {MOE_PIECES} token slices on two streams")
         w.host_in, w.scaling, w.extra = x, "weak", ep
-        w.compute_ops = ("route", "scatter", "combine", "grouped_indexed", "grouped_indexed_into", "ep_plan")
+        w.compute_ops = ("route", "scatter", "combine", "combine_into", "grouped_indexed", "grouped_indexed_into",
+                         "grouped_indexed_peer", "ep_plan", "ep_return_plan")
         w.exchange_ops = ("ep_push", "ep_pull_combine")
     else:
         m, d, ff = 65536, 4096, 16384
@@ -1036,10 +1039,14 @@ def main():
     ap.add_argument("--moe-pieces", default="2",
                     help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams; "
                          "a count, or comma-separated weights such as 1,3,3,1")
+    ap.add_argument("--moe-return", default="pull", choices=["pull", "push"],
+                    help="expert-parallel MoE: results read by the token's rank while it combines (pull), or stored "
+                         "into the token rank's buffer by the owner's down-projection GEMM (push)")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
-    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES
+    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN
+    MOE_RETURN = args.moe_return
     MLP_EXCHANGE, HEAD_EXCHANGE = args.mlp_exchange, args.head_exchange
     parts = [int(v) for v in str(args.moe_pieces).split(",")]
     MOE_PIECES = parts[0] if len(parts) == 1 else parts

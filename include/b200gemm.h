@@ -581,6 +581,37 @@ B200GEMM_API int b200gemm_sum_parts(b200gemm_handle_t h, void* stream, const voi
                                     int64_t part_stride, int32_t parts, int64_t count, void* dst,
                                     int32_t dst_type, int32_t max_blocks);
 
+/*
+ * The return leg of the expert-parallel exchange fused into the expert GEMM (new, like the
+ * calls above): instead of writing its results into a local buffer for the token owners to
+ * read later (b200gemm_moe_ep_pull_combine), the grouped GEMM stores every group's rows
+ * straight into the buffer of the rank those rows came from, from its epilogue, so the
+ * transfer over NVLink runs underneath the tensor-core work of the same kernel.
+ *
+ *   return_plan  from all_counts[world][experts]: for every group g = (source rank s, local
+ *                expert e) of MY inbox, group_dst_rank[g] = s and group_dst_row[g] = the row of
+ *                rank s's own permuted order (b200gemm_moe_route's dest_row) where the rows of
+ *                that expert begin.  Device int32 [experts] each.
+ *   grouped_gemm_peer  b200gemm_grouped_gemm_indexed without activation, whose C is not a
+ *                local matrix: rows of group g land in peer_out[group_dst_rank[g]] (bf16,
+ *                row stride ld_out elements, 0 = n) at rows group_dst_row[g] + (row - first row
+ *                of g).  Plain 16-byte stores, 128 bytes per row and 64-column chunk; a row at
+ *                or beyond out_rows is not written and device status 105 is recorded.
+ * After every rank's GEMM (one barrier), each rank combines ITS tokens from ITS buffer with
+ * b200gemm_moe_combine, exactly as on one GPU.  world <= 8, n % 8 == 0.
+ */
+B200GEMM_API int b200gemm_moe_ep_return_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts,
+                                             int32_t world, int32_t rank, int32_t experts,
+                                             int32_t* group_dst_rank, int32_t* group_dst_row);
+B200GEMM_API int b200gemm_grouped_gemm_peer(b200gemm_handle_t h, void* stream, const void* a, int64_t lda,
+                                            const void* b, int32_t b_layout, int64_t ldb,
+                                            int64_t batch_stride_b, int32_t b_count,
+                                            const int32_t* group_b_index, void* const* peer_out,
+                                            int32_t world, int64_t ld_out, int64_t out_rows,
+                                            const int32_t* group_dst_rank, const int32_t* group_dst_row,
+                                            const int32_t* offsets, int32_t groups, int64_t total_rows,
+                                            int64_t n, int64_t k);
+
 /* Synchronises `stream`, reads and clears the device status word; returns
  * B200GEMM_ERR_DEVICE if a kernel recorded a timeout, and the raw code in
  * *device_code (may be NULL).  The reference has no counterpart: its kernels

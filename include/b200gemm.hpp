@@ -161,6 +161,20 @@ class Tcgen05Gemm {
     return b200gemm_moe_ep_pull_combine(h_, stream, peer_results, selected, slots, dst_base, gates, residual,
                                         result_rows, world, experts, tokens, top_k, d, out, out_type);
   }
+  /// Where my inbox's groups return to (rank and first row), for grouped_gemm_peer.
+  int moe_ep_return_plan(void* stream, const int32_t* all_counts, int32_t world, int32_t rank, int32_t experts,
+                         int32_t* group_dst_rank, int32_t* group_dst_row) const {
+    return b200gemm_moe_ep_return_plan(h_, stream, all_counts, world, rank, experts, group_dst_rank, group_dst_row);
+  }
+  /// The expert GEMM whose epilogue stores each group's rows into the buffer of the rank they came from.
+  int grouped_gemm_peer(void* stream, const Operand& a, const Operand& b, int32_t b_count, const int32_t* group_b_index,
+                        void* const* peer_out, int32_t world, int64_t ld_out, int64_t out_rows,
+                        const int32_t* group_dst_rank, const int32_t* group_dst_row, const int32_t* offsets,
+                        int32_t groups) const {
+    return b200gemm_grouped_gemm_peer(h_, stream, a.ptr, a.ld, b.ptr, b.layout, b.ld, b.batch_stride, b_count,
+                                      group_b_index, peer_out, world, ld_out, out_rows, group_dst_rank, group_dst_row,
+                                      offsets, groups, a.rows, b.rows, a.k);
+  }
   /// Rows offsets[g]..offsets[g+1] of `a` times expert g's matrix, bf16 out, optional SiLU.
   int grouped_gemm(void* stream, const Operand& a, const Operand& b, void* c, int64_t ldc,
                    const int32_t* offsets, int32_t groups, bool silu) const {

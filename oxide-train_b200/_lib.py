@@ -113,6 +113,12 @@ SIGNATURES = {
                                               C.c_int32, C.c_float, C.c_void_p]),
     "b200gemm_lmhead_ce_merge_shards": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,
                                                   C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200gemm_moe_ep_return_plan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                              C.c_void_p, C.c_void_p]),
+    "b200gemm_grouped_gemm_peer": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int32,
+                                             C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.POINTER(C.c_void_p),
+                                             C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
     "b200gemm_sum_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int64,
                                      C.c_void_p, C.c_int32, C.c_int32]),
     "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,

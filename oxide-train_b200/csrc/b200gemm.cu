@@ -540,7 +540,9 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
                  int64_t ldc, const int32_t* offsets, int32_t groups, int64_t total_rows, int64_t n,
                  int64_t k, int32_t activation, const int32_t* group_b_index = nullptr,
                  int32_t b_count = 0, void* panel = nullptr, int64_t ld_panel = 0,
-                 const void* saved = nullptr, int64_t ld_saved = 0) {
+                 const void* saved = nullptr, int64_t ld_saved = 0, const PeerBuffers* peer_out = nullptr,
+                 const int32_t* group_dst_rank = nullptr, const int32_t* group_dst_row = nullptr,
+                 int64_t peer_rows = 0) {
   // activation 2 (SwiGLU): B is [gate | up], 2 * n columns; C = silu(gate) * up has n.
   // activation 3 / 4: the backward of SiLU / SwiGLU applied to the product (an input gradient)
   // from `saved`; with 4, C is the [rows, 2, n] gradient panel.
@@ -556,7 +558,9 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
     if (ld_saved < c_cols || (ld_saved % 8) != 0 || (reinterpret_cast<uintptr_t>(saved) & 15u) != 0)
       return fail(B200GEMM_ERR_SHAPE, "saved activations: row stride must cover the row and be a multiple of 8, base 16-byte aligned");
   }
-  if (!a || !b || !c || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (!a || !b || (!c && !peer_out) || !offsets) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (peer_out && (!group_dst_rank || !group_dst_row || activation != 0 || (n % 8) != 0 || peer_rows <= 0))
+    return fail(B200GEMM_ERR_INVALID, "the peer-store form needs its group tables, no activation, n %% 8 == 0 and a row limit");
   if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
   const int32_t b_mats = group_b_index ? b_count : groups;
   if (b_layout < 0 || b_layout > 1 || activation < 0 || activation > 4)
@@ -586,8 +590,15 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   if (!b_mn) rc = encode_map(ctx, &params.map_b, bf16, 2, b, k, bn, b_mats, ldb, bsb, 64, kTileN / 2, "B");
   else rc = encode_map(ctx, &params.map_b, bf16, 2, b, bn, k, b_mats, ldb, bsb, 64, 64, "B");
   if (rc) return rc;
-  rc = encode_map(ctx, &params.map_c, bf16, 2, c, c_cols, total_rows, 1, ldc, 0, 64, 32, "C");
-  if (rc) return rc;
+  if (!peer_out) {
+    rc = encode_map(ctx, &params.map_c, bf16, 2, c, c_cols, total_rows, 1, ldc, 0, 64, 32, "C");
+    if (rc) return rc;
+  } else {
+    params.peer_out = *peer_out;
+    params.group_dst_rank = group_dst_rank;
+    params.group_dst_row = group_dst_row;
+    params.peer_rows = peer_rows;
+  }
   if (panel) {
     rc = encode_map(ctx, &params.map_d, bf16, 2, panel, panel_cols, total_rows, 1, ld_panel, 0, 64, 32, "panel");
     if (rc) return rc;
@@ -620,6 +631,7 @@ int grouped_gemm(b200gemm_context* ctx, cudaStream_t stream, const void* a, int6
   const int grid = static_cast<int>(std::min<int64_t>(max_items, units)) * 2;
   if (glu) return launch_kernel<2, kEpiBf16GroupedGlu, kSchedGrouped>(ctx, params, grid, stream);
   if (act_bwd) return launch_kernel<2, kEpiBf16GroupedActBwd, kSchedGrouped>(ctx, params, grid, stream);
+  if (peer_out) return launch_kernel<2, kEpiBf16GroupedPeer, kSchedGrouped>(ctx, params, grid, stream);
   return launch_kernel<2, kEpiBf16Grouped, kSchedGrouped>(ctx, params, grid, stream);
 }
 
@@ -1099,6 +1111,43 @@ int b200gemm_moe_ep_plan(b200gemm_handle_t h, void* stream, const int32_t* all_c
                                                                       group_offsets, group_b_index);
   CUDA_TRY(cudaGetLastError());
   return B200GEMM_OK;
+}
+
+int b200gemm_moe_ep_return_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts, int32_t world,
+                                int32_t rank, int32_t experts, int32_t* group_dst_rank, int32_t* group_dst_row) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!all_counts || !group_dst_rank || !group_dst_row) return fail(B200GEMM_ERR_INVALID, "null pointer");
+  if (world < 1 || world > kMoeMaxPeers || rank < 0 || rank >= world)
+    return fail(B200GEMM_ERR_SHAPE, "world must be in [1, %d] and rank inside it", kMoeMaxPeers);
+  if (experts < world || experts > kMaxGroups || experts % world)
+    return fail(B200GEMM_ERR_SHAPE, "experts must be a multiple of world and at most %d", kMaxGroups);
+  moe_ep_return_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(all_counts, world, rank, experts,
+                                                                               group_dst_rank, group_dst_row);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
+int b200gemm_grouped_gemm_peer(b200gemm_handle_t h, void* stream, const void* a, int64_t lda, const void* b,
+                               int32_t b_layout, int64_t ldb, int64_t batch_stride_b, int32_t b_count,
+                               const int32_t* group_b_index, void* const* peer_out, int32_t world,
+                               int64_t ld_out, int64_t out_rows, const int32_t* group_dst_rank,
+                               const int32_t* group_dst_row, const int32_t* offsets, int32_t groups,
+                               int64_t total_rows, int64_t n, int64_t k) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!peer_out) return fail(B200GEMM_ERR_INVALID, "null peer pointer table");
+  if (world < 1 || world > kMaxPeerRanks) return fail(B200GEMM_ERR_SHAPE, "world must be in [1, %d]", kMaxPeerRanks);
+  if (group_b_index && b_count < 1) return fail(B200GEMM_ERR_SHAPE, "b_count must be positive with a group index");
+  PeerBuffers pb = {};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_out[r] || (reinterpret_cast<uintptr_t>(peer_out[r]) & 15u) != 0)
+      return fail(B200GEMM_ERR_INVALID, "peer pointer %d is null or not 16-byte aligned", r);
+    pb.ptr[r] = static_cast<uint16_t*>(peer_out[r]);
+  }
+  return grouped_gemm(h, static_cast<cudaStream_t>(stream), a, lda, b, b_layout, ldb, batch_stride_b, nullptr,
+                      ld_out, offsets, groups, total_rows, n, k, 0, group_b_index, b_count, nullptr, 0, nullptr, 0,
+                      &pb, group_dst_rank, group_dst_row, out_rows);
 }
 
 int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const uint32_t* selected,

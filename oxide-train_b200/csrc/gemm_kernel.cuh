@@ -75,11 +75,22 @@ enum EpilogueKind : int {
   // C = acc * silu'(saved) (p.act_silu == 2, saved [rows, n]) or, for SwiGLU (p.act_silu == 3,
   // saved = the [rows, 2, n] gate/up panel), C [rows, 2, n] = {acc * up * silu'(gate), acc * silu(gate)}.
   kEpiBf16GroupedActBwd = 8,
+  // Ragged row groups whose results go straight to OTHER GPUs: every group's rows are stored
+  // (plain 16-byte stores, 128 bytes per row and chunk) into the buffer of the rank the rows
+  // came from, at the place that rank's own permutation expects them.  The expert GEMM and the
+  // return leg of the expert-parallel exchange in one kernel: the transfer rides under the MMAs.
+  kEpiBf16GroupedPeer = 9,
 };
 
 __host__ __device__ constexpr bool epi_is_grouped(int epi) {
-  return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu || epi == kEpiBf16GroupedActBwd;
+  return epi == kEpiBf16Grouped || epi == kEpiBf16GroupedGlu || epi == kEpiBf16GroupedActBwd ||
+         epi == kEpiBf16GroupedPeer;
 }
+
+constexpr int kMaxPeerRanks = 8;
+struct PeerBuffers {
+  uint16_t* ptr[kMaxPeerRanks];
+};
 
 enum ScheduleKind : int { kSchedDense = 0, kSchedCeForward = 1, kSchedGrouped = 2, kSchedGroupedWgrad = 3 };
 
@@ -132,6 +143,13 @@ struct GemmParams {
                        // kEpiBf16GroupedActBwd: 2 = SiLU backward, 3 = SwiGLU backward
   const uint16_t* saved;   // kEpiBf16GroupedActBwd: what the forward kept ([rows, n] or [rows, 2, n])
   long long ld_saved;
+  // ---- kEpiBf16GroupedPeer: group g's rows go to peer_out.ptr[group_dst_rank[g]], rows
+  // group_dst_row[g] + (row - first row of g), row stride ldc; rows at or beyond peer_rows are
+  // not written (device status 105)
+  PeerBuffers peer_out;
+  const int* group_dst_rank;
+  const int* group_dst_row;
+  long long peer_rows;
   // ---- kEpiBf16GroupedGlu (the reference's [rows, 2, ff] gate/up panel, gpu/ops/src/lib.rs:1149-1171)
   int glu_cols;        // ff: B's "up" block starts this many columns after its "gate" block; C is [rows, ff]
   CUtensorMap map_d;   // optional second output, the bf16 panel {2 * ff, rows, 1}, box {64, 32, 1};
@@ -155,6 +173,7 @@ struct Tile {
   int k0;          // first element of the tile's walk along K (kb_begin * 64 except in kSchedGroupedWgrad)
   int k_tail;      // elements of the walk's last K block that belong to it (64 = all of them)
   int first, last;  // position inside a kSchedCeForward run
+  int group, group_row0;   // kSchedGrouped: the tile's group and that group's first row
 };
 
 // Iterates the tiles of one CTA/cluster.  All three roles run the same
@@ -264,6 +283,8 @@ struct TileWalk {
       t.m0 = group_row_start[g] + (tm - group_tile_start[g]) * kTileM;
       t.m_end = group_row_start[g + 1];
       t.tile_n = tn;
+      t.group = g;
+      t.group_row0 = group_row_start[g];
     }
     if constexpr (kSched == kSchedGroupedWgrad) {
       // item -> (row chunk over all groups, output tile) with the tile fastest: the clusters
@@ -371,7 +392,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     prefetch_tensormap(&p.map_a);
     prefetch_tensormap(&p.map_b);
     if (kEpi == kEpiF32Tma || kEpi == kEpiF32DualBf16 || kEpi == kEpiBf16Tma || kEpi == kEpiCeBackward ||
-        epi_is_grouped(kEpi))
+        (epi_is_grouped(kEpi) && kEpi != kEpiBf16GroupedPeer))
       prefetch_tensormap(&p.map_c);
     if (kEpi == kEpiBf16GroupedGlu || kEpi == kEpiF32DualBf16 || (kEpi == kEpiBf16Grouped && p.d_bf16))
       prefetch_tensormap(&p.map_d);
@@ -695,6 +716,36 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         // for a warp that straddles the end of its group, write this thread's row directly.
         auto put_chunk = [&](const CUtensorMap* map, uint16_t* base_ptr, long long ld, int col, int col_end,
                              const uint32_t* packed) {
+          if constexpr (kEpi == kEpiBf16GroupedPeer) {
+            // Through shared memory, so that eight lanes write one row's 128 bytes side by side
+            // (four rows per store instruction) instead of every lane writing 16 bytes of a row
+            // of its own: the stores cross NVLink, where the size of a write matters.
+            const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
+            stage_row(buf, packed);
+            __syncwarp();
+            uint16_t* dst_base = p.peer_out.ptr[p.group_dst_rank[t.group]];
+            const long long dst_row0 = static_cast<long long>(p.group_dst_row[t.group]) + (row0 - t.group_row0);
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3);
+              const int j = lane & 7;
+              uint32_t v0, v1, v2, v3;
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                           : "r"(buf + rr * 128u + ((static_cast<uint32_t>(j) ^ (rr & 7u)) << 4)));
+              const long long dr = dst_row0 + rr;
+              if (row0 + rr < t.m_end && col + 8 * j + 8 <= col_end) {
+                if (dr < p.peer_rows) {
+                  *reinterpret_cast<uint4*>(dst_base + dr * ld + col + 8 * j) = make_uint4(v0, v1, v2, v3);
+                } else {
+                  atomicCAS(p.status, 0, kDevInboxOverflow);
+                }
+              }
+            }
+            __syncwarp();
+            ++chunk_counter;
+            return;
+          }
           if (warp_inside) {
             const uint32_t buf = my_epi + (chunk_counter & 1u) * kEpiBufBytes;
             if (lane == 0) tma_wait_group_read<1>();

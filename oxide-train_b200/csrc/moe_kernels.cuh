@@ -625,6 +625,23 @@ __global__ void moe_ep_plan_kernel(const int* __restrict__ all_counts, int world
   }
 }
 
+// Where the results of MY inbox's groups go when the owner sends them back itself (the
+// grouped GEMM with peer stores in its epilogue): group g = (source rank s, local expert e)
+// returns to rank s, whose own permutation holds the rows of expert E = rank * local + e from
+// row sum over E' < E of all_counts[s][E'] on, in slot order -- the order they sit in my inbox.
+__global__ void moe_ep_return_plan_kernel(const int* __restrict__ all_counts, int world, int rank,
+                                          int experts, int* __restrict__ group_dst_rank,
+                                          int* __restrict__ group_dst_row) {
+  const int local = experts / world;
+  for (int g = threadIdx.x; g < experts; g += blockDim.x) {
+    const int s = g / local, e = g - s * local;
+    int base = 0;
+    for (int other = 0; other < rank * local + e; ++other) base += all_counts[s * experts + other];
+    group_dst_rank[g] = s;
+    group_dst_row[g] = base;
+  }
+}
+
 // Dispatch: one warp per token reads the token's row once and stores it into the
 // inbox of each selected expert's owner (a plain peer store over NVLink, or a
 // local store when this rank owns the expert).

@@ -115,6 +115,16 @@ class DeviceOps:
     def combine(self, y_permuted, routing, residual, out_dtype):
         return self._moe.combine(self.gemm, y_permuted, routing, residual, out_dtype)
 
+    def combine_into(self, y_permuted, routing, residual, out):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        L.check(self.gemm._lib.b200gemm_moe_combine(
+            self.gemm._h, _stream_ptr(), y_permuted.data_ptr(), routing.dest_row.data_ptr(),
+            routing.gate_weights.data_ptr(), residual.data_ptr() if residual is not None else None,
+            routing.tokens, routing.top_k, y_permuted.shape[1], out.data_ptr(),
+            L.OUT_F32 if out.dtype == torch.float32 else L.OUT_BF16))
+        return out
+
     def grouped_indexed(self, a, b, offsets, group_b_index, silu):
         from . import _lib as L
         from .gemm import _stream_ptr
@@ -151,6 +161,28 @@ class DeviceOps:
                                                     rank, experts, dst_base.data_ptr(), offsets.data_ptr(),
                                                     index.data_ptr()))
         return dst_base, offsets, index
+
+    def ep_return_plan(self, all_counts, world, rank, experts):
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        dev = all_counts.device
+        dst_rank = torch.empty(experts, dtype=torch.int32, device=dev)
+        dst_row = torch.empty(experts, dtype=torch.int32, device=dev)
+        L.check(self.gemm._lib.b200gemm_moe_ep_return_plan(self.gemm._h, _stream_ptr(), all_counts.data_ptr(), world,
+                                                           rank, experts, dst_rank.data_ptr(), dst_row.data_ptr()))
+        return dst_rank, dst_row
+
+    def grouped_indexed_peer(self, a, b, offsets, group_b_index, peer_ptrs, world, ld_out, out_rows, dst_rank, dst_row):
+        """The expert GEMM whose epilogue stores each (source rank, expert) group's rows into that
+        rank's buffer (``peer_ptrs``: every rank's buffer as seen from here)."""
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        rows, k = a.shape
+        n = b.shape[2]
+        L.check(self.gemm._lib.b200gemm_grouped_gemm_peer(
+            self.gemm._h, _stream_ptr(), a.data_ptr(), a.stride(0), b.data_ptr(), L.MN_MAJOR, b.stride(1),
+            b.stride(0), b.shape[0], group_b_index.data_ptr(), peer_ptrs, world, ld_out, out_rows,
+            dst_rank.data_ptr(), dst_row.data_ptr(), offsets.data_ptr(), group_b_index.numel(), rows, n, k))
 
     def ep_push(self, x, routing, dst_base, peer_ptrs, inbox_rows, world, experts):
         from . import _lib as L
@@ -397,12 +429,16 @@ class ExpertParallelMoe:
 
     ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
 
-    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces: int = 1,
-                 use_peer_copies: bool = False, exchange: str = "nccl"):
+    def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces=1,
+                 use_peer_copies: bool = False, exchange: str = "nccl", return_path: str = "pull"):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
         self.pieces, self._side = pieces, None
         self.use_peer_copies, self._peer, self._peer_shape, self._index = use_peer_copies, None, None, None
         self.exchange, self._dev = exchange, None       # "nccl" | "device" (peer stores / loads)
+        # device exchange, how results come back: "pull" = the token's rank reads each result row
+        # from its owner (peer loads) while it combines; "push" = the owner's down-projection GEMM
+        # stores its rows into the token rank's buffer from its epilogue, and the combine is local
+        self.return_path = return_path
         self.reserve_sms = 4                            # SMs kept free of GEMM CTAs in the device path
         self.world, self.rank = _world(group)
         if experts % self.world:
@@ -460,8 +496,20 @@ class ExpertParallelMoe:
                     a_res[r] = h_res.get_buffer(r, (total, d_out), torch.bfloat16).data_ptr() + first[p] * d_out * 2
                 ptrs_in.append(a_in)
                 ptrs_res.append(a_res)
-            self._dev = {"key": key, "inbox": inbox, "results": results, "handles": (h_in, h_res),
-                         "ptrs_in": ptrs_in, "ptrs_res": ptrs_res,
+            pair_rows = [rows * self.top_k for _, rows in slices]
+            pair_first = [sum(pair_rows[:i]) for i in range(len(pair_rows))]
+            returned = symm_mem.empty((sum(pair_rows), d_out), dtype=torch.bfloat16, device=x.device)
+            h_back = symm_mem.rendezvous(returned, grp.group_name)
+            ptrs_back = []
+            for p in range(len(slices)):
+                a_back = (C.c_void_p * self.world)()
+                for r in range(self.world):
+                    a_back[r] = (h_back.get_buffer(r, (sum(pair_rows), d_out), torch.bfloat16).data_ptr()
+                                 + pair_first[p] * d_out * 2)
+                ptrs_back.append(a_back)
+            self._dev = {"key": key, "inbox": inbox, "results": results, "handles": (h_in, h_res, h_back),
+                         "ptrs_in": ptrs_in, "ptrs_res": ptrs_res, "returned": returned, "ptrs_back": ptrs_back,
+                         "pair_rows": pair_rows, "pair_first": pair_first,
                          "hidden": torch.empty((total, ff), dtype=torch.bfloat16, device=x.device),
                          "token": torch.zeros(1, device=x.device)}
         dv = self._dev
@@ -504,24 +552,37 @@ class ExpertParallelMoe:
                 allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
                 dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
                 dst_base, offsets, index = self.ops.ep_plan(allc, self.world, self.rank, self.experts)
+                back = (self.ops.ep_return_plan(allc, self.world, self.rank, self.experts)
+                        if self.return_path == "push" else ())
                 self.ops.ep_push(x[sl], r, dst_base, dv["ptrs_in"][p], caps[p], self.world, self.experts)
                 dist.all_reduce(dv["token"], group=self.group)        # every rank's rows have landed
                 if st is not main:
-                    for tns in (allc, dst_base, offsets, index):
+                    for tns in (allc, dst_base, offsets, index) + tuple(back):
                         tns.record_stream(st)
-            routed.append((sl, r, dst_base, offsets, index))
+            routed.append((sl, r, dst_base, offsets, index, back))
         # Stage 2, every slice: expert GEMMs on what arrived, barrier, pull + combine.
-        for p, (sl, r, dst_base, offsets, index) in enumerate(routed):
+        for p, (sl, r, dst_base, offsets, index, back) in enumerate(routed):
             st = streams[p % len(streams)]
             with torch.cuda.stream(st):
                 inbox = dv["inbox"][first[p]:first[p] + caps[p]]
                 hidden = dv["hidden"][first[p]:first[p] + caps[p]]
                 res = dv["results"][first[p]:first[p] + caps[p]]
                 self.ops.grouped_indexed_into(inbox, self.w_up, offsets, index, True, hidden)
-                self.ops.grouped_indexed_into(hidden, self.w_down, offsets, index, False, res)
-                dist.all_reduce(dv["token"], group=self.group)        # every rank's results are complete
-                self.ops.ep_pull_combine(dv["ptrs_res"][p], r, dst_base, residual[sl] if residual is not None else None,
-                                         caps[p], self.world, self.experts, d_out, out[sl])
+                res_in = residual[sl] if residual is not None else None
+                if self.return_path == "push":
+                    # the down projection sends its rows home from its epilogue; after the
+                    # barrier this rank's own buffer holds its tokens' results in its own order
+                    rows_back = dv["pair_rows"][p]
+                    self.ops.grouped_indexed_peer(hidden, self.w_down, offsets, index, dv["ptrs_back"][p], self.world,
+                                                  d_out, rows_back, back[0], back[1])
+                    dist.all_reduce(dv["token"], group=self.group)    # every rank's results have landed
+                    mine = dv["returned"][dv["pair_first"][p]:dv["pair_first"][p] + rows_back]
+                    self.ops.combine_into(mine, r, res_in, out[sl])
+                else:
+                    self.ops.grouped_indexed_into(hidden, self.w_down, offsets, index, False, res)
+                    dist.all_reduce(dv["token"], group=self.group)    # every rank's results are complete
+                    self.ops.ep_pull_combine(dv["ptrs_res"][p], r, dst_base, res_in,
+                                             caps[p], self.world, self.experts, d_out, out[sl])
                 if st is not main:
                     out.record_stream(st)
         for st in streams:
@@ -529,7 +590,7 @@ class ExpertParallelMoe:
                 main.wait_stream(st)
         # `rows_received` stays on the device (one int32 per slice: the last group offset);
         # rows_received() reads it when a report wants it.
-        self.last = {"routing": routed[0][1], "pieces": pieces, "exchange": "device",
+        self.last = {"routing": routed[0][1], "pieces": pieces, "exchange": "device", "return_path": self.return_path,
                      "rows_received": None, "rows_sent": n * self.top_k,
                      "group_offsets": [t[3] for t in routed]}
         return out

@@ -63,6 +63,37 @@ def test_emulated_ranks_match_single_gpu_moe(pkg, oracle, world, experts, top_k,
         assert torch.allclose(out, want[r], atol=1e-5, rtol=1e-5), float((out - want[r]).abs().max())
     assert gemm.device_status() == 0
 
+    # The return leg fused into the expert GEMM: every owner's down projection stores its rows
+    # straight into the buffer of the rank they came from; each rank then combines its own tokens
+    # from its own buffer with the single-GPU combine.  Same result, to the last bit.
+    pairs = tokens * top_k
+    returned = [torch.full((pairs + 5, d), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptr_back = (C.c_void_p * world)(*[t.data_ptr() for t in returned])
+    for j in range(world):
+        _, offsets, index = plans[j]
+        dst_rank, dst_row = ops.ep_return_plan(counts, world, j, experts)
+        assert np.array_equal(dst_rank.cpu().numpy(), np.repeat(np.arange(world), local))
+        want_row = [c[s, :j * local + e].sum() for s in range(world) for e in range(local)]
+        assert np.array_equal(dst_row.cpu().numpy(), np.array(want_row))
+        ops.grouped_indexed_into(inbox[j], w_up[j * local:(j + 1) * local], offsets, index, True, hidden)
+        ops.grouped_indexed_peer(hidden, w_dn[j * local:(j + 1) * local], offsets, index, ptr_back, world, d,
+                                 pairs, dst_rank, dst_row)
+    for r in range(world):
+        assert torch.isnan(returned[r][pairs:]).all()                          # nothing written behind the routed rows
+        out = ops.combine(returned[r][:pairs], routed[r], xs[r], torch.float32)
+        assert torch.equal(out, pkg.moe.combine(gemm, returned[r][:pairs], routed[r], xs[r]))
+        assert torch.allclose(out, want[r], atol=1e-5, rtol=1e-5), float((out - want[r]).abs().max())
+    assert gemm.device_status() == 0
+    # a return buffer that is too small: the rows beyond it are not written, the status word says so
+    j = world - 1
+    _, offsets, index = plans[j]
+    dst_rank, dst_row = ops.ep_return_plan(counts, world, j, experts)
+    ops.grouped_indexed_peer(hidden, w_dn[j * local:(j + 1) * local], offsets, index, ptr_back, world, d,
+                             max(1, int(c[0, :j * local].sum())), dst_rank, dst_row)
+    with pytest.raises(pkg.B200GemmError):
+        gemm.device_status()
+    assert gemm.device_status() == 0
+
     # an inbox that is too small: rows beyond it are dropped and the status word says so
     # (the last rank's rows come last in every inbox, so some of them must fall beyond the limit)
     small = max(1, int(c[:, :local].sum()) // 2)

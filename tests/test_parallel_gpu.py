@@ -128,6 +128,14 @@ def _worker(rank, port, failures):
             out3 = ep3.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
             assert ep3.last["exchange"] == "device"
             assert torch.allclose(out3, ref, atol=1e-5, rtol=1e-5), float((out3 - ref).abs().max())
+        # ... with the results sent home by the owner's down-projection GEMM itself (peer stores from its epilogue)
+        ep5 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=2, exchange="device",
+                                    return_path="push")
+        for _ in range(2):
+            out5 = ep5.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert ep5.last["return_path"] == "push"
+            assert torch.allclose(out5, ref, atol=1e-5, rtol=1e-5), float((out5 - ref).abs().max())
         # ... and with token slices of different sizes (a short first and last slice)
         ep4 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
                                     dn[rank * local:(rank + 1) * local].contiguous(), pieces=[1, 2, 1], exchange="device")
