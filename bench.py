@@ -615,12 +615,14 @@ def sharded_line(torch, dist, w, workload, world, ms, clocks, peaks, extra_e2e=N
         ep = w.extra
         dev = w.host_in.device
         recv = torch.tensor([float(ep.rows_received()), float(ep.last.get("rows_sent", 0)),
-                             float(ep.last.get("rows_sent_remote", -1))], device=dev)
+                             float(ep.rows_sent_remote())], device=dev)
         allr = [torch.zeros_like(recv) for _ in range(world)]
         dist.all_gather(allr, recv)
         rows = [float(t[0].item()) for t in allr]
         out["moe_rows_received_per_rank"] = rows
         out["moe_rows_routed_per_rank"] = [float(t[1].item()) for t in allr]
+        out["moe_rows_sent_to_other_ranks"] = [float(t[2].item()) for t in allr]
+        out["moe_return_path"] = ep.last.get("return_path")
         out["moe_load_imbalance_max_over_mean"] = max(rows) / (sum(rows) / len(rows))
     return out
 
@@ -702,7 +704,8 @@ def run_sharded(args):
                      "algorithmic_flops_per_step": w.flops},
         "exchange_timeline": timeline,
     }
-    for key in ("moe_rows_received_per_rank", "moe_rows_routed_per_rank", "moe_load_imbalance_max_over_mean"):
+    for key in ("moe_rows_received_per_rank", "moe_rows_routed_per_rank", "moe_rows_sent_to_other_ranks",
+                "moe_load_imbalance_max_over_mean", "moe_return_path"):
         if key in sub:
             line[key] = sub[key]
     if rank == 0:

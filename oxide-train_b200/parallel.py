@@ -592,8 +592,17 @@ class ExpertParallelMoe:
         # rows_received() reads it when a report wants it.
         self.last = {"routing": routed[0][1], "pieces": pieces, "exchange": "device", "return_path": self.return_path,
                      "rows_received": None, "rows_sent": n * self.top_k,
-                     "group_offsets": [t[3] for t in routed]}
+                     "group_offsets": [t[3] for t in routed], "accepted_counts": [t[1].accepted_counts for t in routed]}
         return out
+
+    def rows_sent_remote(self) -> int:
+        """Routed rows of the last forward whose expert lives on another rank (synchronises)."""
+        local = self.experts // self.world
+        total = 0
+        for counts in self.last.get("accepted_counts", []):
+            c = counts.to(torch.int64)
+            total += int((c.sum() - c[self.rank * local:(self.rank + 1) * local].sum()).item())
+        return total
 
     def rows_received(self) -> int:
         """Rows this rank's experts multiplied in the last forward (synchronises when the
