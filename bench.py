@@ -373,6 +373,7 @@ MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
 MOE_PIECES = 2                 # set from --moe-pieces: token slices of the expert-parallel step
 MOE_RETURN = "pull"            # set from --moe-return
+MLP_PIECES = [1, 3, 4, 4, 3, 1]   # set from --mlp-pieces (several GPUs)
 
 
 class Sharded:
@@ -478,7 +479,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         how = MLP_EXCHANGE if world > 1 else "nccl"
         # rows go through in pieces; on several GPUs short pieces at both ends, because what no GEMM
         # covers is the exchange of the last piece (forward and backward) and the gather of the first
-        pieces = 4 if world == 1 else [1, 3, 4, 4, 3, 1]
+        pieces = 4 if world == 1 else MLP_PIECES
         mlp = par.TensorParallelMlp(ops, w1, w2, chunks=pieces, partial_dtype=bf, exchange=how)
         dy_local = rnd((m // world, d), 0.01)
         dw1 = torch.zeros((d, cols), device=dev, dtype=f32)
@@ -868,9 +869,10 @@ def run_only(args):
     x = torch.randn((m, i), device=dev).to(bf)
     w = (torch.randn((i, o), device=dev) * 0.02).to(bf)
     dy = (torch.randn((m, o), device=dev) * 0.01).to(bf)
+    tile = {"auto": 0, "wide": pkg._lib.FLAG_WIDE_TILE, "narrow": pkg._lib.FLAG_NARROW_TILE}[args.tile]
     if kind == "forward":
         out = torch.empty((m, o), device=dev, dtype=bf if name == "lm_head" else f32)
-        fn = lambda: gemm.gemm(x, w, out, transposed_b=True)
+        fn = lambda: gemm.gemm(x, w, out, transposed_b=True, flags=0 if name == "lm_head" else tile)
     elif kind == "forward_dual":            # fp32 result + its bf16 copy from one launch
         out = torch.empty((m, o), device=dev, dtype=f32)
         out16 = torch.empty((m, o), device=dev, dtype=bf)
@@ -884,10 +886,10 @@ def run_only(args):
             gemm.convert_f32_to_bf16(out, out16)
     elif kind == "input_grad":
         out = torch.empty((m, i), device=dev, dtype=f32)
-        fn = lambda: gemm.f32_store(dy, w, out)
+        fn = lambda: gemm.f32_store(dy, w, out, flags=tile)
     else:
         out = torch.zeros((i, o), device=dev, dtype=f32)
-        fn = lambda: gemm.f32_accumulate_transposed(x, dy, out)
+        fn = lambda: gemm.f32_accumulate_transposed(x, dy, out, flags=tile)
     for _ in range(args.warmup):
         fn()
     torch.cuda.synchronize()
@@ -1033,6 +1035,8 @@ def main():
                          "lm_head.fused_backward, moe.forward, moe.gated_forward, moe.backward, moe.gated_backward, "
                          "mlp_gate_up.{swiglu,swiglu_no_panel,plain_gemm_only,unfused}")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
+    ap.add_argument("--tile", default="auto", choices=["auto", "wide", "narrow"],
+                    help="with --only <gemm>.<kind>: 256x512 tiles per CTA pair, 256x256, or the planner's choice")
     ap.add_argument("--scheduler", default="dynamic", choices=["static", "dynamic"],
                     help="how the persistent kernels hand out tiles (see b200gemm_set_scheduler)")
     ap.add_argument("--workload", default="dense_step", choices=["dense_step", "lmhead", "moe", "tp_mlp"],
@@ -1045,11 +1049,15 @@ def main():
     ap.add_argument("--moe-return", default="pull", choices=["pull", "push"],
                     help="expert-parallel MoE: results read by the token's rank while it combines (pull), or stored "
                          "into the token rank's buffer by the owner's down-projection GEMM (push)")
+    ap.add_argument("--mlp-pieces", default="1,3,4,4,3,1",
+                    help="tensor-parallel MLP on several GPUs: row pieces, a count or comma-separated weights")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
     args = ap.parse_args()
-    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN
+    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN, MLP_PIECES
     MOE_RETURN = args.moe_return
+    parts = [int(v) for v in str(args.mlp_pieces).split(",")]
+    MLP_PIECES = parts[0] if len(parts) == 1 else parts
     MLP_EXCHANGE, HEAD_EXCHANGE = args.mlp_exchange, args.head_exchange
     parts = [int(v) for v in str(args.moe_pieces).split(",")]
     MOE_PIECES = parts[0] if len(parts) == 1 else parts

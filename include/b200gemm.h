@@ -66,6 +66,8 @@ typedef enum { B200GEMM_STORE = 0, B200GEMM_ACCUMULATE = 1 } b200gemm_mode_t;
 /* flags */
 #define B200GEMM_FLAG_CTA_GROUP_1 0x1u /* force one-CTA 128x256 tiles               */
 #define B200GEMM_FLAG_CTA_GROUP_2 0x2u /* force CTA-pair 256x256 tiles (cta_group::2) */
+#define B200GEMM_FLAG_WIDE_TILE   0x4u /* force 256x512 tiles per CTA pair (fp32 output; chosen by itself for deep reductions) */
+#define B200GEMM_FLAG_NARROW_TILE 0x8u /* never use 256x512 tiles */
 
 /*
  * One launch: for e in [0, batch):  C[e][m, n] (=|+=) A[e] * B[e]^T

@@ -17,7 +17,7 @@ OK, ERR_INVALID, ERR_SHAPE, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
 K_MAJOR, MN_MAJOR = 0, 1
 OUT_F32, OUT_BF16 = 0, 1
 STORE, ACCUMULATE = 0, 1
-FLAG_CTA_GROUP_1, FLAG_CTA_GROUP_2 = 0x1, 0x2
+FLAG_CTA_GROUP_1, FLAG_CTA_GROUP_2, FLAG_WIDE_TILE, FLAG_NARROW_TILE = 0x1, 0x2, 0x4, 0x8
 OP_NN, OP_NT, OP_TN = 0, 1, 2
 
 

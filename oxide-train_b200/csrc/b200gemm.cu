@@ -61,7 +61,7 @@ struct b200gemm_context {
   // staging for b200gemm_gemm_host
   void* stage[3] = {nullptr, nullptr, nullptr};
   size_t stage_bytes[3] = {0, 0, 0};
-  bool smem_opt_in[2][12][4] = {};   // [cta_group - 1][epilogue kind][schedule kind]: one per kernel instantiation
+  bool smem_opt_in[3][12][4] = {};   // [cta_group - 1, or 2 = wide CTA-pair tiles][epilogue kind][schedule kind]: one per kernel instantiation
   // per-segment expert counts of b200gemm_moe_route: one buffer per stream, so that routing
   // calls issued on different streams can overlap on the GPU without sharing scratch
   struct Scratch {
@@ -119,6 +119,7 @@ struct Plan {
   int smem = 0;
   int epi = kEpiF32Tma;
   int reduce = 0;
+  int wide = 0;              // 256 x 512 tiles per CTA pair (deep reductions, fp32 output)
   int64_t lda = 0, ldb = 0, ldc = 0, bsa = 0, bsb = 0, bsc = 0;
 };
 
@@ -179,13 +180,29 @@ int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
   p->cta_group = want2 ? 2 : (want1 ? 1 : (d->m > 128 ? 2 : 1));
   p->tile_m = kTileMCta * p->cta_group;
   p->tiles_m = ceil_div(d->m, p->tile_m);
-  p->tiles_n = ceil_div(d->n, kTileN);
   p->k_blocks = ceil_div(d->k, kBlockK);
+  const bool f32 = d->out_type == B200GEMM_OUT_F32;
+  const int units = std::max(1, ctx->sm_count / p->cta_group);
+  // Wide tiles: one 512-column accumulator per CTA pair, a third less operand traffic per FLOP,
+  // no overlap of a tile's drain with the next tile's MMAs -- so only where a tile's reduction is
+  // so deep that the drain does not matter (weight gradients over the tokens, K >= 8192 per item)
+  // and the columns fill whole wide tiles well.
+  const bool want_wide = (d->flags & B200GEMM_FLAG_WIDE_TILE) != 0;
+  const bool no_wide = (d->flags & B200GEMM_FLAG_NARROW_TILE) != 0;
+  if (want_wide && (p->cta_group != 2 || !f32)) return fail(B200GEMM_ERR_UNSUPPORTED, "wide tiles need CTA pairs and fp32 output");
+  p->wide = 0;
+  if (p->cta_group == 2 && f32 && !no_wide) {
+    const int64_t wide_tiles = static_cast<int64_t>(d->batch) * p->tiles_m * ceil_div(d->n, 2 * kTileN);
+    const int64_t slices = std::max<int64_t>(1, (units + wide_tiles - 1) / wide_tiles);   // K slices it would take to fill the machine
+    const bool deep = p->k_blocks / slices >= 128;
+    const bool fills = d->n % (2 * kTileN) == 0 || d->n >= 8 * kTileN;
+    p->wide = want_wide || (deep && fills && d->split_k == 0) ? 1 : 0;
+  }
+  const int tile_n = p->wide ? 2 * kTileN : kTileN;
+  p->tiles_n = ceil_div(d->n, tile_n);
   const int64_t items = static_cast<int64_t>(d->batch) * p->tiles_m * p->tiles_n;
   if (items > (1ll << 30)) return fail(B200GEMM_ERR_SHAPE, "too many tiles");
-  const int units = std::max(1, ctx->sm_count / p->cta_group);
 
-  const bool f32 = d->out_type == B200GEMM_OUT_F32;
   p->split_k = 1;
   if (f32) {
     if (d->split_k == 0) p->split_k = choose_split_k(items, p->k_blocks, units);
@@ -207,7 +224,7 @@ int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
   }
   const int64_t work = items * p->split_k;
   p->grid = static_cast<int>(std::min<int64_t>(work, units)) * p->cta_group;
-  p->smem = p->cta_group == 2 ? GemmCfg<2>::kSmemBytes : GemmCfg<1>::kSmemBytes;
+  p->smem = p->cta_group == 2 ? (p->wide ? GemmCfg<2, true>::kSmemBytes : GemmCfg<2>::kSmemBytes) : GemmCfg<1>::kSmemBytes;
   return B200GEMM_OK;
 }
 
@@ -229,9 +246,9 @@ int sched_counters_for(b200gemm_context* ctx, cudaStream_t stream, int** out) {
   return B200GEMM_OK;
 }
 
-template <int CG, int EPI, int SCHED>
+template <int CG, int EPI, int SCHED, bool WIDE = false>
 int launch_kernel(b200gemm_context* ctx, const GemmParams& params_in, int grid, cudaStream_t stream) {
-  auto kernel = gemm_tcgen05_kernel<CG, EPI, SCHED>;
+  auto kernel = gemm_tcgen05_kernel<CG, EPI, SCHED, WIDE>;
   GemmParams params = params_in;
   const bool static_only = params.sched_counter == kStaticScheduleOnly;
   params.sched_counter = nullptr;
@@ -241,16 +258,16 @@ int launch_kernel(b200gemm_context* ctx, const GemmParams& params_in, int grid, 
   }
   // Per-device opt-in to > 48 KiB dynamic shared memory, once per kernel
   // (the reference's opt_in_dynamic_smem, host.rs:485-505).
-  bool& ready = ctx->smem_opt_in[CG - 1][EPI][SCHED];
+  bool& ready = ctx->smem_opt_in[CG - 1 + (WIDE ? 2 : 0)][EPI][SCHED];
   if (!ready) {
     CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  GemmCfg<CG>::kSmemBytes));
+                                  GemmCfg<CG, WIDE>::kSmemBytes));
     ready = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = GemmCfg<CG>::kSmemBytes;
+  cfg.dynamicSmemBytes = GemmCfg<CG, WIDE>::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -291,6 +308,7 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
     rc = encode_map(ctx, &params.map_c, bf16, 2, d->c, d->n, d->m, d->batch, plan.ldc, plan.bsc, 64, 32, "C");
   if (rc) return rc;
 
+  if (dual_bf16 && plan.wide) return fail(B200GEMM_ERR_UNSUPPORTED, "the dual-output form does not use wide tiles");
   if (dual_bf16) {
     rc = encode_map(ctx, &params.map_d, bf16, 2, dual_bf16, d->n, d->m, d->batch, ld_dual, batch_stride_dual, 64, 32,
                     "bf16 copy of C");
@@ -333,7 +351,9 @@ int launch_gemm(b200gemm_context* ctx, cudaStream_t stream, const b200gemm_desc_
     }
   }
   switch (plan.epi) {
-    case kEpiF32Tma: return launch_one<2, kEpiF32Tma>(ctx, params, plan, stream);
+    case kEpiF32Tma:
+      if (plan.wide) return launch_kernel<2, kEpiF32Tma, kSchedDense, true>(ctx, params, plan.grid, stream);
+      return launch_one<2, kEpiF32Tma>(ctx, params, plan, stream);
     case kEpiBf16Tma: return launch_one<2, kEpiBf16Tma>(ctx, params, plan, stream);
     default: return launch_one<2, kEpiBf16Rmw>(ctx, params, plan, stream);
   }

@@ -98,13 +98,20 @@ __host__ __device__ constexpr bool sched_is_grouped(int sched) {
   return sched == kSchedGrouped || sched == kSchedGroupedWgrad;
 }
 
-template <int kCtaGroup>
+// kWide (CTA pairs only): a 256 x 512 tile per pair -- ONE 512-column accumulator instead of two
+// of 256, two UMMAs (N = 256 each) per K = 16 step, 48 KiB stages.  A third less operand traffic
+// from L2 per FLOP (A is loaded once per 512 columns), at the price of the ping-pong: the next
+// tile's MMAs wait for this tile's drain.  For deep reductions only (weight gradients).
+template <int kCtaGroup, bool kWide = false>
 struct GemmCfg {
-  static constexpr int kBRowsCta = kTileN / kCtaGroup;            // B rows this CTA loads
+  static_assert(!kWide || kCtaGroup == 2, "wide tiles are a CTA-pair configuration");
+  static constexpr int kTileNCfg = kWide ? 2 * kTileN : kTileN;   // output columns per tile
+  static constexpr int kBRowsCta = kTileNCfg / kCtaGroup;         // B rows this CTA loads
   static constexpr int kABytes = kTileMCta * kBlockK * 2;         // 16 KiB
   static constexpr int kBBytes = kBRowsCta * kBlockK * 2;         // 32 / 16 KiB
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kCtaGroup == 1 ? 4 : 6;          // 192 KiB of operand ring
+  static constexpr int kStages = (kCtaGroup == 1 || kWide) ? 4 : 6;   // 192 KiB of operand ring
+  static constexpr int kAccumulators = kWide ? 1 : 2;             // of kTileNCfg TMEM columns each
   static constexpr int kTileM = kTileMCta * kCtaGroup;
   static constexpr int kEpiBytes = 4 * 2 * kEpiBufBytes;          // 32 KiB staging
   static constexpr int kNumBarriers = 2 * kStages + 4;
@@ -341,10 +348,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <int kCtaGroup, int kEpi, int kSched>
+template <int kCtaGroup, int kEpi, int kSched, bool kWide = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = GemmCfg<kCtaGroup>;
+  static_assert(!kWide || (kEpi == kEpiF32Tma && kSched == kSchedDense), "wide tiles: plain fp32 GEMM only");
+  using Cfg = GemmCfg<kCtaGroup, kWide>;
+  constexpr int kTileNK = Cfg::kTileNCfg;        // this instantiation's tile width
   using Walk = TileWalk<kSched, Cfg::kTileM>;
   extern __shared__ uint8_t smem_raw[];
   // kSchedGrouped: [0, groups]: first m-tile of each group; [kMaxGroups + 1, ...]: first row of each group
@@ -447,7 +456,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
         // columns 0-127 and the matching up values in columns 128-255.
         const int n0 = kEpi == kEpiBf16GroupedGlu
                            ? t.tile_n * (kTileN / 2) + static_cast<int>(cta_rank) * p.glu_cols
-                           : t.tile_n * kTileN + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? Cfg::kBRowsCta : 0);
+                           : t.tile_n * kTileNK + static_cast<int>(cta_rank) * (kCtaGroup == 2 ? kTileN / 2 : 0);
         const int a_batch = sched_is_grouped(kSched) ? 0 : t.batch;   // grouped A is one [rows, K] matrix
         const int b_batch = kSched == kSchedGroupedWgrad ? 0 : t.batch;   // and so is a weight gradient's B
         for (int kb = t.kb_begin; kb < t.kb_begin + t.kb_count; ++kb, ++g) {
@@ -470,12 +479,20 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
               for (int i = 0; i < kTileMCta / 64; ++i)
                 tma_load_3d<kCtaGroup>(a_dst + i * kSubtileBytes, &p.map_a, fb, m0 + 64 * i, k0, a_batch);
             }
-            if (!p.b_mn) {
-              tma_load_3d<kCtaGroup>(b_dst, &p.map_b, fb, k0, n0, b_batch);
-            } else {
+            // A wide tile is two 256-column halves: this CTA's 128 rows of B for each of them,
+            // one after the other in the stage (the second UMMA of a K step reads the second).
 #pragma unroll
-              for (int i = 0; i < Cfg::kBRowsCta / 64; ++i)
-                tma_load_3d<kCtaGroup>(b_dst + i * kSubtileBytes, &p.map_b, fb, n0 + 64 * i, k0, b_batch);
+            for (int half = 0; half < (kWide ? 2 : 1); ++half) {
+              const int nh = n0 + half * kTileN;
+              const uint32_t bh = b_dst + half * (Cfg::kBBytes / 2);
+              constexpr int kRowsPerHalf = kWide ? kTileN / 2 : Cfg::kBRowsCta;
+              if (!p.b_mn) {
+                tma_load_3d<kCtaGroup>(bh, &p.map_b, fb, k0, nh, b_batch);
+              } else {
+#pragma unroll
+                for (int i = 0; i < kRowsPerHalf / 64; ++i)
+                  tma_load_3d<kCtaGroup>(bh + i * kSubtileBytes, &p.map_b, fb, nh + 64 * i, k0, b_batch);
+              }
             }
           }
           __syncwarp();
@@ -490,7 +507,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     // uniform registers, which is what tcgen05.mma takes its operands from, and
     // the issuing path from one MMA to the next stays short.
     if (cta_rank == 0) {
-      const uint32_t idesc = make_idesc_bf16(Cfg::kTileM, kTileN, p.a_mn != 0, p.b_mn != 0);
+      const uint32_t idesc = make_idesc_bf16(Cfg::kTileM, kTileN, p.a_mn != 0, p.b_mn != 0);   // one UMMA: N = 256
       // K-major: LBO unused (encoded 1), next K=16 slice is 32 bytes along the swizzled row.
       // MN-major: LBO = one 64x64 subtile, next K=16 slice is 16 rows of 128 bytes.
       // The descriptors of stage 0 / slice 0 are built once; every other one differs
@@ -505,12 +522,12 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
       Tile t;
       for (; ok && walk.get(t); walk.next(t), ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+        const int acc = kWide ? 0 : (it & 1);
+        const uint32_t acc_phase = kWide ? (it & 1) : ((it >> 1) & 1);
         ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, p.status, kDevTimeoutMma, abort_flag));
         if (!ok) break;
         tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        const uint32_t d_tmem = tmem_base + acc * kTileNK;
         for (int kb = 0; kb < t.kb_count; ++kb) {
           ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, p.status, kDevTimeoutMma, abort_flag));
           if (!ok) break;
@@ -544,10 +561,21 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
           const uint64_t da = a_desc0 + stage * kStageAdd;
           const uint64_t db = b_desc0 + stage * kStageAdd;
           if (elect_one()) {
-            umma_bf16<kCtaGroup>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
+            if constexpr (!kWide) {
+              umma_bf16<kCtaGroup>(d_tmem, da, db, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 1; k < kBlockK / kUmmaK; ++k)
-              umma_bf16<kCtaGroup>(d_tmem, da + k * a_kadd, db + k * b_kadd, idesc, 1u);
+              for (int k = 1; k < kBlockK / kUmmaK; ++k)
+                umma_bf16<kCtaGroup>(d_tmem, da + k * a_kadd, db + k * b_kadd, idesc, 1u);
+            } else {
+              // two 256-column halves per K step: B's second half sits half a B stage further on
+              constexpr uint64_t kHalfB = (Cfg::kBBytes / 2) >> 4;
+#pragma unroll
+              for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                const uint32_t accumulate = (kb != 0 || k != 0) ? 1u : 0u;
+                umma_bf16<kCtaGroup>(d_tmem, da + k * a_kadd, db + k * b_kadd, idesc, accumulate);
+                umma_bf16<kCtaGroup>(d_tmem + kTileN, da + k * a_kadd, db + kHalfB + k * b_kadd, idesc, accumulate);
+              }
+            }
             umma_commit<kCtaGroup>(empty_bar(stage));   // stage reusable once these MMAs retire
           }
           __syncwarp();
@@ -618,16 +646,16 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     Walk walk(p, group_tile_start, cluster_id, num_clusters, dynamic ? sched_ring : nullptr, abort_flag);
     Tile t;
     for (; ok && walk.get(t); walk.next(t), ++it) {
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+      const int acc = kWide ? 0 : (it & 1);
+      const uint32_t acc_phase = kWide ? (it & 1) : ((it >> 1) & 1);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, p.status, kDevTimeoutEpilogue, abort_flag)) {
         ok = false;
         break;
       }
       tcgen05_fence_after_sync();
       const int row0 = t.m0 + static_cast<int>(cta_rank) * kTileMCta + lane_base;   // warp's first row
-      const int col0 = t.tile_n * (kEpi == kEpiBf16GroupedGlu ? kTileN / 2 : kTileN);
-      const uint32_t t_acc = tmem_base + (lane_base << 16) + acc * kTileN;
+      const int col0 = t.tile_n * (kEpi == kEpiBf16GroupedGlu ? kTileN / 2 : kTileNK);
+      const uint32_t t_acc = tmem_base + (lane_base << 16) + acc * kTileNK;
 
       auto release_accumulator = [&]() {
         tcgen05_fence_before_sync();
@@ -651,7 +679,7 @@ gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
       };
 
       if constexpr (kEpi == kEpiF32Tma || kEpi == kEpiF32DualBf16) {
-        constexpr int kChunks = kTileN / 32;
+        constexpr int kChunks = kTileNK / 32;
         [[maybe_unused]] uint32_t packed[32];       // kEpiF32DualBf16: two fp32 chunks make one bf16 chunk
         constexpr int kStep = kEpi == kEpiF32DualBf16 ? 2 : 1;
 #pragma unroll 1

@@ -439,3 +439,54 @@ def test_host_buffer_form_leaves_the_callers_padding_alone(pkg, oracle, gemm):
     assert np.all(wide[:, :N] == -7.0) and np.all(wide[:, 2 * N:] == -7.0)
     assert_gemm_close(wide[:, N:2 * N], 2 * ref, "host accumulate into a column slice", rel_fro=2e-5, elem=2e-4)
     assert gemm.device_status() == 0
+
+
+# ---- 256 x 512 tiles per CTA pair (one 512-column accumulator, two UMMAs per K step): chosen by
+# ---- the planner for deep reductions, forced here on small shapes of every kind ------------
+
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, True), (False, True), (True, False)])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 256), (512, 1024, 192), (200, 840, 328), (256, 264, 64)])
+def test_wide_tiles_match_the_oracle(pkg, oracle, gemm, ta, tb, m, n, k):
+    import torch
+    wide = pkg._lib.FLAG_WIDE_TILE
+    a, av = bf16_operand(oracle, (k, m) if ta else (m, k), 95, kind="uniform")
+    b, bv = bf16_operand(oracle, (k, n) if tb else (n, k), 96, kind="uniform")
+    A = np.ascontiguousarray(av.T if ta else av)
+    Bt = np.ascontiguousarray(bv if tb else bv.T)
+    ref = oracle.matmul(A, Bt, THREADS)
+    c = torch.full((m + 8, n), 5.0, dtype=torch.float32, device="cuda")          # canary rows
+    gemm.gemm(a, b, c[:m], transposed_a=ta, transposed_b=tb, flags=wide)
+    assert gemm.device_status() == 0
+    host = c.cpu().numpy()
+    assert np.all(host[m:] == 5.0)
+    assert_gemm_close(host[:m], ref, f"wide store ta={ta} tb={tb}", rel_fro=2e-5, elem=2e-4)
+    narrow = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    gemm.gemm(a, b, narrow, transposed_a=ta, transposed_b=tb, flags=pkg._lib.FLAG_NARROW_TILE | pkg._lib.FLAG_CTA_GROUP_2, split_k=1)
+    assert torch.equal(c[:m], narrow)            # the same products added in the same order: bit-identical
+    gemm.gemm(a, b, c[:m], transposed_a=ta, transposed_b=tb, accumulate=True, flags=wide)
+    assert_gemm_close(c[:m].cpu().numpy(), 2 * ref, "wide accumulate", rel_fro=2e-5, elem=2e-4)
+    assert gemm.device_status() == 0
+
+
+def test_wide_tiles_are_chosen_for_deep_reductions_and_split_k(pkg, oracle, gemm):
+    """The weight-gradient orientation with K = 16384 tokens: the planner picks wide tiles and splits K;
+    many items per CTA pair, exact on integer operands."""
+    import torch
+    m, n, k = 512, 1024, 16384
+    i, j = np.meshgrid(np.arange(k), np.arange(m), indexing="ij")
+    av = (((i * 5 + j * 3) % 7) - 3).astype(np.float32)
+    i, j = np.meshgrid(np.arange(k), np.arange(n), indexing="ij")
+    bv = (((i * 4 + j * 5) % 5) - 2).astype(np.float32)
+    a, b = to_dev_bf16(oracle.bf16_bits(av)), to_dev_bf16(oracle.bf16_bits(bv))
+    c = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    cfg = gemm.launch_config(a, b, c, transposed_a=True, transposed_b=True, accumulate=True)
+    assert cfg["smem_bytes"] == gemm.launch_config(a, b, c, transposed_a=True, transposed_b=True, accumulate=True,
+                                                   flags=pkg._lib.FLAG_WIDE_TILE)["smem_bytes"]       # wide by itself
+    assert cfg["split_k"] > 1
+    gemm.f32_accumulate_transposed(a, b, c)
+    assert gemm.device_status() == 0
+    want = av.astype(np.int64).T @ bv.astype(np.int64)
+    assert np.array_equal(c.cpu().numpy(), want.astype(np.float32))
+    with pytest.raises(pkg.B200GemmError):                      # bf16 output has no wide form
+        gemm.gemm(a, b, torch.zeros((m, n), dtype=torch.bfloat16, device="cuda"), transposed_a=True,
+                  transposed_b=True, flags=pkg._lib.FLAG_WIDE_TILE)
