@@ -192,11 +192,18 @@ int make_plan(const b200gemm_context* ctx, const b200gemm_desc_t* d, Plan* p) {
   if (want_wide && (p->cta_group != 2 || !f32)) return fail(B200GEMM_ERR_UNSUPPORTED, "wide tiles need CTA pairs and fp32 output");
   p->wide = 0;
   if (p->cta_group == 2 && f32 && !no_wide) {
+    // What the wide plan would look like: its tiles, the K split that fills the machine with
+    // them, and how deep one item's reduction then is.  Measured on the step's weight gradients:
+    // 171 K blocks per item win 10 % (4096 x 1536), 128 lose 1 % (1536 x 4608, where 54 wide
+    // tiles need a 4-way split).
     const int64_t wide_tiles = static_cast<int64_t>(d->batch) * p->tiles_m * ceil_div(d->n, 2 * kTileN);
-    const int64_t slices = std::max<int64_t>(1, (units + wide_tiles - 1) / wide_tiles);   // K slices it would take to fill the machine
-    const bool deep = p->k_blocks / slices >= 128;
+    const int wide_split = d->split_k ? d->split_k : choose_split_k(wide_tiles, p->k_blocks, units);
+    const bool deep = p->k_blocks / std::max(1, wide_split) >= 160;
     const bool fills = d->n % (2 * kTileN) == 0 || d->n >= 8 * kTileN;
-    p->wide = want_wide || (deep && fills && d->split_k == 0) ? 1 : 0;
+    // A store that has to be split pays a clearing pass and a read-modify-write of C per slice:
+    // wide tiles halve the tile count, hence split sooner, so a store only goes wide unsplit.
+    const bool cheap_split = d->mode == B200GEMM_ACCUMULATE || wide_split == 1;
+    p->wide = want_wide || (deep && fills && cheap_split) ? 1 : 0;
   }
   const int tile_n = p->wide ? 2 * kTileN : kTileN;
   p->tiles_n = ceil_div(d->n, tile_n);

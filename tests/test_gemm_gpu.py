@@ -469,9 +469,23 @@ def test_wide_tiles_match_the_oracle(pkg, oracle, gemm, ta, tb, m, n, k):
 
 
 def test_wide_tiles_are_chosen_for_deep_reductions_and_split_k(pkg, oracle, gemm):
-    """The weight-gradient orientation with K = 16384 tokens: the planner picks wide tiles and splits K;
-    many items per CTA pair, exact on integer operands."""
+    """The planner picks wide tiles for the MLP's weight gradient over 32768 tokens (K slices deep
+    enough that the unoverlapped drain does not matter) and keeps the 256-wide ones for a forward;
+    wide tiles with K split four ways, many items per CTA pair, are exact on integer operands."""
     import torch
+    L = pkg._lib
+    x = torch.empty((32768, 4096), dtype=torch.bfloat16, device="cuda")
+    dy = torch.empty((32768, 1536), dtype=torch.bfloat16, device="cuda")
+    dw = torch.empty((4096, 1536), dtype=torch.float32, device="cuda")
+    kw = dict(transposed_a=True, transposed_b=True, accumulate=True)
+    chosen = gemm.launch_config(x, dy, dw, **kw)
+    assert chosen == gemm.launch_config(x, dy, dw, flags=L.FLAG_WIDE_TILE, **kw)          # wide by itself
+    assert chosen["smem_bytes"] != gemm.launch_config(x, dy, dw, flags=L.FLAG_NARROW_TILE, **kw)["smem_bytes"]
+    y = torch.empty((32768, 1536), dtype=torch.float32, device="cuda")
+    w = torch.empty((4096, 1536), dtype=torch.bfloat16, device="cuda")
+    assert gemm.launch_config(x, w, y, transposed_b=True) == gemm.launch_config(x, w, y, transposed_b=True,
+                                                                                 flags=L.FLAG_NARROW_TILE)
+    del x, dy, dw, y, w
     m, n, k = 512, 1024, 16384
     i, j = np.meshgrid(np.arange(k), np.arange(m), indexing="ij")
     av = (((i * 5 + j * 3) % 7) - 3).astype(np.float32)
@@ -479,14 +493,10 @@ def test_wide_tiles_are_chosen_for_deep_reductions_and_split_k(pkg, oracle, gemm
     bv = (((i * 4 + j * 5) % 5) - 2).astype(np.float32)
     a, b = to_dev_bf16(oracle.bf16_bits(av)), to_dev_bf16(oracle.bf16_bits(bv))
     c = torch.zeros((m, n), dtype=torch.float32, device="cuda")
-    cfg = gemm.launch_config(a, b, c, transposed_a=True, transposed_b=True, accumulate=True)
-    assert cfg["smem_bytes"] == gemm.launch_config(a, b, c, transposed_a=True, transposed_b=True, accumulate=True,
-                                                   flags=pkg._lib.FLAG_WIDE_TILE)["smem_bytes"]       # wide by itself
-    assert cfg["split_k"] > 1
-    gemm.f32_accumulate_transposed(a, b, c)
+    gemm.f32_accumulate_transposed(a, b, c, flags=L.FLAG_WIDE_TILE, split_k=4)
     assert gemm.device_status() == 0
     want = av.astype(np.int64).T @ bv.astype(np.int64)
     assert np.array_equal(c.cpu().numpy(), want.astype(np.float32))
     with pytest.raises(pkg.B200GemmError):                      # bf16 output has no wide form
         gemm.gemm(a, b, torch.zeros((m, n), dtype=torch.bfloat16, device="cuda"), transposed_a=True,
-                  transposed_b=True, flags=pkg._lib.FLAG_WIDE_TILE)
+                  transposed_b=True, flags=L.FLAG_WIDE_TILE)
