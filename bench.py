@@ -659,7 +659,7 @@ def run_sharded(args):
 
     # The expert-parallel exchange sets up peer mappings, side streams and their scheduler
     # counters during its first steps; a few more untimed steps keep that out of the clock.
-    warmup = max(args.warmup, 10 if args.workload == "moe" else 3)
+    warmup = max(args.warmup, {"moe": 10, "tp_mlp": 6, "lmhead": 5}[args.workload])
     for _ in range(warmup):
         launches = w.step()
     ms, clocks = time_steps(torch, dist, w.step, args.steps, local)
@@ -724,7 +724,9 @@ def sharded_block(args, torch, dist, pkg, gemm, dev, rank, world, local):
     block = {}
     for workload in SHARDED:
         w = build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world)
-        for _ in range(10 if workload == "moe" else 3):
+        # the exchanges set up peer mappings, side streams and scheduler counters in their first
+        # steps, and the first steps through freshly mapped peer memory are slow: keep them out
+        for _ in range({"moe": 10, "tp_mlp": 6, "lmhead": 5}[workload]):
             w.step()
         ms, clocks = time_steps(torch, dist, w.step, steps, local)
         tt = torch.tensor([ms], device=dev, dtype=torch.float64)
