@@ -573,6 +573,29 @@ B200GEMM_API int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream,
                                               int32_t out_type);
 
 /*
+ * A barrier between the GPUs of one box, as a kernel small enough to share an SM with a
+ * persistent GEMM CTA (one block, no shared memory) -- which a collective library's kernel is
+ * not, so a barrier made of one waits until the GEMM ends or needs SMs kept free for it.
+ * New: the reference is single-GPU.
+ *   peer_words[r]  rank r's array of `world` 64-bit arrival words (zero at the start) as seen
+ *                  from the calling process (peer-mapped memory, e.g. symmetric memory)
+ *   epoch          1, 2, 3, ... : the same on every rank for the same barrier, never reused with
+ *                  the same arrays
+ *   payload / peer_tables  optional all-gather on the way: this rank's `payload_count` int32
+ *                  are written into row `rank` of every rank's table (peer_tables[r] = rank r's
+ *                  [world][payload_count] table) before the arrival words, so that after the
+ *                  barrier every table holds every rank's integers
+ * What this rank stored into peer memory earlier on `stream` is visible to the peers' kernels
+ * launched after their barrier.  The wait is bounded: after limit_ms the kernel gives up,
+ * records device status 108 (b200gemm_device_status) and returns; the arrays then hold a stale
+ * epoch and must not be used again.  Ranks must not share a GPU.  world <= 8.
+ */
+B200GEMM_API int b200gemm_peer_barrier(b200gemm_handle_t h, void* stream, void* const* peer_words,
+                                       int32_t world, int32_t rank, uint64_t epoch, int64_t limit_ms,
+                                       const int32_t* payload, int32_t payload_count,
+                                       void* const* peer_tables);
+
+/*
  * dst[i] = sum over p in [0, parts), ascending, of src[p * part_stride + i], i in [0, count):
  * the last step of a reduce-scatter whose parts were delivered by copies (one part per rank,
  * e.g. by the copy engines over NVLink while the SMs keep multiplying).  Element types:

@@ -306,6 +306,13 @@ class Tcgen05Gemm {
     return b200gemm_transpose_bf16(h_, stream, src, dst, rows, cols);
   }
 
+  /// Barrier between the GPUs of one box (optionally gathering a few integers per rank on the way).
+  int peer_barrier(void* stream, void* const* peer_words, int32_t world, int32_t rank, uint64_t epoch,
+                   int64_t limit_ms = 2000, const int32_t* payload = nullptr, int32_t payload_count = 0,
+                   void* const* peer_tables = nullptr) const {
+    return b200gemm_peer_barrier(h_, stream, peer_words, world, rank, epoch, limit_ms, payload, payload_count,
+                                 peer_tables);
+  }
   /// dst = sum of `parts` equally long arrays `part_stride` apart (the tail of a copy-delivered reduce-scatter).
   int sum_parts(void* stream, const void* src, b200gemm_out_t src_type, int64_t part_stride, int32_t parts,
                 int64_t count, void* dst, b200gemm_out_t dst_type, int32_t max_blocks = 0) const {

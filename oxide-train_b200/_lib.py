@@ -119,6 +119,8 @@ SIGNATURES = {
                                              C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.POINTER(C.c_void_p),
                                              C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                              C.c_int32, C.c_int64, C.c_int64, C.c_int64]),
+    "b200gemm_peer_barrier": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                        C.c_uint64, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)]),
     "b200gemm_sum_parts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int64,
                                      C.c_void_p, C.c_int32, C.c_int32]),
     "b200gemm_lmhead_ce_forward_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,

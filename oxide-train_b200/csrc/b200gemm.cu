@@ -1177,6 +1177,36 @@ int b200gemm_grouped_gemm_peer(b200gemm_handle_t h, void* stream, const void* a,
                       &pb, group_dst_rank, group_dst_row, out_rows);
 }
 
+int b200gemm_peer_barrier(b200gemm_handle_t h, void* stream, void* const* peer_words, int32_t world, int32_t rank,
+                          uint64_t epoch, int64_t limit_ms, const int32_t* payload, int32_t payload_count,
+                          void* const* peer_tables) {
+  int rc = check_handle(h);
+  if (rc) return rc;
+  if (!peer_words) return fail(B200GEMM_ERR_INVALID, "null pointer table");
+  if (world < 1 || world > kMoeMaxPeers || rank < 0 || rank >= world)
+    return fail(B200GEMM_ERR_SHAPE, "world must be in [1, %d] and rank inside it", kMoeMaxPeers);
+  if (epoch == 0) return fail(B200GEMM_ERR_INVALID, "epochs start at 1 (the arrival words start at 0)");
+  if (limit_ms < 1 || limit_ms > 10000) return fail(B200GEMM_ERR_INVALID, "limit must be 1..10000 ms");
+  if ((payload != nullptr) != (peer_tables != nullptr) || (payload && (payload_count < 1 || payload_count > 4096)))
+    return fail(B200GEMM_ERR_INVALID, "payload and peer tables go together, 1..4096 integers per rank");
+  PeerWords words = {};
+  PeerTables tables = {};
+  for (int r = 0; r < world; ++r) {
+    if (!peer_words[r] || (reinterpret_cast<uintptr_t>(peer_words[r]) & 7u) != 0)
+      return fail(B200GEMM_ERR_INVALID, "peer word array %d is null or not 8-byte aligned", r);
+    words.ptr[r] = static_cast<unsigned long long*>(peer_words[r]);
+    if (peer_tables) {
+      if (!peer_tables[r]) return fail(B200GEMM_ERR_INVALID, "null peer table %d", r);
+      tables.ptr[r] = static_cast<int*>(peer_tables[r]);
+    }
+  }
+  peer_barrier_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      words, world, rank, epoch, payload, payload ? payload_count : 0, tables, h->status,
+      static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  CUDA_TRY(cudaGetLastError());
+  return B200GEMM_OK;
+}
+
 int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const uint32_t* selected,
                          const uint32_t* slots, const int32_t* dst_base, void* const* peer_inbox,
                          int64_t inbox_rows, int32_t world, int32_t experts, int64_t tokens,
@@ -1494,7 +1524,7 @@ int b200gemm_device_status(b200gemm_handle_t h, void* stream, int32_t* device_co
       for (auto& kv : h->sched_counters) CUDA_TRY(cudaMemsetAsync(kv.second, 0, 2 * sizeof(int), s));
     }
     return fail(B200GEMM_ERR_DEVICE,
-                "a kernel reported device status %d (101-104, 106: a bounded wait ran out; 105: a row fell "
+                "a kernel reported device status %d (101-104, 106, 108: a bounded wait ran out; 105: a row fell "
                 "outside an exchange buffer; 107: a cross-entropy target outside [0, classes))",
                 code);
   }

@@ -781,4 +781,59 @@ __global__ void __launch_bounds__(256) moe_ep_pull_combine_kernel(PeerPointers r
   }
 }
 
+// ------------------------------------------------------------------ barrier between the GPUs of one box
+// Every rank owns a small array of 64-bit arrival words that its peers can address (peer-mapped
+// memory), one word per source rank.  A barrier = "write my epoch into my word of every peer's
+// array, then wait until every word of my own array has reached the epoch".  One block, no
+// shared memory: it fits on an SM next to a persistent GEMM CTA, which a collective library's
+// kernel does not, so it neither waits for the GEMM to end nor needs SMs set aside for it.
+// Optionally the ranks exchange a few integers on the way (an all-gather of `count` int32 per
+// rank: the expert-parallel exchange's per-expert counts), written before the arrival word.
+// The wait is bounded: after `limit_ns` the kernel records kDevTimeoutPeer and returns.
+struct PeerWords {
+  unsigned long long* ptr[kMoeMaxPeers];
+};
+struct PeerTables {
+  int* ptr[kMoeMaxPeers];
+};
+
+__global__ void __launch_bounds__(256) peer_barrier_kernel(PeerWords words, int world, int rank,
+                                                           unsigned long long epoch, const int* __restrict__ payload,
+                                                           int count, PeerTables tables, int* status,
+                                                           unsigned long long limit_ns) {
+  // 1. my integers into row `rank` of every peer's table
+  if (payload) {
+    for (int i = threadIdx.x; i < world * count; i += blockDim.x) {
+      const int peer = i / count, j = i - peer * count;
+      tables.ptr[peer][rank * count + j] = payload[j];
+    }
+  }
+  // everything this rank wrote into peer memory before this kernel, and the integers above,
+  // are visible system-wide before the arrival words are
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) {
+    volatile unsigned long long* theirs = words.ptr[threadIdx.x] + rank;
+    *theirs = epoch;
+    // 2. wait for peer `threadIdx.x`'s word in my own array
+    volatile unsigned long long* mine = words.ptr[rank] + threadIdx.x;
+    unsigned long long start = 0;
+    for (unsigned spin = 1;; ++spin) {
+      if (*mine >= epoch) break;
+      __nanosleep(100);
+      if ((spin & 0xff) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (start == 0) {
+          start = now;
+        } else if (now - start > limit_ns) {
+          atomicCAS(status, 0, 108);
+          break;
+        }
+      }
+    }
+  }
+  __threadfence_system();
+}
+
 }  // namespace b200

@@ -19,6 +19,7 @@ enum DeviceStatus : int {
   kDevInboxOverflow = 105,     // expert-parallel exchange: a row fell outside the owner's buffer
   kDevTimeoutSchedule = 106,   // a role waited too long for its next tile from the tile scheduler
   kDevBadTarget = 107,         // cross-entropy: a target index outside [0, classes)
+  kDevTimeoutPeer = 108,       // a barrier between GPUs waited too long for a peer's arrival
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
