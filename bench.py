@@ -373,6 +373,10 @@ MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
 MOE_PIECES = 2                 # set from --moe-pieces: token slices of the expert-parallel step
 MOE_RETURN = "pull"            # set from --moe-return
+MOE_RESERVE = None             # set from --moe-reserve-sms
+MOE_CTAS = 0                   # set from --moe-exchange-ctas
+MOE_BULK = False               # set from --moe-exchange-bulk
+RANK_BARRIER = "kernel"        # set from --rank-barrier: how the copy / device exchanges order the ranks
 MLP_PIECES = [1, 3, 4, 4, 3, 1]   # set from --mlp-pieces (several GPUs)
 
 
@@ -403,7 +407,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
             # each rank keeps its own m / N rows of the summed d_hidden (a reduce-scatter): what a
             # row-parallel layer below the head consumes; `d_hidden="all"` would gather them again
             head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve, exchange="copy",
-                                         d_hidden="scatter" if world > 1 else "all")
+                                         d_hidden="scatter" if world > 1 else "all", barrier=RANK_BARRIER)
         else:
             reserve = 32 if world >= 8 else 16
             head = par.VocabParallelHead(ops, classes, v, reserve_sms=reserve,
@@ -429,7 +433,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         w.host_in, w.scaling = hidden, "strong"
         w.compute_ops = ("head_forward_shard", "head_merge_shards", "head_dlogits", "head_dhidden_partial",
                          "head_dweight", "widen")
-        w.exchange_ops = ("sum_parts",)
+        w.exchange_ops = ("sum_parts", "peer_barrier")
     elif workload == "moe":
         # 32768 tokens PER GPU (weak scaling): expert parallelism serves data-parallel
         # token batches; the experts, not the tokens, are what is divided.
@@ -452,7 +456,10 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         w_up = rnd((experts, d, ff), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         w_dn = rnd((experts, ff, d), 0.02)[rank * e_local:(rank + 1) * e_local].contiguous()
         ep = par.ExpertParallelMoe(ops, experts, top_k, w_up, w_dn, pieces=MOE_PIECES, exchange="device",
-                                   return_path=MOE_RETURN)
+                                   return_path=MOE_RETURN, barrier=RANK_BARRIER)
+        if MOE_RESERVE is not None:
+            ep.reserve_sms = MOE_RESERVE
+        ep.exchange_ctas, ep.exchange_bulk = MOE_CTAS, MOE_BULK
 
         def step():
             w.result["out"] = ep.forward(x, logits, scores_are_logits=True)
@@ -467,7 +474,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         w.host_in, w.scaling, w.extra = x, "weak", ep
         w.compute_ops = ("route", "scatter", "combine", "combine_into", "grouped_indexed", "grouped_indexed_into",
                          "grouped_indexed_peer", "ep_plan", "ep_return_plan")
-        w.exchange_ops = ("ep_push", "ep_pull_combine")
+        w.exchange_ops = ("ep_push", "ep_pull_combine", "peer_barrier")
     else:
         m, d, ff = 65536, 4096, 16384
         cols = ff // world
@@ -480,7 +487,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         # rows go through in pieces; on several GPUs short pieces at both ends, because what no GEMM
         # covers is the exchange of the last piece (forward and backward) and the gather of the first
         pieces = 4 if world == 1 else MLP_PIECES
-        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=pieces, partial_dtype=bf, exchange=how)
+        mlp = par.TensorParallelMlp(ops, w1, w2, chunks=pieces, partial_dtype=bf, exchange=how, barrier=RANK_BARRIER)
         dy_local = rnd((m // world, d), 0.01)
         dw1 = torch.zeros((d, cols), device=dev, dtype=f32)
         dw2 = torch.zeros((cols, d), device=dev, dtype=f32)
@@ -499,7 +506,7 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
                       + (" (copy-engine pushes into peer memory + local sum)" if how == "copy" else ""))
         w.host_in, w.scaling = x, "strong"
         w.compute_ops = ("linear", "linear_weight_grad", "linear_input_grad", "linear_input_grad_into")
-        w.exchange_ops = ("sum_parts",)
+        w.exchange_ops = ("sum_parts", "peer_barrier")
     w.step = step
     if not hasattr(w, "exchange_ops"):
         w.exchange_ops = ()
@@ -526,9 +533,10 @@ def time_steps(torch, dist, step, steps, local, sample_clocks=True):
     return s0.elapsed_time(e0) / steps, (sampler.stop() if sampler else None)
 
 
-def exchange_timeline(torch, dist, ops, w):
-    """One more step with CUDA events around every collective and every compute call (this
-    rank): how long each collective took and how much of that no GEMM of this rank covered.
+def exchange_timeline(torch, dist, ops, w, spans_too=False):
+    """More steps with CUDA events around every collective and every compute call (this rank),
+    the middle one of three back-to-back steps analysed: how long each collective took and how
+    much of that no GEMM of this rank covered.
     The events sit on whichever stream the call was issued on; an exposed millisecond is one
     during which a collective (or the expert exchange's push / pull kernels) ran and none of the
     compute calls did."""
@@ -565,12 +573,19 @@ def exchange_timeline(torch, dist, ops, w):
         w.step()                      # once with the recorders in place, untimed (first-use costs of the events)
         torch.cuda.synchronize()
         dist.barrier()
+        # three steps back to back, the middle one analysed: its neighbours keep the queues
+        # full, as in the timed loop (a lone step after a synchronise also pays launch latency)
         marks.clear()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w.step()
+        first = len(marks)
         t0.record()
         w.step()
         t1.record()
+        last = len(marks)
+        w.step()
         torch.cuda.synchronize()
+        marks = marks[first:last]
     finally:
         for obj, name, fn in restore:
             setattr(obj, name, fn)
@@ -601,8 +616,11 @@ def exchange_timeline(torch, dist, ops, w):
             longest = {"op": name, "ms": round(b - a, 4), "exposed_ms": round(exposed, 4), "bytes": nb}
     for d in per_op.values():
         d["ms"], d["exposed_ms"] = round(d["ms"], 4), round(d["exposed_ms"], 4)
-    return {"step_ms": round(t0.elapsed_time(t1), 4), "compute_busy_ms": round(sum(b - a for a, b in merged), 4),
-            "collectives": per_op, "longest_exposed_collective": longest}
+    out = {"step_ms": round(t0.elapsed_time(t1), 4), "compute_busy_ms": round(sum(b - a for a, b in merged), 4),
+           "collectives": per_op, "longest_exposed_collective": longest}
+    if spans_too:
+        out["spans"] = [[name, round(a, 4), round(b, 4)] for name, _, a, b, _ in sorted(spans, key=lambda t: t[2])]
+    return out
 
 
 def sharded_line(torch, dist, w, workload, world, ms, clocks, peaks, extra_e2e=None):
@@ -683,7 +701,7 @@ def run_sharded(args):
     tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     ms, e2e_ms = tt.tolist()
-    timeline = exchange_timeline(torch, dist, ops, w)
+    timeline = exchange_timeline(torch, dist, ops, w, spans_too=args.timeline_spans)
     status = gemm.device_status()
     peaks = measured_peaks()
     sub = sharded_line(torch, dist, w, args.workload, world, ms, None, peaks)
@@ -1055,8 +1073,21 @@ def main():
                     help="tensor-parallel MLP on several GPUs: row pieces, a count or comma-separated weights")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
+    ap.add_argument("--moe-reserve-sms", type=int, default=None,
+                    help="expert-parallel MoE: SMs the expert GEMMs leave free (default: the class's)")
+    ap.add_argument("--moe-exchange-ctas", type=int, default=0,
+                    help="expert-parallel MoE: thread blocks of the dispatch / combine kernels (0 = two per SM)")
+    ap.add_argument("--moe-exchange-bulk", action="store_true",
+                    help="expert-parallel MoE: the bulk-copy forms of the dispatch / combine kernels")
+    ap.add_argument("--timeline-spans", action="store_true",
+                    help="with --workload: add every timed call of the analysed step (name, start ms, end ms)")
+    ap.add_argument("--rank-barrier", default="kernel", choices=["kernel", "nccl"],
+                    help="how the copy-engine and device-driven exchanges order the ranks: this library's one-block "
+                         "barrier kernel over peer memory, or one-element NCCL all-reduces")
     args = ap.parse_args()
-    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN, MLP_PIECES
+    global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN, MLP_PIECES, RANK_BARRIER, MOE_RESERVE, MOE_CTAS, MOE_BULK
+    MOE_RESERVE, MOE_CTAS, MOE_BULK = args.moe_reserve_sms, args.moe_exchange_ctas, args.moe_exchange_bulk
+    RANK_BARRIER = args.rank_barrier
     MOE_RETURN = args.moe_return
     parts = [int(v) for v in str(args.mlp_pieces).split(",")]
     MLP_PIECES = parts[0] if len(parts) == 1 else parts

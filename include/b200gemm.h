@@ -113,6 +113,16 @@ B200GEMM_API int b200gemm_destroy(b200gemm_handle_t h);
  * same time, since a persistent grid would otherwise hold every SM until it ends. */
 B200GEMM_API int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms);
 
+/* Thread blocks of the expert exchange's dispatch and combine kernels (b200gemm_moe_ep_push,
+ * b200gemm_moe_ep_pull_combine) of later launches; 0 restores the default of two 256-thread
+ * blocks per SM.  New: those kernels are bound by the links between the GPUs, not by the SMs,
+ * and run beside the expert GEMMs -- fewer blocks take less from the GEMM.
+ *   bulk = 0  the store- / load-driven kernels with `ctas` blocks
+ *   bulk = 1  rows move by bulk asynchronous copies through a ring in shared memory (two
+ *             warps per block dispatch, nine combine); the results are bit-identical
+ */
+B200GEMM_API int b200gemm_set_exchange_ctas(b200gemm_handle_t h, int32_t ctas, int32_t bulk);
+
 /* How the persistent kernels of later launches hand out their tiles.
  *   0  static: cluster c takes items c, c + clusters, ...  (the reference's walk,
  *      gpu/gemm/src/optimized.rs:776-802)
@@ -583,8 +593,10 @@ B200GEMM_API int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream,
  *                  the same arrays
  *   payload / peer_tables  optional all-gather on the way: this rank's `payload_count` int32
  *                  are written into row `rank` of every rank's table (peer_tables[r] = rank r's
- *                  [world][payload_count] table) before the arrival words, so that after the
- *                  barrier every table holds every rank's integers
+ *                  [2][world][payload_count] table; half epoch & 1 is the one written, so a
+ *                  rank already at the next barrier does not overwrite what a slower peer
+ *                  still reads) before the arrival words, so that after the barrier that
+ *                  half of every table holds every rank's integers
  * What this rank stored into peer memory earlier on `stream` is visible to the peers' kernels
  * launched after their barrier.  The wait is bounded: after limit_ms the kernel gives up,
  * records device status 108 (b200gemm_device_status) and returns; the arrays then hold a stale

@@ -346,6 +346,7 @@ class Tcgen05Gemm {
   void set_split_k(int split_k) { split_k_ = split_k; }
   /// Persistent kernels on at most `sms` SMs (0 = all): room for a collective's kernels.
   int set_sm_limit(int sms) const { return b200gemm_set_sm_limit(h_, sms); }
+  int set_exchange_ctas(int ctas, bool bulk = false) const { return b200gemm_set_exchange_ctas(h_, ctas, bulk ? 1 : 0); }
   /// Tiles from a device-side counter (true, the default) or the fixed round-robin walk.
   int set_scheduler(bool dynamic) const { return b200gemm_set_scheduler(h_, dynamic ? 1 : 0); }
 

@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200gemm_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
     "b200gemm_destroy": (C.c_int, [C.c_void_p]),
     "b200gemm_set_sm_limit": (C.c_int, [C.c_void_p, C.c_int32]),
+    "b200gemm_set_exchange_ctas": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "b200gemm_set_scheduler": (C.c_int, [C.c_void_p, C.c_int32]),
     "b200gemm_gemm_dual": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64]),
     "b200gemm_gemm": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(GemmDesc)]),

@@ -56,6 +56,10 @@ struct b200gemm_context {
   int device = 0;
   int sm_count = 0;          // SMs the persistent kernels spread over (b200gemm_set_sm_limit)
   int sm_total = 0;          // SMs of the device
+  bool push_bulk_opt_in = false;               // ... and for the bulk-copy dispatch
+  bool pull_bulk_opt_in[2] = {false, false};   // large dynamic shared memory enabled for the bulk-copy combine (f32, bf16 out)
+  bool exchange_bulk = false;   // the bulk-copy forms of those kernels
+  int exchange_ctas = 0;     // thread blocks of the expert exchange's kernels (b200gemm_set_exchange_ctas); 0 = two per SM
   int* status = nullptr;        // device status word
   EncodeTiledFn encode = nullptr;
   // staging for b200gemm_gemm_host
@@ -795,6 +799,15 @@ int b200gemm_set_sm_limit(b200gemm_handle_t h, int32_t sms) {
   return B200GEMM_OK;
 }
 
+int b200gemm_set_exchange_ctas(b200gemm_handle_t h, int32_t ctas, int32_t bulk) {
+  if (!h) return fail(B200GEMM_ERR_INVALID, "null handle");
+  if (ctas < 0 || ctas > 4 * h->sm_total) return fail(B200GEMM_ERR_INVALID, "ctas must be 0 (default) .. 4 per SM");
+  if (bulk < 0 || bulk > 1) return fail(B200GEMM_ERR_INVALID, "bulk must be 0 or 1");
+  h->exchange_ctas = ctas;
+  h->exchange_bulk = bulk != 0 && ctas > 0;
+  return B200GEMM_OK;
+}
+
 int b200gemm_set_scheduler(b200gemm_handle_t h, int32_t mode) {
   int rc = check_handle(h);
   if (rc) return rc;
@@ -1223,9 +1236,36 @@ int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const
     if (!peer_inbox[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
     pp.ptr[r] = static_cast<uint16_t*>(peer_inbox[r]);
   }
+  if (h->exchange_bulk) {
+    // A few blocks were asked for: rows travel by bulk asynchronous copies through a
+    // shared-memory ring, which fills the links from few SMs (when the ring is deep enough
+    // for the batches of stores in flight).
+    int top_k_pad = 1;
+    while (top_k_pad < top_k) top_k_pad *= 2;
+    const int per_batch = 32 / top_k_pad;
+    const size_t row_bytes = static_cast<size_t>(d) * 2;
+    const size_t fixed = sizeof(PushBulkSmem) + static_cast<size_t>(experts) * sizeof(int);
+    const size_t budget = 200 * 1024;
+    const int need = (kPushPendingBatches + 2) * per_batch;
+    int stages = std::max(32, need);
+    if (budget > fixed) stages = static_cast<int>(std::min<size_t>(stages, (budget - fixed) / row_bytes));
+    if (stages >= need && stages <= kPushMaxStages) {
+      const size_t smem = stages * row_bytes + fixed;
+      if (!h->push_bulk_opt_in) {
+        CUDA_TRY(cudaFuncSetAttribute(moe_ep_push_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        h->push_bulk_opt_in = true;
+      }
+      const int bulk_grid = static_cast<int>(std::min<int64_t>(tokens, h->exchange_ctas));
+      moe_ep_push_bulk_kernel<<<bulk_grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const uint16_t*>(x), selected, slots, dst_base, pp, experts, experts / world, tokens, top_k,
+          top_k_pad, d, inbox_rows, stages, h->status);
+      CUDA_TRY(cudaGetLastError());
+      return B200GEMM_OK;
+    }
+  }
   // Two 256-thread CTAs per SM at most: the link, not the SMs, bounds this kernel, and a
   // persistent GEMM CTA (224 threads, nearly all shared memory) must still fit beside them.
-  const int push_grid = std::min(stream_grid(tokens * 32, h->sm_total), 2 * h->sm_total);
+  const int push_grid = std::min(stream_grid(tokens * 32, h->sm_total), h->exchange_ctas ? h->exchange_ctas : 2 * h->sm_total);
   moe_ep_push_kernel<<<push_grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint16_t*>(x), selected, slots, dst_base, pp, experts / world, tokens, top_k, d,
       inbox_rows, h->status);
@@ -1250,8 +1290,41 @@ int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const*
     if (!peer_results[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
     pp.ptr[r] = static_cast<uint16_t*>(peer_results[r]);
   }
-  const int grid = std::min(stream_grid(tokens * 32, h->sm_total), 2 * h->sm_total);   // see b200gemm_moe_ep_push
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (h->exchange_bulk) {
+    // A few blocks were asked for: the form that keeps the links busy from few SMs (bulk
+    // asynchronous copies into a shared-memory ring), if a token's rows fit the ring twice.
+    int top_k_pad = 1;
+    while (top_k_pad < top_k) top_k_pad *= 2;
+    const size_t stage_bytes = static_cast<size_t>(top_k) * d * 2;
+    const size_t fixed = sizeof(PullBulkSmem) + static_cast<size_t>(experts) * sizeof(int);
+    const size_t budget = 200 * 1024;
+    int stages = stage_bytes > 0 && budget > fixed ? static_cast<int>(std::min<size_t>(8, (budget - fixed) / stage_bytes)) : 0;
+    if (stages >= 2) {
+      const size_t smem = stages * stage_bytes + fixed;
+      const int bulk_grid = static_cast<int>(std::min<int64_t>(tokens, h->exchange_ctas));
+      const int which = out_type == B200GEMM_OUT_BF16 ? 1 : 0;
+      if (!h->pull_bulk_opt_in[which]) {
+        if (which)
+          CUDA_TRY(cudaFuncSetAttribute(moe_ep_pull_bulk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        else
+          CUDA_TRY(cudaFuncSetAttribute(moe_ep_pull_bulk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        h->pull_bulk_opt_in[which] = true;
+      }
+      if (which)
+        moe_ep_pull_bulk_kernel<true><<<bulk_grid, 32 * (stages + 1), smem, s>>>(
+            pp, selected, slots, dst_base, gates, static_cast<const uint16_t*>(residual), experts, experts / world,
+            tokens, top_k, top_k_pad, d, result_rows, stages, h->status, out);
+      else
+        moe_ep_pull_bulk_kernel<false><<<bulk_grid, 32 * (stages + 1), smem, s>>>(
+            pp, selected, slots, dst_base, gates, static_cast<const uint16_t*>(residual), experts, experts / world,
+            tokens, top_k, top_k_pad, d, result_rows, stages, h->status, out);
+      CUDA_TRY(cudaGetLastError());
+      return B200GEMM_OK;
+    }
+  }
+  const int grid = std::min(stream_grid(tokens * 32, h->sm_total),
+                            h->exchange_ctas ? h->exchange_ctas : 2 * h->sm_total);   // see b200gemm_moe_ep_push
   if (out_type == B200GEMM_OUT_BF16)
     moe_ep_pull_combine_kernel<true><<<grid, 256, 0, s>>>(pp, selected, slots, dst_base, gates,
                                                           static_cast<const uint16_t*>(residual), experts / world,

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ptx.cuh"
+
 namespace b200 {
 
 constexpr uint32_t kMoeDropped = 0xFFFFFFFFu;   // u32::MAX marks a dropped assignment
@@ -781,6 +783,304 @@ __global__ void __launch_bounds__(256) moe_ep_pull_combine_kernel(PeerPointers r
   }
 }
 
+// Combine, the form for a few SMs: the same sums in the same order as
+// moe_ep_pull_combine_kernel, but the result rows are fetched by bulk asynchronous copies
+// (cp.async.bulk, global or peer memory -> shared memory, completion on an mbarrier)
+// instead of by loads.  A load-driven combine needs some thousand warps resident to keep
+// the links between the GPUs busy -- warps that share SMs, issue slots and load/store units
+// with the expert GEMM running at the same time.  Here one producer warp per block keeps
+// `stages` tokens (top_k rows each) in flight, so a dozen blocks on SMs the GEMM left free
+// move the same bytes per second.
+//   warp `stages`         producer: per token, the row addresses and gates, one bulk copy per row
+//   warps 0..stages-1     consumers: warp w owns stage w; gate-weighted sum from shared memory
+// Shared memory: [stages][top_k][d] bf16 rows | [stages][16] gates | [stages] row masks |
+// full / empty barriers | dst_base table.
+struct PullBulkSmem {
+  unsigned long long full[8];
+  unsigned long long empty[8];
+  float gates[8][kMoeMaxTopK];
+  uint32_t mask[8];
+  int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_load_row(uint32_t smem_dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+template <bool kOutBf16>
+__global__ void __launch_bounds__(288) moe_ep_pull_bulk_kernel(PeerPointers results,
+                                                               const uint32_t* __restrict__ selected,
+                                                               const uint32_t* __restrict__ slots,
+                                                               const int* __restrict__ dst_base,
+                                                               const float* __restrict__ gates,
+                                                               const uint16_t* __restrict__ residual,
+                                                               int experts, int experts_per_rank, long long tokens,
+                                                               int top_k, int top_k_pad, long long d,
+                                                               long long result_rows, int stages, int* status,
+                                                               void* __restrict__ out) {
+  extern __shared__ __align__(128) unsigned char pull_smem[];
+  const uint32_t row_bytes = static_cast<uint32_t>(d * 2);
+  const uint32_t stage_bytes = row_bytes * top_k;
+  PullBulkSmem* ctl = reinterpret_cast<PullBulkSmem*>(pull_smem + static_cast<size_t>(stages) * stage_bytes);
+  int* base_tab = reinterpret_cast<int*>(ctl + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) base_tab[e] = dst_base[e];
+  __syncthreads();
+  volatile int* abort_flag = &ctl->abort_flag;
+  // this block's tokens: blockIdx.x, blockIdx.x + gridDim.x, ...; the i-th of them uses stage i % stages
+  const long long mine = tokens > blockIdx.x ? (tokens - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (warp == stages) {
+    // ---------------------------------------------------------------- producer
+    // tokens whose rows one pass of the warp fetches (never two that share a stage)
+    const int per_batch = (32 / top_k_pad) < stages ? (32 / top_k_pad) : stages;
+    const int sub = lane / top_k_pad, r = lane % top_k_pad;
+    // the routing of the batch after the current one is loaded while the current one's copies
+    // are issued: the producer never waits for global memory between two tokens
+    uint32_t next_e = 0, next_sl = kMoeDropped;
+    float next_g = 0.f;
+    if (sub < per_batch && sub < mine && r < top_k) {
+      const long long q = (blockIdx.x + static_cast<long long>(sub) * gridDim.x) * top_k + r;
+      next_e = selected[q];
+      next_sl = slots[q];
+      next_g = gates[q];
+    }
+    for (long long i0 = 0; i0 < mine && !*abort_flag; i0 += per_batch) {
+      const long long i = i0 + sub;
+      const bool live = sub < per_batch && i < mine;
+      const uint32_t e = next_e, sl = next_sl;
+      const float g_loaded = next_g;
+      next_sl = kMoeDropped;
+      if (sub < per_batch && i + per_batch < mine && r < top_k) {
+        const long long q = (blockIdx.x + (i + per_batch) * gridDim.x) * top_k + r;
+        next_e = selected[q];
+        next_sl = slots[q];
+        next_g = gates[q];
+      }
+      const uint16_t* src = nullptr;
+      float g = 0.f;
+      if (live && r < top_k && sl != kMoeDropped) {
+        const long long row = static_cast<long long>(base_tab[e]) + sl;
+        if (row < result_rows) {
+          src = results.ptr[static_cast<int>(e) / experts_per_rank] + row * d;
+          g = g_loaded;
+        } else {
+          atomicCAS(status, 0, 105);           // outside the owner's buffer: skip the row, report it
+        }
+      }
+      const int stage = static_cast<int>(i % stages);
+      const uint32_t phase = static_cast<uint32_t>((i / stages) & 1);
+      const uint32_t votes = __ballot_sync(0xffffffffu, src != nullptr);
+      const uint32_t my_mask = (votes >> (sub * top_k_pad)) & ((1u << top_k_pad) - 1u);   // top_k_pad <= 16
+      bool ok = true;
+      if (live && r == 0) {
+        // the stage is free once its consumer has read the token that used it before
+        ok = mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, status, kDevTimeoutProducer, abort_flag);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (live && r < top_k) ctl->gates[stage][r] = g;
+      if (live && r == 0) ctl->mask[stage] = my_mask;
+      __syncwarp();
+      if (live && r == 0) mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), __popc(my_mask) * row_bytes);
+      __syncwarp();
+      if (src != nullptr)
+        bulk_load_row(smem_u32(pull_smem + static_cast<size_t>(stage) * stage_bytes + static_cast<size_t>(r) * row_bytes),
+                      src, row_bytes, smem_u32(&ctl->full[stage]));
+    }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    const long long vecs = d / 8;
+    for (long long i = warp; i < mine; i += stages) {
+      const uint32_t phase = static_cast<uint32_t>((i / stages) & 1);
+      if (!mbar_wait(smem_u32(&ctl->full[warp]), phase, status, kDevTimeoutEpilogue, abort_flag)) break;
+      const long long token = blockIdx.x + i * gridDim.x;
+      const uint32_t mask = ctl->mask[warp];
+      const unsigned char* rows = pull_smem + static_cast<size_t>(warp) * stage_bytes;
+      for (long long v = lane; v < vecs; v += 32) {
+        float acc[8];
+        if (residual) {
+          const uint4 rr = reinterpret_cast<const uint4*>(residual + token * d)[v];
+          const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] = __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        }
+        for (int r = 0; r < top_k; ++r) {
+          if (!((mask >> r) & 1u)) continue;
+          const float g = ctl->gates[warp][r];
+          const uint4 y = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(r) * row_bytes)[v];
+          const uint32_t w[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(g, __uint_as_float(w[j] << 16)));
+            acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(g, __uint_as_float(w[j] & 0xffff0000u)));
+          }
+        }
+        if (kOutBf16) {
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ow[j]) : "f"(acc[2 * j + 1]), "f"(acc[2 * j]));
+          reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + token * d)[v] = o;
+        } else {
+          float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + token * d) + 2 * v;
+          o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl->empty[warp]));
+    }
+  }
+  __syncthreads();
+  // After a wait gave up, copies may still be on their way into this block's shared memory:
+  // give each stage's barrier a last bounded chance to complete before the block ends.
+  if (*abort_flag && threadIdx.x < stages) {
+    const long long issued = mine;   // upper bound of what the producer may have armed
+    if (issued > threadIdx.x) {
+      const long long last = ((issued - 1 - threadIdx.x) / stages);
+      int ignored = 0;
+      mbar_wait(smem_u32(&ctl->full[threadIdx.x]), static_cast<uint32_t>(last & 1), status, kDevTimeoutDrain, &ignored,
+                100000000ull);
+    }
+  }
+}
+
+// Dispatch, the form for a few SMs: every token's row is fetched once into a shared-memory
+// ring (bulk asynchronous copy) and stored from there into the inbox of each selected
+// expert's owner by bulk asynchronous copies, shared memory -> global or peer memory.  Two
+// warps per block keep tens of rows in flight, where the store-driven kernel above needs
+// hundreds of warps to fill the links.
+//   warp 0, one lane   loader: one bulk load per token
+//   warp 1             storer: lane (token of the batch, r) issues the store of pair r
+// Shared memory: [stages][d] bf16 rows | full / empty barriers | dst_base table.
+constexpr int kPushMaxStages = 64;
+constexpr int kPushPendingBatches = 2;     // batches of stores in flight per lane
+struct PushBulkSmem {
+  unsigned long long full[kPushMaxStages];
+  unsigned long long empty[kPushMaxStages];
+  int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_store_row(void* dst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(64) moe_ep_push_bulk_kernel(const uint16_t* __restrict__ x,
+                                                              const uint32_t* __restrict__ selected,
+                                                              const uint32_t* __restrict__ slots,
+                                                              const int* __restrict__ dst_base, PeerPointers inbox,
+                                                              int experts, int experts_per_rank, long long tokens,
+                                                              int top_k, int top_k_pad, long long d,
+                                                              long long inbox_rows, int stages, int* status) {
+  extern __shared__ __align__(128) unsigned char push_smem[];
+  const uint32_t row_bytes = static_cast<uint32_t>(d * 2);
+  PushBulkSmem* ctl = reinterpret_cast<PushBulkSmem*>(push_smem + static_cast<size_t>(stages) * row_bytes);
+  int* base_tab = reinterpret_cast<int*>(ctl + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    ctl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) base_tab[e] = dst_base[e];
+  __syncthreads();
+  volatile int* abort_flag = &ctl->abort_flag;
+  const long long mine = tokens > blockIdx.x ? (tokens - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- loader
+    if (lane == 0) {
+      for (long long i = 0; i < mine; ++i) {
+        const int stage = static_cast<int>(i % stages);
+        const uint32_t phase = static_cast<uint32_t>((i / stages) & 1);
+        if (!mbar_wait(smem_u32(&ctl->empty[stage]), phase ^ 1u, status, kDevTimeoutProducer, abort_flag)) break;
+        const long long token = blockIdx.x + i * gridDim.x;
+        mbar_arrive_expect_tx(smem_u32(&ctl->full[stage]), row_bytes);
+        bulk_load_row(smem_u32(push_smem + static_cast<size_t>(stage) * row_bytes), x + token * d, row_bytes,
+                      smem_u32(&ctl->full[stage]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- storer
+    const int per_batch = 32 / top_k_pad;
+    const int sub = lane / top_k_pad, r = lane % top_k_pad;
+    uint32_t next_e = 0, next_sl = kMoeDropped;
+    if (sub < mine && r < top_k) {
+      const long long q = (blockIdx.x + static_cast<long long>(sub) * gridDim.x) * top_k + r;
+      next_e = selected[q];
+      next_sl = slots[q];
+    }
+    bool ok = true;
+    for (long long i0 = 0; i0 < mine; i0 += per_batch) {
+      const long long i = i0 + sub;
+      const bool live = i < mine;
+      const uint32_t e = next_e, sl = next_sl;
+      next_sl = kMoeDropped;
+      if (i + per_batch < mine && r < top_k) {
+        const long long q = (blockIdx.x + (i + per_batch) * gridDim.x) * top_k + r;
+        next_e = selected[q];
+        next_sl = slots[q];
+      }
+      uint16_t* dst = nullptr;
+      if (live && r < top_k && sl != kMoeDropped) {
+        const long long row = static_cast<long long>(base_tab[e]) + sl;
+        if (row < inbox_rows)
+          dst = inbox.ptr[static_cast<int>(e) / experts_per_rank] + row * d;
+        else
+          atomicCAS(status, 0, 105);           // the owner's inbox is too small: drop the row, report it
+      }
+      const int stage = static_cast<int>(i % stages);
+      const uint32_t phase = static_cast<uint32_t>((i / stages) & 1);
+      bool landed = true;
+      if (live && r == 0) landed = mbar_wait(smem_u32(&ctl->full[stage]), phase, status, kDevTimeoutEpilogue, abort_flag);
+      ok = __all_sync(0xffffffffu, landed);
+      if (!ok) break;
+      fence_proxy_async_smem();
+      if (dst != nullptr) bulk_store_row(dst, smem_u32(push_smem + static_cast<size_t>(stage) * row_bytes), row_bytes);
+      tma_commit_group();
+      // the stores of the batch issued kPushPendingBatches ago have read their rows: free them
+      tma_wait_group_read<kPushPendingBatches>();
+      __syncwarp();
+      const long long freed = i - static_cast<long long>(kPushPendingBatches) * per_batch;
+      if (r == 0 && freed >= 0 && freed < mine) mbar_arrive(smem_u32(&ctl->empty[static_cast<int>(freed % stages)]));
+    }
+    // every store of this lane has been written before the kernel ends
+    tma_wait_group<0>();
+  }
+  __syncthreads();
+  if (*abort_flag && threadIdx.x < stages) {
+    // copies may still be on their way into this block's shared memory: a last bounded wait
+    if (mine > threadIdx.x) {
+      const long long last = (mine - 1 - threadIdx.x) / stages;
+      int ignored = 0;
+      mbar_wait(smem_u32(&ctl->full[threadIdx.x]), static_cast<uint32_t>(last & 1), status, kDevTimeoutDrain, &ignored,
+                100000000ull);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ barrier between the GPUs of one box
 // Every rank owns a small array of 64-bit arrival words that its peers can address (peer-mapped
 // memory), one word per source rank.  A barrier = "write my epoch into my word of every peer's
@@ -789,6 +1089,8 @@ __global__ void __launch_bounds__(256) moe_ep_pull_combine_kernel(PeerPointers r
 // kernel does not, so it neither waits for the GEMM to end nor needs SMs set aside for it.
 // Optionally the ranks exchange a few integers on the way (an all-gather of `count` int32 per
 // rank: the expert-parallel exchange's per-expert counts), written before the arrival word.
+// A table has two halves used by odd and even epochs in turn, so that a rank that is already
+// at the next barrier does not overwrite integers a slower peer is still reading.
 // The wait is bounded: after `limit_ns` the kernel records kDevTimeoutPeer and returns.
 struct PeerWords {
   unsigned long long* ptr[kMoeMaxPeers];
@@ -805,7 +1107,7 @@ __global__ void __launch_bounds__(256) peer_barrier_kernel(PeerWords words, int 
   if (payload) {
     for (int i = threadIdx.x; i < world * count; i += blockDim.x) {
       const int peer = i / count, j = i - peer * count;
-      tables.ptr[peer][rank * count + j] = payload[j];
+      tables.ptr[peer][((epoch & 1) * world + rank) * count + j] = payload[j];
     }
   }
   // everything this rank wrote into peer memory before this kernel, and the integers above,

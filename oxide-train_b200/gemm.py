@@ -122,6 +122,11 @@ class Tcgen05Gemm:
         L.check(self._lib.b200gemm_set_sm_limit(self._h, int(sms)))
         self.sm_limit = int(sms)
 
+    def set_exchange_ctas(self, ctas: int = 0, bulk: bool = False) -> None:
+        """Thread blocks of the expert exchange's dispatch / combine kernels (0 = two per SM);
+        ``bulk``: the forms that move rows by bulk asynchronous copies through shared memory."""
+        L.check(self._lib.b200gemm_set_exchange_ctas(self._h, int(ctas), 1 if bulk else 0))
+
     def set_scheduler(self, dynamic: bool) -> None:
         """Tiles from a device-side counter (``True``) or the fixed round-robin walk (``False``)."""
         L.check(self._lib.b200gemm_set_scheduler(self._h, 1 if dynamic else 0))

@@ -221,6 +221,16 @@ class DeviceOps:
     def linear_weight_grad(self, x, dy, dw):
         self.gemm.f32_accumulate_transposed(x, dy, dw)
 
+    def peer_barrier(self, peer_words, world, rank, epoch, limit_ms, payload=None, peer_tables=None):
+        """Launches the barrier kernel on the current stream (``peer_words`` / ``peer_tables``:
+        ctypes arrays of every rank's buffer as seen from here)."""
+        from . import _lib as L
+        from .gemm import _stream_ptr
+        L.check(self.gemm._lib.b200gemm_peer_barrier(
+            self.gemm._h, _stream_ptr(), peer_words, world, rank, epoch, limit_ms,
+            payload.data_ptr() if payload is not None else None,
+            payload.numel() if payload is not None else 0, peer_tables))
+
     def sum_parts(self, parts, out):
         """``out = sum_p parts[p]`` (``parts`` is ``[p, ...]``, contiguous), added in fp32 in order."""
         from . import _lib as L
@@ -307,8 +317,9 @@ def merge_softmax_stats(row_max, row_sum, row_target_logit, group=None):
 class VocabParallelHead:
     def __init__(self, ops, classes: int, vocab_padded: int, group=None, w_layout: str = "in_out",
                  reduce_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl",
-                 d_hidden: str = "all"):
+                 d_hidden: str = "all", barrier: str = "kernel"):
         self.ops, self.group, self.w_layout, self.reduce_dtype = ops, group, w_layout, reduce_dtype
+        self.barrier = barrier              # how the copy exchange orders the ranks (PeerRowExchange)
         self.reserve_sms = reserve_sms      # SMs the weight-gradient GEMM leaves to d_hidden's exchange
         # d_hidden's sum over the shards: "nccl" = all_reduce; "copy" = copy-engine reduce-scatter
         # (+ all-gather) through peer memory, see PeerRowExchange.  d_hidden = "all": every rank
@@ -374,7 +385,8 @@ class VocabParallelHead:
         use_copy = self.exchange == "copy" and self.world > 1 and m % self.world == 0
         scatter = self.d_hidden == "scatter" and m % self.world == 0
         if use_copy and (self._px is None or self._px_key != (m, k, dh.dtype)):
-            self._px = PeerRowExchange(self.ops, self.group, dh.device, [m // self.world], k, dh.dtype)
+            self._px = PeerRowExchange(self.ops, self.group, dh.device, [m // self.world], k, dh.dtype,
+                                       barrier=self.barrier)
             self._px_key = (m, k, dh.dtype)
         mine = None
         if use_copy or scatter:
@@ -430,8 +442,19 @@ class ExpertParallelMoe:
     ``w_up_local`` is ``[experts / world, d, ff]``, ``w_down_local`` ``[experts / world, ff, d]``."""
 
     def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces=1,
-                 use_peer_copies: bool = False, exchange: str = "nccl", return_path: str = "pull"):
+                 use_peer_copies: bool = False, exchange: str = "nccl", return_path: str = "pull",
+                 barrier: str = "kernel", exchange_ctas: int = 0, exchange_bulk: bool = False):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
+        # device exchange: thread blocks of the dispatch / combine kernels that run beside an
+        # expert GEMM (0 = two per SM) and whether they are the bulk-copy forms, which fill the
+        # links from the few SMs `reserve_sms` keeps free of GEMM CTAs.  The first slice's
+        # dispatch and the last slice's combine have the GPU to themselves and always spread
+        # over all of it.
+        self.exchange_ctas, self.exchange_bulk = exchange_ctas, exchange_bulk
+        # device exchange, how the ranks wait for one another: "kernel" = this library's barrier
+        # kernel, which also gathers the per-expert counts (PeerBarrier); "nccl" = an all-gather
+        # of the counts and one-element all-reduces
+        self.barrier = barrier
         self.pieces, self._side = pieces, None
         self.use_peer_copies, self._peer, self._peer_shape, self._index = use_peer_copies, None, None, None
         self.exchange, self._dev = exchange, None       # "nccl" | "device" (peer stores / loads)
@@ -511,7 +534,10 @@ class ExpertParallelMoe:
                          "ptrs_in": ptrs_in, "ptrs_res": ptrs_res, "returned": returned, "ptrs_back": ptrs_back,
                          "pair_rows": pair_rows, "pair_first": pair_first,
                          "hidden": torch.empty((total, ff), dtype=torch.bfloat16, device=x.device),
-                         "token": torch.zeros(1, device=x.device)}
+                         "token": torch.zeros(1, device=x.device),
+                         # one barrier object per slice: each slice's kernels stay on one stream
+                         "barriers": ([PeerBarrier(self.ops, grp, x.device, payload_count=self.experts)
+                                       for _ in slices] if self.barrier == "kernel" else None)}
         dv = self._dev
         out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
         # The expert GEMMs leave a few SMs to the one-element all-reduces used as barriers
@@ -536,9 +562,20 @@ class ExpertParallelMoe:
         n = x.shape[0]
         d_out = out.shape[1]
         pieces = len(slices)
-        streams = self._streams(x.device) if pieces > 1 else [torch.cuda.current_stream()]
+        # With the barrier kernel every slice has a stream of its own and the order between
+        # slices is stated by events (below).  NCCL runs a group's collectives one after another
+        # in issue order whatever stream they were issued on, so there two streams are enough.
+        per_slice = pieces if dv["barriers"] is not None else 2
+        streams = self._streams(x.device, per_slice) if pieces > 1 else [torch.cuda.current_stream()]
         main = torch.cuda.current_stream()
         routed = []
+        # The slices form a pipeline: slice p's rows cross the links while slice p-1 is
+        # multiplied, and slice p-1's results come back while slice p is multiplied.  Two
+        # rules keep it one: a slice's dispatch starts when the previous slice's has left
+        # (two dispatches at once only halve each other's link rate and finish together,
+        # after which nothing is left to hide behind the GEMMs), and a slice's GEMMs start
+        # when the previous slice's are done (so its results can start home at once).
+        pushed, multiplied = [], []
         # Stage 1, every slice: route, plan, push, barrier.  Issued for all slices before
         # any GEMM so that the collectives (which NCCL runs in issue order) of a later
         # slice are not queued behind an earlier slice's post-GEMM barrier.
@@ -549,15 +586,24 @@ class ExpertParallelMoe:
                 st.wait_stream(main)
             with torch.cuda.stream(st):
                 r = self.ops.route(scores[sl].contiguous(), self.top_k, scores_are_logits)
-                allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
-                dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
+                bar = dv["barriers"][p] if dv["barriers"] is not None else None
+                if bar is not None:
+                    allc = bar.all_gather_i32(r.accepted_counts)
+                else:
+                    allc = torch.empty((self.world, self.experts), dtype=torch.int32, device=x.device)
+                    dist.all_gather_into_tensor(allc, r.accepted_counts, group=self.group)
                 dst_base, offsets, index = self.ops.ep_plan(allc, self.world, self.rank, self.experts)
                 back = (self.ops.ep_return_plan(allc, self.world, self.rank, self.experts)
                         if self.return_path == "push" else ())
+                if pushed:
+                    st.wait_event(pushed[-1])
+                self._size_exchange(alone=(p == 0))
                 self.ops.ep_push(x[sl], r, dst_base, dv["ptrs_in"][p], caps[p], self.world, self.experts)
-                dist.all_reduce(dv["token"], group=self.group)        # every rank's rows have landed
+                pushed.append(torch.cuda.Event())
+                pushed[-1].record(st)
+                self._sync_ranks(dv, p)                               # every rank's rows have landed
                 if st is not main:
-                    for tns in (allc, dst_base, offsets, index) + tuple(back):
+                    for tns in (dst_base, offsets, index) + tuple(back) + (() if bar is not None else (allc,)):
                         tns.record_stream(st)
             routed.append((sl, r, dst_base, offsets, index, back))
         # Stage 2, every slice: expert GEMMs on what arrived, barrier, pull + combine.
@@ -567,6 +613,8 @@ class ExpertParallelMoe:
                 inbox = dv["inbox"][first[p]:first[p] + caps[p]]
                 hidden = dv["hidden"][first[p]:first[p] + caps[p]]
                 res = dv["results"][first[p]:first[p] + caps[p]]
+                if multiplied:
+                    st.wait_event(multiplied[-1])
                 self.ops.grouped_indexed_into(inbox, self.w_up, offsets, index, True, hidden)
                 res_in = residual[sl] if residual is not None else None
                 if self.return_path == "push":
@@ -575,16 +623,22 @@ class ExpertParallelMoe:
                     rows_back = dv["pair_rows"][p]
                     self.ops.grouped_indexed_peer(hidden, self.w_down, offsets, index, dv["ptrs_back"][p], self.world,
                                                   d_out, rows_back, back[0], back[1])
-                    dist.all_reduce(dv["token"], group=self.group)    # every rank's results have landed
+                    multiplied.append(torch.cuda.Event())
+                    multiplied[-1].record(st)
+                    self._sync_ranks(dv, p)                           # every rank's results have landed
                     mine = dv["returned"][dv["pair_first"][p]:dv["pair_first"][p] + rows_back]
                     self.ops.combine_into(mine, r, res_in, out[sl])
                 else:
                     self.ops.grouped_indexed_into(hidden, self.w_down, offsets, index, False, res)
-                    dist.all_reduce(dv["token"], group=self.group)    # every rank's results are complete
+                    multiplied.append(torch.cuda.Event())
+                    multiplied[-1].record(st)
+                    self._sync_ranks(dv, p)                           # every rank's results are complete
+                    self._size_exchange(alone=(p == pieces - 1))
                     self.ops.ep_pull_combine(dv["ptrs_res"][p], r, dst_base, res_in,
                                              caps[p], self.world, self.experts, d_out, out[sl])
                 if st is not main:
                     out.record_stream(st)
+        self._size_exchange(alone=True)
         for st in streams:
             if st is not main:
                 main.wait_stream(st)
@@ -594,6 +648,21 @@ class ExpertParallelMoe:
                      "rows_received": None, "rows_sent": n * self.top_k,
                      "group_offsets": [t[3] for t in routed], "accepted_counts": [t[1].accepted_counts for t in routed]}
         return out
+
+    def _size_exchange(self, alone: bool):
+        """Grid of the next dispatch / combine kernel (read by the library when it is enqueued)."""
+        if self.exchange_ctas:
+            if alone:
+                self.ops.gemm.set_exchange_ctas(0)
+            else:
+                self.ops.gemm.set_exchange_ctas(self.exchange_ctas, self.exchange_bulk)
+
+    def _sync_ranks(self, dv, p):
+        """Stream-ordered barrier of slice ``p``: the barrier kernel, or a one-element all-reduce."""
+        if dv["barriers"] is not None:
+            dv["barriers"][p].barrier()
+        else:
+            dist.all_reduce(dv["token"], group=self.group)
 
     def rows_sent_remote(self) -> int:
         """Routed rows of the last forward whose expert lives on another rank (synchronises)."""
@@ -760,10 +829,12 @@ class ExpertParallelMoe:
             self._index = torch.arange(local, dtype=torch.int32, device=device).repeat(self.world)
         return self._index
 
-    def _streams(self, device):
+    def _streams(self, device, count: int = 2):
         if self._side is None:
-            self._side = [torch.cuda.Stream(device=device), torch.cuda.Stream(device=device)]
-        return self._side
+            self._side = []
+        while len(self._side) < count:
+            self._side.append(torch.cuda.Stream(device=device))
+        return self._side[:count]
 
 
 class _NullCtx:
@@ -805,6 +876,61 @@ class PeerExchange:
         dist.all_reduce(self._token, group=self.group)
 
 
+class PeerBarrier:
+    """Stream-ordered barrier between the GPUs of one box, made of one tiny kernel per rank.
+
+    Each rank owns ``world`` arrival words in symmetric memory.  ``barrier()`` launches a
+    one-block kernel on the current stream that writes this rank's epoch into its word on
+    every peer and waits (bounded) until all of its own words reached the epoch.  The kernel
+    uses no shared memory and fits on an SM beside a persistent GEMM CTA, so it neither waits
+    for the GEMM to finish nor needs SMs kept free, which a one-element NCCL all-reduce does;
+    it costs a launch and one NVLink round trip.  ``all_gather_i32`` gathers a few integers
+    per rank on the way (the expert-parallel exchange's per-expert counts).
+
+    Every rank must call the same sequence on ONE stream per object (epochs count up); a
+    wait that runs out leaves device status 108 on the handle and the object unusable."""
+
+    def __init__(self, ops, group, device, payload_count: int = 0, limit_ms: int = 2000):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm_mem
+        self.ops = ops
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.limit_ms, self.count, self.epoch = limit_ms, payload_count, 0
+        name = self.group.group_name
+        self._words = symm_mem.empty((self.world,), dtype=torch.int64, device=device)
+        self._words.zero_()
+        self._h_words = symm_mem.rendezvous(self._words, name)
+        self._ptr_words = (C.c_void_p * self.world)()
+        for r in range(self.world):
+            self._ptr_words[r] = self._h_words.get_buffer(r, (self.world,), torch.int64).data_ptr()
+        self._ptr_tables = None
+        if payload_count:
+            shape = (2, self.world, payload_count)
+            self._table = symm_mem.empty(shape, dtype=torch.int32, device=device)
+            self._h_table = symm_mem.rendezvous(self._table, name)
+            self._ptr_tables = (C.c_void_p * self.world)()
+            for r in range(self.world):
+                self._ptr_tables[r] = self._h_table.get_buffer(r, shape, torch.int32).data_ptr()
+        # no peer may write an arrival word before every rank has zeroed its own
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
+
+    def barrier(self):
+        self.epoch += 1
+        self.ops.peer_barrier(self._ptr_words, self.world, self.rank, self.epoch, self.limit_ms)
+
+    def all_gather_i32(self, mine):
+        """Every rank's ``mine`` (int32, ``payload_count`` long) as ``[world, payload_count]``: a
+        view of this rank's table, valid until the second next call."""
+        if mine.numel() != self.count or mine.dtype != torch.int32:
+            raise ValueError("payload must be payload_count int32")
+        self.epoch += 1
+        self.ops.peer_barrier(self._ptr_words, self.world, self.rank, self.epoch, self.limit_ms, mine,
+                              self._ptr_tables)
+        return self._table[self.epoch & 1]
+
+
 def exchange_plan(counts_all, rank, world):
     """Offsets of a dispatch from the full counts matrix ``counts_all[src, expert]`` (host ints).
 
@@ -832,11 +958,14 @@ class PeerRowExchange:
     between peer-mapped buffers: the copy engines move the bytes over NVLink, no SM is
     involved), a one-element all-reduce orders the ranks, and a small kernel of this library
     adds the ``world`` parts that arrived (fp32 adds, rank order).  The all-gather is the same
-    without the sum.  Buffers are ``torch.distributed`` symmetric memory; no kernel here reads
-    or writes a peer's memory and nothing spins on a peer's flag."""
+    without the sum.  Buffers are ``torch.distributed`` symmetric memory; the row data moves by
+    copy engine only, and the ranks wait for one another in a one-block barrier kernel
+    (``PeerBarrier``, bounded wait) or, on request, a one-element all-reduce."""
 
-    def __init__(self, ops, group, device, shares, width, dtype=torch.bfloat16):
-        """``shares[s]`` = rows every rank owns in slot ``s`` (slots may differ in size)."""
+    def __init__(self, ops, group, device, shares, width, dtype=torch.bfloat16, barrier="kernel"):
+        """``shares[s]`` = rows every rank owns in slot ``s`` (slots may differ in size).
+        ``barrier``: "kernel" = this library's barrier kernel (``PeerBarrier``), "nccl" = a
+        one-element all-reduce."""
         import torch.distributed._symmetric_memory as symm_mem
         self.ops = ops
         self.group = group if group is not None else dist.group.WORLD
@@ -853,6 +982,7 @@ class PeerRowExchange:
         self._peer_inbox = [self._h_in.get_buffer(r, (total,), dtype) for r in range(self.world)]
         self._peer_gathered = [self._h_all.get_buffer(r, (total,), dtype) for r in range(self.world)]
         self._token = torch.zeros(1, device=device)
+        self._barrier = PeerBarrier(ops, self.group, device) if barrier == "kernel" else None
 
     def _slot(self, flat, slot):
         """``[world, share, width]`` view of slot ``slot`` of a flat buffer."""
@@ -862,7 +992,10 @@ class PeerRowExchange:
 
     def barrier(self):
         """Stream-ordered: what follows on this stream starts after every rank got here."""
-        dist.all_reduce(self._token, group=self.group)
+        if self._barrier is not None:
+            self._barrier.barrier()
+        else:
+            dist.all_reduce(self._token, group=self.group)
 
     def reduce_scatter(self, slot, partial, out):
         """``out [share, width] = sum over ranks of their partial[rank_rows]``; ``partial`` is
@@ -903,8 +1036,10 @@ class TensorParallelMlp:
     at both ends shorten exactly that, while the long ones in the middle keep the GEMMs large."""
 
     def __init__(self, ops, w_up_shard, w_down_shard, group=None, chunks=4,
-                 partial_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl"):
+                 partial_dtype=torch.bfloat16, reserve_sms: int = 0, exchange: str = "nccl",
+                 barrier: str = "kernel"):
         self.ops, self.group, self.chunks = ops, group, chunks
+        self.barrier = barrier              # how the copy exchange orders the ranks (PeerRowExchange)
         self.reserve_sms = reserve_sms      # SMs every GEMM leaves to the collectives on the side stream
         self.world, self.rank = _world(group)
         self.w_up, self.w_down = w_up_shard, w_down_shard
@@ -936,7 +1071,7 @@ class TensorParallelMlp:
             if self.w_down.shape[1] != x.shape[1]:
                 raise ValueError("the copy exchange needs the MLP's input and output widths to match")
             self._px = PeerRowExchange(self.ops, self.group, x.device, [rows // self.world for _, rows in plan],
-                                       x.shape[1], self.partial_dtype)
+                                       x.shape[1], self.partial_dtype, barrier=self.barrier)
             self._px_key = key
         return self._px
 

@@ -83,7 +83,7 @@ def test_cpp_host_mirror_compiles_links_and_covers_the_header(pkg, tmp_path):
       int rc = g.f32_store_with_bf16_copy(stream, a, b, f, p);
       rc |= g.grouped_gemm_swiglu(stream, a, b, 1, i, p, 0, p, 0, i, 1, 128);
       rc |= g.grouped_gemm_indexed(stream, a, b, 1, i, p, 0, i, 1, 0);
-      rc |= g.set_scheduler(true) | g.set_sm_limit(0) | g.device_status(stream);
+      rc |= g.set_scheduler(true) | g.set_sm_limit(0) | g.set_exchange_ctas(0, false) | g.device_status(stream);
       rc |= g.convert_f32_to_bf16(stream, f, p, 8) | g.transpose_bf16(stream, p, p, 8, 8);
       rc |= g.sgemm(stream, 0, false, f, f, f, 4, 4, 4);
       return rc;

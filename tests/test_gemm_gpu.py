@@ -229,6 +229,43 @@ def test_bounded_wait_reports_a_status_code_and_the_context_survives(pkg, oracle
     assert_gemm_close(c.cpu().numpy(), oracle.matmul_nt(av, bv, THREADS), "after timeout", rel_fro=2e-5, elem=2e-4)
 
 
+def test_peer_barrier_passes_when_the_peer_arrived_and_gives_up_when_it_did_not(pkg, gemm):
+    """The barrier between GPUs, both "ranks'" arrays on this GPU and the peer played by the
+    host: with the peer's arrival word already written the kernel passes, delivers its integers
+    into both tables (the half the epoch selects) and leaves status 0; with a word nothing
+    writes it gives up after its limit with code 108 and the handle stays usable."""
+    import ctypes as C
+    import torch
+    ops = pkg.parallel.DeviceOps(gemm)
+    world, count = 2, 5
+    words = [torch.zeros(world, dtype=torch.int64, device="cuda") for _ in range(world)]
+    tables = [torch.full((2, world, count), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    pw, pt = (C.c_void_p * world)(), (C.c_void_p * world)()
+    for r in range(world):
+        pw[r], pt[r] = words[r].data_ptr(), tables[r].data_ptr()
+    mine = torch.arange(10, 10 + count, dtype=torch.int32, device="cuda")
+    for epoch in (1, 2):
+        words[0][1] = epoch                                   # "rank 1" has arrived
+        ops.peer_barrier(pw, world, 0, epoch, 200, mine + epoch, pt)
+        assert gemm.device_status() == 0
+        assert words[0].tolist() == [epoch, epoch] and words[1].tolist() == [epoch, 0]
+        for t in tables:
+            assert t[epoch & 1, 0].tolist() == (mine + epoch).tolist()
+            assert t[epoch & 1, 1].tolist() == [-1] * count   # the peer's row is the peer's to write
+    assert tables[0][1, 0].tolist() == (mine + 1).tolist()    # the other half kept the previous epoch's
+    ops.peer_barrier(pw, world, 0, 3, 50)                     # nobody writes epoch 3 into words[0][1]
+    with pytest.raises(pkg.B200GemmError) as e:
+        gemm.device_status()
+    assert e.value.code == pkg._lib.ERR_DEVICE and "108" in str(e.value)
+    assert gemm.device_status() == 0
+    ops.peer_barrier((C.c_void_p * 1)(words[0].data_ptr()), 1, 0, 4, 50)    # a world of one never waits
+    assert gemm.device_status() == 0
+    with pytest.raises(pkg.B200GemmError):
+        ops.peer_barrier(pw, world, 0, 0, 50)                 # epochs start at 1
+    with pytest.raises(pkg.B200GemmError):
+        ops.peer_barrier(pw, world, 2, 1, 50)                 # rank outside the world
+
+
 def test_host_buffer_form_copies_in_and_out(pkg, oracle, gemm):
     """b200gemm_gemm_host: A, B (and C when accumulating) live in host memory."""
     import ctypes as C

@@ -61,6 +61,42 @@ def test_emulated_ranks_match_single_gpu_moe(pkg, oracle, world, experts, top_k,
         out = torch.empty((tokens, d), dtype=torch.float32, device="cuda")
         ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], xs[r], cap, world, experts, d, out)
         assert torch.allclose(out, want[r], atol=1e-5, rtol=1e-5), float((out - want[r]).abs().max())
+        # the few-block forms (stores from 3 or 16 blocks; rows fetched by bulk copies into a
+        # shared-memory ring): the same sums in the same order, so the same bits, fp32 and bf16
+        for ctas in (3, 16):
+            gemm.set_exchange_ctas(ctas, bulk=True)
+            for dtype in (torch.float32, torch.bfloat16):
+                ref_out = torch.empty((tokens, d), dtype=dtype, device="cuda")
+                gemm.set_exchange_ctas(0)
+                ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], xs[r], cap, world, experts, d, ref_out)
+                gemm.set_exchange_ctas(ctas, bulk=True)
+                few = torch.full((tokens, d), float("nan"), dtype=dtype, device="cuda")
+                ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], xs[r], cap, world, experts, d, few)
+                assert torch.equal(few, ref_out), (ctas, dtype)
+            few = torch.full((tokens, d), float("nan"), dtype=torch.float32, device="cuda")
+            ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], None, cap, world, experts, d, few)   # no residual
+            gemm.set_exchange_ctas(0)
+            ref_out = torch.empty((tokens, d), dtype=torch.float32, device="cuda")
+            ops.ep_pull_combine(ptr_res, routed[r], plans[r][0], None, cap, world, experts, d, ref_out)
+            assert torch.equal(few, ref_out), ctas
+        gemm.set_exchange_ctas(0)
+    assert gemm.device_status() == 0
+    # pushes from a few blocks land the same rows
+    gemm.set_exchange_ctas(5, bulk=True)
+    inbox2 = [torch.zeros((cap, d), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    ptr_in2 = (C.c_void_p * world)(*[t.data_ptr() for t in inbox2])
+    for r in range(world):
+        ops.ep_push(xs[r], routed[r], plans[r][0], ptr_in2, cap, world, experts)
+    gemm.set_exchange_ctas(0)
+    for a, b in zip(inbox, inbox2):
+        assert torch.equal(a, b)
+    # a result buffer that is too small for the bulk form too: rows beyond it are left out and reported
+    gemm.set_exchange_ctas(4, bulk=True)
+    few = torch.empty((tokens, d), dtype=torch.float32, device="cuda")
+    ops.ep_pull_combine(ptr_res, routed[0], plans[0][0], xs[0], 1, world, experts, d, few)
+    gemm.set_exchange_ctas(0)
+    with pytest.raises(pkg.B200GemmError):
+        gemm.device_status()
     assert gemm.device_status() == 0
 
     # The return leg fused into the expert GEMM: every owner's down projection stores its rows
@@ -98,8 +134,10 @@ def test_emulated_ranks_match_single_gpu_moe(pkg, oracle, world, experts, top_k,
     # (the last rank's rows come last in every inbox, so some of them must fall beyond the limit)
     small = max(1, int(c[:, :local].sum()) // 2)
     last = world - 1
-    ops.ep_push(xs[last], routed[last], plans[last][0], ptr_in, small, world, experts)
-    with pytest.raises(pkg.B200GemmError):
-        gemm.device_status()
-    assert gemm.device_status() == 0
+    for ctas in (0, 4, 7):                                # the store-driven form, the bulk-copy form, few blocks
+        gemm.set_exchange_ctas(ctas, bulk=ctas == 4)
+        ops.ep_push(xs[last], routed[last], plans[last][0], ptr_in, small, world, experts)
+        with pytest.raises(pkg.B200GemmError):
+            gemm.device_status()
+        assert gemm.device_status() == 0
     gemm.close()

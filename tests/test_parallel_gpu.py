@@ -42,6 +42,36 @@ def _worker(rank, port, failures):
         gen.manual_seed(5)                                   # same data on every rank
         bf = torch.bfloat16
 
+        # ---- the barrier kernel: integers gathered on the way, data stored before it visible after it
+        bar = par.PeerBarrier(ops, None, dev, payload_count=6)
+        import torch.distributed._symmetric_memory as symm_mem
+        box = symm_mem.empty((WORLD, 4096), dtype=torch.float32, device=dev)
+        hbox = symm_mem.rendezvous(box, dist.group.WORLD.group_name)
+        for step in range(1, 5):
+            mine = torch.arange(6, dtype=torch.int32, device=dev) * (rank + 1) + 100 * step
+            for r in range(WORLD):                            # my row of every rank's box
+                hbox.get_buffer(r, (WORLD, 4096), torch.float32)[rank].copy_(
+                    torch.full((4096,), float(step * 10 + rank), device=dev), non_blocking=True)
+            got = bar.all_gather_i32(mine)
+            for r in range(WORLD):
+                assert got[r].tolist() == [j * (r + 1) + 100 * step for j in range(6)], (step, r)
+                assert bool((box[r] == float(step * 10 + r)).all()), (step, r)
+            bar.barrier()                                     # nobody overwrites a row a peer still reads
+        assert gemm.device_status() == 0
+        # a peer that never comes: the wait gives up, the host reads code 108, the context
+        # stays usable (only rank 0 calls; its arrival word stays behind, so the object is dropped)
+        lonely = par.PeerBarrier(ops, None, dev, limit_ms=100)
+        if rank == 0:
+            lonely.barrier()
+            try:
+                gemm.device_status()
+                raise AssertionError("the wait should have run out")
+            except pkg.B200GemmError as e:
+                assert e.code == pkg._lib.ERR_DEVICE and "108" in str(e)
+        assert gemm.device_status() == 0
+        dist.barrier()
+        del lonely
+
         # ---- vocabulary-parallel head vs the single-GPU fused head
         m, k, v, classes = 1024, 256, 2048, 2000
         h = torch.randn((m, k), generator=gen, device=dev).to(bf)
@@ -128,6 +158,22 @@ def _worker(rank, port, failures):
             out3 = ep3.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
             assert ep3.last["exchange"] == "device"
             assert torch.allclose(out3, ref, atol=1e-5, rtol=1e-5), float((out3 - ref).abs().max())
+        # ... with NCCL's all-gather and one-element all-reduces in place of the barrier kernel
+        ep6 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=2, exchange="device",
+                                    barrier="nccl")
+        for _ in range(2):
+            out6 = ep6.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert torch.equal(out6, out3)
+        # ... in four slices whose middle dispatches and combines are the few-block bulk-copy kernels
+        ep7 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
+                                    dn[rank * local:(rank + 1) * local].contiguous(), pieces=4, exchange="device",
+                                    exchange_ctas=6, exchange_bulk=True)
+        ep7.reserve_sms = 8
+        for _ in range(2):
+            out7 = ep7.forward(x[rank].contiguous(), logits[rank].contiguous(), scores_are_logits=True)
+            assert ep7.last["pieces"] == 4
+            assert torch.equal(out7, out3)
         # ... with the results sent home by the owner's down-projection GEMM itself (peer stores from its epilogue)
         ep5 = par.ExpertParallelMoe(ops, experts, top_k, up[rank * local:(rank + 1) * local].contiguous(),
                                     dn[rank * local:(rank + 1) * local].contiguous(), pieces=2, exchange="device",
@@ -168,13 +214,15 @@ def _worker(rank, port, failures):
         shard = (w1[:, cols].contiguous(), w2[cols].contiguous())
         mlp_nccl = par.TensorParallelMlp(ops, *shard, chunks=[1, 2, 1], partial_dtype=bf)
         mlp_copy = par.TensorParallelMlp(ops, *shard, chunks=[1, 2, 1], partial_dtype=bf, exchange="copy")
+        mlp_copy_nccl = par.TensorParallelMlp(ops, *shard, chunks=[1, 2, 1], partial_dtype=bf, exchange="copy",
+                                              barrier="nccl")
         dy_local = (torch.randn((m // WORLD, d), generator=gen, device=dev) * 0.1).to(bf)
         rows = mlp_copy.owned_rows(m)                          # short pieces at both ends: another ownership
         pick = rows[[0, 1, len(rows) // 2, len(rows) - 1]]
         hid = orc.bf16_round(orc.matmul(x2[pick].float().cpu().numpy(), w1.float().cpu().numpy(), 4))
         full = orc.matmul(hid, w2.float().cpu().numpy(), 4)
         outs = []
-        for blk in (mlp_nccl, mlp_copy, mlp_copy):
+        for blk in (mlp_nccl, mlp_copy, mlp_copy, mlp_copy_nccl):
             dw1 = torch.zeros((d, ff // WORLD), device=dev, dtype=torch.float32)
             dw2 = torch.zeros((ff // WORLD, d), device=dev, dtype=torch.float32)
             yb = blk.forward(x2)
@@ -184,7 +232,7 @@ def _worker(rank, port, failures):
         assert mlp_copy._px is not None
         got = outs[1][0][[0, 1, len(rows) // 2, len(rows) - 1]].cpu().numpy()
         assert np.linalg.norm(got - full) / np.linalg.norm(full) <= 1e-2         # against the oracle rows above
-        for a, b in ((outs[0], outs[1]), (outs[1], outs[2])):
+        for a, b in ((outs[0], outs[1]), (outs[1], outs[2]), (outs[1], outs[3])):
             for u, v2, what in zip(a, b, ("y", "dx", "dw_up", "dw_down")):
                 rel = float((u - v2).norm() / u.norm())
                 assert rel <= (1e-2 if a is outs[0] else 1e-6), (what, rel)
