@@ -102,8 +102,9 @@ def cpu_sample(threads: int, rows: int | None = None, k_tokens: int | None = Non
     `k_tokens` of the 32768-token reduction.  Returns (seconds, flops, text)."""
     from oracle import oracle as orc
     orc.build()
-    # About 130 MFLOP per sampled row: 128 rows per thread is roughly 10 s of scalar work.
-    rows = min(8192, 128 * threads) if rows is None else rows
+    # About 130 MFLOP per sampled row; measured at 4.8 GFLOP/s per host core of the GPU box, so
+    # 384 rows per thread are about 10 s of scalar work.
+    rows = min(8192, 384 * threads) if rows is None else rows
     k_tokens = rows if k_tokens is None else k_tokens
     flops, secs = 0.0, 0.0
     for _, i, o in PROJECTIONS:
@@ -371,11 +372,11 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
 SHARDED = ("lmhead", "tp_mlp", "moe")
 MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
-MOE_PIECES = 2                 # set from --moe-pieces: token slices of the expert-parallel step
+MOE_PIECES = 4                 # set from --moe-pieces: token slices of the expert-parallel step
 MOE_RETURN = "pull"            # set from --moe-return
-MOE_RESERVE = None             # set from --moe-reserve-sms
-MOE_CTAS = 0                   # set from --moe-exchange-ctas
-MOE_BULK = False               # set from --moe-exchange-bulk
+MOE_RESERVE = 24               # set from --moe-reserve-sms
+MOE_CTAS = 48                  # set from --moe-exchange-ctas
+MOE_BULK = True                # set from --moe-exchange-form
 RANK_BARRIER = "kernel"        # set from --rank-barrier: how the copy / device exchanges order the ranks
 MLP_PIECES = [1, 3, 4, 4, 3, 1]   # set from --mlp-pieces (several GPUs)
 
@@ -468,9 +469,13 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         w.flops = 2.0 * n_tok * top_k * d * ff * 2
         w.title = ("MoE grouped expert GEMM: 32768 tokens per GPU, D=1536, E=64, top-8, expert FF=768, "
                    "up -> SiLU -> down, Zipf-skewed routing; routing, dispatch and combine included")
-        w.par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch by peer stores and combine by "
-                      "peer loads over NVLink (symmetric memory, sizes never leave the device), NCCL for the "
-                      f"counts and the two barriers; {MOE_PIECES} token slices on two streams")
+        how = ("bulk asynchronous copies through shared memory" if MOE_BULK and MOE_CTAS else "peer stores / peer loads")
+        sync = ("this library's barrier kernel, which also gathers the counts" if RANK_BARRIER == "kernel"
+                else "NCCL for the counts and the barriers")
+        w.par_text = (f"experts split over {world} GPU(s), 32768 tokens on each; dispatch and combine by {how} over "
+                      f"NVLink (symmetric memory, sizes never leave the device; {MOE_CTAS or 'two per SM'} blocks beside "
+                      f"the GEMMs, which leave {ep.reserve_sms} SMs free), results returned by {MOE_RETURN}; {sync}; "
+                      f"{MOE_PIECES} token slices as a pipeline")
         w.host_in, w.scaling, w.extra = x, "weak", ep
         w.compute_ops = ("route", "scatter", "combine", "combine_into", "grouped_indexed", "grouped_indexed_into",
                          "grouped_indexed_peer", "ep_plan", "ep_return_plan")
@@ -1063,7 +1068,7 @@ def main():
                     help="dense_step (default) is the headline; the others are the sharded configurations")
     ap.add_argument("--head-exchange", default="copy", choices=["copy", "nccl"],
                     help="vocabulary-parallel head on several GPUs: how d_hidden is summed over the shards")
-    ap.add_argument("--moe-pieces", default="2",
+    ap.add_argument("--moe-pieces", default="4",
                     help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams; "
                          "a count, or comma-separated weights such as 1,3,3,1")
     ap.add_argument("--moe-return", default="pull", choices=["pull", "push"],
@@ -1073,12 +1078,14 @@ def main():
                     help="tensor-parallel MLP on several GPUs: row pieces, a count or comma-separated weights")
     ap.add_argument("--mlp-exchange", default="copy", choices=["copy", "nccl"],
                     help="tensor-parallel MLP on several GPUs: copy-engine pushes + local sum, or NCCL collectives")
-    ap.add_argument("--moe-reserve-sms", type=int, default=None,
-                    help="expert-parallel MoE: SMs the expert GEMMs leave free (default: the class's)")
-    ap.add_argument("--moe-exchange-ctas", type=int, default=0,
-                    help="expert-parallel MoE: thread blocks of the dispatch / combine kernels (0 = two per SM)")
-    ap.add_argument("--moe-exchange-bulk", action="store_true",
-                    help="expert-parallel MoE: the bulk-copy forms of the dispatch / combine kernels")
+    ap.add_argument("--moe-reserve-sms", type=int, default=24,
+                    help="expert-parallel MoE: SMs the expert GEMMs leave free for the exchange kernels")
+    ap.add_argument("--moe-exchange-ctas", type=int, default=48,
+                    help="expert-parallel MoE: thread blocks of the dispatch / combine kernels that run beside a GEMM "
+                         "(0 = two per SM)")
+    ap.add_argument("--moe-exchange-form", default="bulk", choices=["bulk", "plain"],
+                    help="expert-parallel MoE: dispatch / combine by bulk asynchronous copies through shared memory, "
+                         "or by plain stores / loads")
     ap.add_argument("--timeline-spans", action="store_true",
                     help="with --workload: add every timed call of the analysed step (name, start ms, end ms)")
     ap.add_argument("--rank-barrier", default="kernel", choices=["kernel", "nccl"],
@@ -1086,7 +1093,7 @@ def main():
                          "barrier kernel over peer memory, or one-element NCCL all-reduces")
     args = ap.parse_args()
     global MLP_EXCHANGE, HEAD_EXCHANGE, MOE_PIECES, MOE_RETURN, MLP_PIECES, RANK_BARRIER, MOE_RESERVE, MOE_CTAS, MOE_BULK
-    MOE_RESERVE, MOE_CTAS, MOE_BULK = args.moe_reserve_sms, args.moe_exchange_ctas, args.moe_exchange_bulk
+    MOE_RESERVE, MOE_CTAS, MOE_BULK = args.moe_reserve_sms, args.moe_exchange_ctas, args.moe_exchange_form == "bulk"
     RANK_BARRIER = args.rank_barrier
     MOE_RETURN = args.moe_return
     parts = [int(v) for v in str(args.mlp_pieces).split(",")]

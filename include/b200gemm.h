@@ -564,7 +564,8 @@ B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const v
  *                 `result_rows` is skipped and device status 105 recorded.
  * The caller orders the phases between ranks (a barrier after every rank's push and
  * after every rank's expert GEMMs); the kernels themselves never wait on a peer.
- * world <= 8, experts a multiple of world and <= 192, top_k <= 16, d % 8 == 0.
+ * world <= 8, experts a multiple of world and <= 192, top_k <= 16, d % 8 == 0; every row buffer
+ * (x, the peers' inboxes and result buffers, residual, out) 16-byte aligned.
  */
 B200GEMM_API int b200gemm_moe_ep_plan(b200gemm_handle_t h, void* stream, const int32_t* all_counts,
                                       int32_t world, int32_t rank, int32_t experts, int32_t* dst_base,

@@ -1228,12 +1228,15 @@ int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const
   if (rc) return rc;
   if (!x || !selected || !slots || !dst_base || !peer_inbox) return fail(B200GEMM_ERR_INVALID, "null pointer");
   if (inbox_rows <= 0) return fail(B200GEMM_ERR_SHAPE, "inbox_rows must be positive");
+  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return fail(B200GEMM_ERR_SHAPE, "x is not 16-byte aligned");
   if (world < 1 || world > kMoeMaxPeers || experts % world) return fail(B200GEMM_ERR_SHAPE, "bad world / experts");
   if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
     return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
   PeerPointers pp = {};
   for (int r = 0; r < world; ++r) {
     if (!peer_inbox[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
+    if ((reinterpret_cast<uintptr_t>(peer_inbox[r]) & 15u) != 0)
+      return fail(B200GEMM_ERR_SHAPE, "peer inbox %d is not 16-byte aligned", r);
     pp.ptr[r] = static_cast<uint16_t*>(peer_inbox[r]);
   }
   if (h->exchange_bulk) {
@@ -1285,9 +1288,13 @@ int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const*
   if (tokens <= 0 || top_k < 1 || top_k > kMoeMaxTopK || d <= 0 || (d % 8) != 0)
     return fail(B200GEMM_ERR_SHAPE, "need tokens > 0, top_k in [1, %d], d a multiple of 8", kMoeMaxTopK);
   if (out_type < 0 || out_type > 1) return fail(B200GEMM_ERR_INVALID, "bad output type");
+  if (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual)) & 15u) != 0)
+    return fail(B200GEMM_ERR_SHAPE, "out / residual not 16-byte aligned");
   PeerPointers pp = {};
   for (int r = 0; r < world; ++r) {
     if (!peer_results[r]) return fail(B200GEMM_ERR_INVALID, "null peer pointer %d", r);
+    if ((reinterpret_cast<uintptr_t>(peer_results[r]) & 15u) != 0)
+      return fail(B200GEMM_ERR_SHAPE, "peer result buffer %d is not 16-byte aligned", r);
     pp.ptr[r] = static_cast<uint16_t*>(peer_results[r]);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -443,7 +443,7 @@ class ExpertParallelMoe:
 
     def __init__(self, ops, experts: int, top_k: int, w_up_local, w_down_local, group=None, pieces=1,
                  use_peer_copies: bool = False, exchange: str = "nccl", return_path: str = "pull",
-                 barrier: str = "kernel", exchange_ctas: int = 0, exchange_bulk: bool = False):
+                 barrier: str = "kernel", exchange_ctas: int = 48, exchange_bulk: bool = True):
         self.ops, self.group, self.experts, self.top_k = ops, group, experts, top_k
         # device exchange: thread blocks of the dispatch / combine kernels that run beside an
         # expert GEMM (0 = two per SM) and whether they are the bulk-copy forms, which fill the
@@ -462,7 +462,7 @@ class ExpertParallelMoe:
         # from its owner (peer loads) while it combines; "push" = the owner's down-projection GEMM
         # stores its rows into the token rank's buffer from its epilogue, and the combine is local
         self.return_path = return_path
-        self.reserve_sms = 4                            # SMs kept free of GEMM CTAs in the device path
+        self.reserve_sms = 24                           # SMs kept free of GEMM CTAs in the device path
         self.world, self.rank = _world(group)
         if experts % self.world:
             raise ValueError("experts must divide evenly over the ranks")
