@@ -413,7 +413,7 @@ def per_shape_table(torch, gemm, head, buf, iters=3):
 SHARDED = ("lmhead", "tp_mlp", "moe")
 MLP_EXCHANGE = "copy"          # set from --mlp-exchange
 HEAD_EXCHANGE = "copy"         # set from --head-exchange
-MOE_PIECES = 4                 # set from --moe-pieces: token slices of the expert-parallel step
+MOE_PIECES = [6, 5, 3, 2]      # set from --moe-pieces: token slices of the expert-parallel step
 MOE_RETURN = "pull"            # set from --moe-return
 MOE_RESERVE = 24               # set from --moe-reserve-sms
 MOE_CTAS = 48                  # set from --moe-exchange-ctas
@@ -1109,9 +1109,10 @@ def main():
                     help="dense_step (default) is the headline; the others are the sharded configurations")
     ap.add_argument("--head-exchange", default="copy", choices=["copy", "nccl"],
                     help="vocabulary-parallel head on several GPUs: how d_hidden is summed over the shards")
-    ap.add_argument("--moe-pieces", default="4",
-                    help="expert-parallel MoE: token slices whose exchanges and GEMMs alternate on two streams; "
-                         "a count, or comma-separated weights such as 1,3,3,1")
+    ap.add_argument("--moe-pieces", default="6,5,3,2",
+                    help="expert-parallel MoE: token slices that go through dispatch, GEMMs and combine as a pipeline; "
+                         "a count, or comma-separated weights (the default ends with short slices: what follows the "
+                         "last dispatch -- that slice's GEMMs and combine -- overlaps nothing)")
     ap.add_argument("--moe-return", default="pull", choices=["pull", "push"],
                     help="expert-parallel MoE: results read by the token's rank while it combines (pull), or stored "
                          "into the token rank's buffer by the owner's down-projection GEMM (push)")
