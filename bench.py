@@ -571,12 +571,17 @@ def time_steps(torch, dist, step, steps, local, sample_clocks=True):
         sampler.start()
     s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    mallocs = torch.cuda.memory_stats().get("num_device_alloc", 0)
     s0.record()
     for _ in range(steps):
         step()
     e0.record()
     barrier()
-    return s0.elapsed_time(e0) / steps, (sampler.stop() if sampler else None)
+    clocks = sampler.stop() if sampler else None
+    if clocks is not None:
+        # a cudaMalloc inside the timed region (the caching allocator growing) would stall the stream
+        clocks["cuda_mallocs_in_region"] = torch.cuda.memory_stats().get("num_device_alloc", 0) - mallocs
+    return s0.elapsed_time(e0) / steps, clocks
 
 
 def exchange_timeline(torch, dist, ops, w, spans_too=False):
@@ -723,7 +728,8 @@ def run_sharded(args):
 
     # The expert-parallel exchange sets up peer mappings, side streams and their scheduler
     # counters during its first steps; a few more untimed steps keep that out of the clock.
-    warmup = max(args.warmup, {"moe": 10, "tp_mlp": 6, "lmhead": 5}[args.workload])
+    # at least as many untimed steps as timed ones: see sharded_block
+    warmup = max(args.warmup, args.steps, {"moe": 10, "tp_mlp": 6, "lmhead": 5}[args.workload])
     for _ in range(warmup):
         launches = w.step()
     ms, clocks = time_steps(torch, dist, w.step, args.steps, local)
@@ -779,6 +785,15 @@ def run_sharded(args):
     dist.destroy_process_group()
 
 
+def device_code(torch, gemm) -> int:
+    """The handle's device status word (read and cleared), without raising."""
+    import ctypes
+    code = ctypes.c_int32(0)
+    gemm._lib.b200gemm_device_status(gemm._h, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+                                     ctypes.byref(code))
+    return int(code.value)
+
+
 def sharded_block(args, torch, dist, pkg, gemm, dev, rank, world, local):
     """The three sharded configurations at this run's N, device-timed (10 steps each), each
     with its exchange timeline: what the default line carries as `sharded`."""
@@ -786,11 +801,36 @@ def sharded_block(args, torch, dist, pkg, gemm, dev, rank, world, local):
     peaks = measured_peaks()
     steps = max(3, min(args.steps, 10))
     block = {}
+    global RANK_BARRIER
+    chosen = RANK_BARRIER
     for workload in SHARDED:
+        RANK_BARRIER = chosen
         w = build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world)
         # the exchanges set up peer mappings, side streams and scheduler counters in their first
         # steps, and the first steps through freshly mapped peer memory are slow: keep them out
-        for _ in range({"moe": 10, "tp_mlp": 6, "lmhead": 5}[workload]):
+        for _ in range(2):
+            w.step()
+        # A bounded wait that ran out on any rank (the barrier kernel gives up after 2 s) must not
+        # be repeated for twenty more steps: fall back to NCCL's barriers for this workload, once.
+        fell_back = None
+        code = torch.tensor([device_code(torch, gemm)], device=dev, dtype=torch.int32)
+        dist.all_reduce(code, op=dist.ReduceOp.MAX)
+        if int(code.item()) != 0:
+            fell_back = int(code.item())
+            if world == 1 or RANK_BARRIER != "kernel":
+                block[workload] = {"error": f"device status {fell_back} in the first steps"}
+                continue
+            del w
+            RANK_BARRIER = "nccl"
+            w = build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world)
+            for _ in range(2):
+                w.step()
+        # ... and at least as many steps as will be timed, enqueued the same way (no host
+        # synchronisation in between): the host runs several steps ahead of the GPU, every step in
+        # flight holds its own output buffers, and the caching allocator must have grown to that
+        # depth before the timed region, or it calls cudaMalloc inside it (reported per line as
+        # clocks.cuda_mallocs_in_region).
+        for _ in range(max({"moe": 8, "tp_mlp": 4, "lmhead": 3}[workload], steps)):
             w.step()
         ms, clocks = time_steps(torch, dist, w.step, steps, local)
         tt = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -799,10 +839,14 @@ def sharded_block(args, torch, dist, pkg, gemm, dev, rank, world, local):
         sub["steps"] = steps
         sub["exchange_timeline"] = exchange_timeline(torch, dist, ops, w)
         sub["device_status"] = gemm.device_status()
+        sub["rank_barrier"] = RANK_BARRIER if world > 1 else None
+        if fell_back is not None:
+            sub["rank_barrier_note"] = f"the barrier kernel left device status {fell_back}; NCCL's barriers were used instead"
         block[workload] = sub
         del w
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
+    RANK_BARRIER = chosen
     return block
 
 

@@ -77,22 +77,22 @@ class DeviceOps:
         return head.backward(hidden, weight_shard, local_targets, lse, dy=dy, d_weight=d_weight,
                              accumulate_dw=accumulate_dw)
 
-    def head_dlogits(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy):
+    def head_dlogits(self, hidden, weight_shard, local_targets, lse, classes_local, w_layout, dy, out=None):
         """First step of the shard's backward: the logits recomputed into bf16 dlogits."""
         head = self._FusedLmHead(self.gemm, classes_local, w_layout)
-        dl, _, _ = head.backward(hidden, weight_shard, local_targets, lse, dy=dy, want_d_hidden=False,
-                                 want_d_weight=False)
+        dl, _, _ = head.backward(hidden, weight_shard, local_targets, lse, dy=dy, dlogits=out,
+                                 want_d_hidden=False, want_d_weight=False)
         return dl
 
-    def head_dhidden_partial(self, dlogits, weight_shard, w_layout, dtype):
+    def head_dhidden_partial(self, dlogits, weight_shard, w_layout, dtype, out=None):
         """This shard's part of d_hidden = dlogits . W_shard^T, in `dtype`."""
         k = weight_shard.shape[0] if w_layout == "in_out" else weight_shard.shape[1]
-        dh = torch.empty((dlogits.shape[0], k), dtype=dtype, device=dlogits.device)
+        dh = torch.empty((dlogits.shape[0], k), dtype=dtype, device=dlogits.device) if out is None else out
         self.gemm.gemm(dlogits, weight_shard, dh, transposed_b=(w_layout != "in_out"))
         return dh
 
-    def widen(self, t):
-        return self.gemm.convert_bf16_to_f32(t)
+    def widen(self, t, out=None):
+        return self.gemm.convert_bf16_to_f32(t, out)
 
     def head_dweight(self, hidden, dlogits, w_layout, d_weight, accumulate_dw):
         """Second half: d_weight (=|+=) hidden^T . dlogits in the weight's orientation."""
@@ -205,13 +205,13 @@ class DeviceOps:
         return out
 
     # dense GEMMs (weights are [IN, OUT], read in place)
-    def linear(self, x, w, out_dtype=torch.bfloat16):
-        y = torch.empty((x.shape[0], w.shape[1]), dtype=out_dtype, device=x.device)
+    def linear(self, x, w, out_dtype=torch.bfloat16, out=None):
+        y = torch.empty((x.shape[0], w.shape[1]), dtype=out_dtype, device=x.device) if out is None else out
         self.gemm.gemm(x, w, y, transposed_b=True)
         return y
 
-    def linear_input_grad(self, dy, w, out_dtype=torch.bfloat16):
-        dx = torch.empty((dy.shape[0], w.shape[0]), dtype=out_dtype, device=dy.device)
+    def linear_input_grad(self, dy, w, out_dtype=torch.bfloat16, out=None):
+        dx = torch.empty((dy.shape[0], w.shape[0]), dtype=out_dtype, device=dy.device) if out is None else out
         self.gemm.gemm(dy, w, dx)
         return dx
 
@@ -331,6 +331,7 @@ class VocabParallelHead:
         self.classes_local = max(0, min(classes, self.c1) - self.c0)
         self._side = None
         self._lt = None
+        self._keep = None                   # buffers of the backward, kept between steps
 
     def shard_weight(self, weight_full):
         """This rank's columns of a full ``[hidden, vocab_padded]`` weight (a copy)."""
@@ -364,7 +365,8 @@ class VocabParallelHead:
 
     def backward(self, hidden, weight_shard, targets, lse, dy: float = 1.0, d_weight=None,
                  accumulate_dw: bool = False):
-        """Returns ``(dlogits shard, d_hidden summed over shards, d_weight shard)``."""
+        """Returns ``(dlogits shard, d_hidden summed over shards, d_weight shard)``.  On CUDA the
+        first two are buffers of this object: valid until the next ``backward``."""
         lt = self.local_targets(targets)
         if not hasattr(self.ops, "head_dweight") or hidden.device.type != "cuda":
             dl, dh, dw = self.ops.head_backward_shard(hidden, weight_shard, lt, lse, self.classes_local,
@@ -376,22 +378,33 @@ class VocabParallelHead:
         # travel as bf16 -- the reference's own d_hidden is a bf16 GEMM output that is
         # widened afterwards (gpu/model/src/lib.rs:3125-3145, 5777-5784) -- which halves
         # the message; `reduce_dtype=torch.float32` keeps fp32 partials instead.
-        dl = self.ops.head_dlogits(hidden, weight_shard, lt, lse, self.classes_local, self.w_layout, dy)
-        dh = self.ops.head_dhidden_partial(dl, weight_shard, self.w_layout, self.reduce_dtype)
+        # The large intermediates (dlogits: rows x local vocabulary; the d_hidden partial; this
+        # rank's rows of the sum; the widened result) live in buffers this object keeps: a step
+        # in steady state allocates nothing, and what is returned is valid until the next call.
+        m, k = hidden.shape
+        v_local = weight_shard.shape[1] if self.w_layout == "in_out" else weight_shard.shape[0]
+        key = (m, k, v_local, self.reduce_dtype, hidden.device)
+        if self._keep is None or self._keep["key"] != key:
+            dev, share = hidden.device, (m // self.world if m % self.world == 0 else m)
+            self._keep = {"key": key,
+                          "dl": torch.empty((m, v_local), dtype=torch.bfloat16, device=dev),
+                          "dh": torch.empty((m, k), dtype=self.reduce_dtype, device=dev),
+                          "mine": torch.empty((share, k), dtype=self.reduce_dtype, device=dev),
+                          "wide": {}}
+        keep = self._keep
+        dl = self.ops.head_dlogits(hidden, weight_shard, lt, lse, self.classes_local, self.w_layout, dy,
+                                   out=keep["dl"])
+        dh = self.ops.head_dhidden_partial(dl, weight_shard, self.w_layout, self.reduce_dtype, out=keep["dh"])
         if self._side is None:
             self._side = torch.cuda.Stream(device=hidden.device)
         self._side.wait_stream(torch.cuda.current_stream())
-        m, k = dh.shape
         use_copy = self.exchange == "copy" and self.world > 1 and m % self.world == 0
         scatter = self.d_hidden == "scatter" and m % self.world == 0
         if use_copy and (self._px is None or self._px_key != (m, k, dh.dtype)):
             self._px = PeerRowExchange(self.ops, self.group, dh.device, [m // self.world], k, dh.dtype,
                                        barrier=self.barrier)
             self._px_key = (m, k, dh.dtype)
-        mine = None
-        if use_copy or scatter:
-            mine = torch.empty((m // self.world, k), dtype=dh.dtype, device=dh.device)
-            mine.record_stream(self._side)
+        mine = keep["mine"] if (use_copy or scatter) else None
         with torch.cuda.stream(self._side):
             if use_copy:
                 self._px.reduce_scatter(0, dh, mine)
@@ -402,13 +415,15 @@ class VocabParallelHead:
             else:
                 dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=self.group)
                 summed = dh
-        dh.record_stream(self._side)
         dh = summed
         with _ReservedSms(self.ops, self.reserve_sms):
             dw = self.ops.head_dweight(hidden, dl, self.w_layout, d_weight, accumulate_dw)
         torch.cuda.current_stream().wait_stream(self._side)
         if dh.dtype != torch.float32:
-            dh = self.ops.widen(dh)
+            wide = keep["wide"].get(tuple(dh.shape))
+            if wide is None:
+                wide = keep["wide"][tuple(dh.shape)] = torch.empty(dh.shape, dtype=torch.float32, device=dh.device)
+            dh = self.ops.widen(dh, wide)
         return dl, dh, dw
 
 
@@ -539,7 +554,12 @@ class ExpertParallelMoe:
                          "barriers": ([PeerBarrier(self.ops, grp, x.device, payload_count=self.experts)
                                        for _ in slices] if self.barrier == "kernel" else None)}
         dv = self._dev
-        out = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
+        # the result lives in a buffer this object keeps (valid until the next forward): a step
+        # in steady state allocates nothing large, so the caching allocator never grows while
+        # the host runs ahead of the GPU
+        out = dv.get(("out", out_dtype))
+        if out is None:
+            out = dv[("out", out_dtype)] = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
         # The expert GEMMs leave a few SMs to the one-element all-reduces used as barriers
         # and to the other slice's small kernels.
         with _ReservedSms(self.ops, self.reserve_sms):
@@ -1048,6 +1068,7 @@ class TensorParallelMlp:
         # "nccl": reduce_scatter_tensor / all_gather_into_tensor; "copy": copy-engine pushes into
         # peer memory + a local sum (PeerRowExchange), CUDA tensors and more than one rank only
         self.exchange, self._px, self._px_key = exchange, None, None
+        self._bufs = {}
 
     def pieces(self, m: int):
         """``[(first row, rows), ...]`` of the pieces ``m`` rows are processed in."""
@@ -1074,6 +1095,19 @@ class TensorParallelMlp:
                                        x.shape[1], self.partial_dtype, barrier=self.barrier)
             self._px_key = key
         return self._px
+
+    def _buf(self, name, shape, dtype, device):
+        """A buffer this object keeps between steps (CUDA): a step in steady state allocates
+        nothing, so the caching allocator never has to grow -- or call cudaMalloc -- while the
+        host runs several steps ahead of the GPU.  What ``forward`` / ``backward`` return lives
+        in such buffers and is valid until the next call of the same method."""
+        if device.type != "cuda":
+            return torch.empty(shape, dtype=dtype, device=device)
+        key = (name, tuple(shape), dtype)
+        t = self._bufs.get(key)
+        if t is None:
+            t = self._bufs[key] = torch.empty(shape, dtype=dtype, device=device)
+        return t
 
     def _side_stream(self, device):
         if device.type != "cuda":
@@ -1109,16 +1143,24 @@ class TensorParallelMlp:
     def _forward(self, x):
         m, d = x.shape[0], self.w_down.shape[1]
         plan = self.pieces(m)
-        out = torch.empty((m // self.world, d), dtype=self.partial_dtype, device=x.device)
+        out = self._buf("y", (m // self.world, d), self.partial_dtype, x.device)
         side = self._side_stream(x.device)
         px = self._peer(x, plan)
         self._hidden = []
         done = 0
+        ff_local = self.w_up.shape[1]
+        fused = hasattr(self.ops, "gemm")                    # the device ops take output buffers
         for c, (start, rows) in enumerate(plan):
             share = rows // self.world
             xs = x[start:start + rows]
-            h = self.ops.linear(xs, self.w_up, torch.bfloat16)
-            y = self.ops.linear(h, self.w_down, self.partial_dtype)
+            if fused:
+                h = self.ops.linear(xs, self.w_up, torch.bfloat16,
+                                    out=self._buf(("h", c), (rows, ff_local), torch.bfloat16, x.device))
+                y = self.ops.linear(h, self.w_down, self.partial_dtype,
+                                    out=self._buf(("partial", c), (rows, d), self.partial_dtype, x.device))
+            else:
+                h = self.ops.linear(xs, self.w_up, torch.bfloat16)
+                y = self.ops.linear(h, self.w_down, self.partial_dtype)
             self._hidden.append(h)
             dst = out[done:done + share]
             done += share
@@ -1131,7 +1173,8 @@ class TensorParallelMlp:
                         px.reduce_scatter(c, y, dst)
                     else:
                         dist.reduce_scatter_tensor(dst, y, op=dist.ReduceOp.SUM, group=self.group)
-                y.record_stream(side)
+                if not fused:
+                    y.record_stream(side)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return out
@@ -1140,13 +1183,11 @@ class TensorParallelMlp:
         m = x.shape[0]
         plan = self.pieces(m)
         first = [sum(rows // self.world for _, rows in plan[:c]) for c in range(len(plan))]   # of my rows, per piece
-        dx = torch.empty((m, x.shape[1]), dtype=self.partial_dtype, device=x.device)
-        dx_local = torch.empty((m // self.world, x.shape[1]), dtype=self.partial_dtype, device=x.device)
+        dx = self._buf("dx_partial", (m, x.shape[1]), self.partial_dtype, x.device)
+        dx_local = self._buf("dx", (m // self.world, x.shape[1]), self.partial_dtype, x.device)
         side = self._side_stream(x.device)
         main = torch.cuda.current_stream() if side is not None else None
-        if side is not None:
-            dx.record_stream(side)
-            dx_local.record_stream(side)
+        fused = hasattr(self.ops, "gemm")
         px = self._peer(x, plan) if dy_local.dtype == self.partial_dtype else None
 
         def gather(c):
@@ -1159,7 +1200,7 @@ class TensorParallelMlp:
                     done = torch.cuda.Event()
                     done.record(side)
                 return dy, done
-            dy = torch.empty((rows, dy_local.shape[1]), dtype=dy_local.dtype, device=x.device)
+            dy = self._buf(("dy", c), (rows, dy_local.shape[1]), dy_local.dtype, x.device)
             if side is None:
                 dist.all_gather_into_tensor(dy, src, group=self.group)
                 return dy, None
@@ -1167,7 +1208,6 @@ class TensorParallelMlp:
                 dist.all_gather_into_tensor(dy, src, group=self.group)
                 done = torch.cuda.Event()
                 done.record(side)
-            dy.record_stream(side)
             return dy, done
 
         if side is not None:
@@ -1182,7 +1222,12 @@ class TensorParallelMlp:
                 main.wait_event(ready)
             h = self._hidden[c]
             self.ops.linear_weight_grad(h, dy, dw_down)                   # dW_down += h^T dy
-            dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16)   # dh = dy W_down^T
+            if fused:                                                     # dh = dy W_down^T
+                dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16,
+                                                out=self._buf("dh", (rows, self.w_down.shape[0]), torch.bfloat16,
+                                                              x.device))
+            else:
+                dh = self.ops.linear_input_grad(dy, self.w_down, torch.bfloat16)
             xs = x[start:start + rows]
             self.ops.linear_weight_grad(xs, dh, dw_up)                    # dW_up += x^T dh
             dxs = dx[start:start + rows]

@@ -241,6 +241,31 @@ def test_vocab_shards_cover_the_vocabulary_in_whole_tiles():
     assert par.vocab_shards(1000, 2) == [(0, 512), (512, 1000)]
 
 
+def test_moe_token_slices_cover_every_token_once():
+    """``ExpertParallelMoe._slices``: equal slices, weighted slices (the default tapers towards the
+    end), and the fall-back to one slice when the weights do not divide the tokens or a slice
+    would be shorter than 256 tokens."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    par = entry.load_package().parallel
+
+    def slices(pieces, n):
+        ep = par.ExpertParallelMoe.__new__(par.ExpertParallelMoe)
+        ep.pieces = pieces
+        return ep._slices(n)
+
+    assert slices(4, 32768) == [(0, 8192), (8192, 8192), (16384, 8192), (24576, 8192)]
+    assert slices([6, 5, 3, 2], 32768) == [(0, 12288), (12288, 10240), (22528, 6144), (28672, 4096)]
+    assert slices(3, 32768) == [(0, 32768)]                  # 32768 is no multiple of 3
+    assert slices([1, 2, 2, 1], 32768) == [(0, 32768)]       # sixths do not divide it either
+    assert slices([6, 5, 3, 2], 1024) == [(0, 1024)]         # the last slice would hold 128 tokens
+    assert slices(2, 300) == [(0, 300)]                      # slices shorter than 256 tokens
+    for pieces, n in ((8, 32768), ([4, 4, 4, 2, 1, 1], 32768), ([6, 5, 3, 2], 16384)):
+        got = slices(pieces, n)
+        assert got[0][0] == 0 and sum(rows for _, rows in got) == n
+        assert all(a[0] + a[1] == b[0] for a, b in zip(got, got[1:]))
+
+
 def test_exchange_plan_offsets_are_consistent_between_ranks():
     sys.path.insert(0, ROOT)
     import __graft_entry__ as entry
