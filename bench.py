@@ -58,11 +58,9 @@ def measured_peaks():
 class ClockSampler(threading.Thread):
     """Polls the SM clock and the throttle reasons while the timed region runs.
 
-    Reads them through NVML inside this process (initialised before the timed region starts):
-    starting `nvidia-smi` every 100 ms attaches a new process to every GPU of the box each
-    time, which now and then held up this process's kernel launches for tens of milliseconds --
-    invisible in a 57 ms step, a threefold error in a 3 ms one.  `nvidia-smi` is the fallback
-    when the NVML binding is missing."""
+    Reads them through NVML inside this process (initialised before the timed region starts)
+    rather than by starting `nvidia-smi` every 100 ms, which attaches a new process to every
+    GPU of the box each time.  `nvidia-smi` is the fallback when the NVML binding is missing."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
