@@ -1248,10 +1248,10 @@ int b200gemm_moe_ep_push(b200gemm_handle_t h, void* stream, const void* x, const
     const int per_batch = 32 / top_k_pad;
     const size_t row_bytes = static_cast<size_t>(d) * 2;
     const size_t fixed = sizeof(PushBulkSmem) + static_cast<size_t>(experts) * sizeof(int);
-    const size_t budget = 200 * 1024;
+    const size_t smem_limit = 200 * 1024;
     const int need = (kPushPendingBatches + 2) * per_batch;
     int stages = std::max(32, need);
-    if (budget > fixed) stages = static_cast<int>(std::min<size_t>(stages, (budget - fixed) / row_bytes));
+    if (smem_limit > fixed) stages = static_cast<int>(std::min<size_t>(stages, (smem_limit - fixed) / row_bytes));
     if (stages >= need && stages <= kPushMaxStages) {
       const size_t smem = stages * row_bytes + fixed;
       if (!h->push_bulk_opt_in) {
@@ -1305,8 +1305,8 @@ int b200gemm_moe_ep_pull_combine(b200gemm_handle_t h, void* stream, void* const*
     while (top_k_pad < top_k) top_k_pad *= 2;
     const size_t stage_bytes = static_cast<size_t>(top_k) * d * 2;
     const size_t fixed = sizeof(PullBulkSmem) + static_cast<size_t>(experts) * sizeof(int);
-    const size_t budget = 200 * 1024;
-    int stages = stage_bytes > 0 && budget > fixed ? static_cast<int>(std::min<size_t>(8, (budget - fixed) / stage_bytes)) : 0;
+    const size_t smem_limit = 200 * 1024;
+    int stages = stage_bytes > 0 && smem_limit > fixed ? static_cast<int>(std::min<size_t>(8, (smem_limit - fixed) / stage_bytes)) : 0;
     if (stages >= 2) {
       const size_t smem = stages * stage_bytes + fixed;
       const int bulk_grid = static_cast<int>(std::min<int64_t>(tokens, h->exchange_ctas));

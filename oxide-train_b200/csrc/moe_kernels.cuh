@@ -1129,7 +1129,7 @@ __global__ void __launch_bounds__(256) peer_barrier_kernel(PeerWords words, int 
         if (start == 0) {
           start = now;
         } else if (now - start > limit_ns) {
-          atomicCAS(status, 0, 108);
+          atomicCAS(status, 0, kDevTimeoutPeer);
           break;
         }
       }
