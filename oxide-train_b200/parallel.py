@@ -8,14 +8,24 @@ the compute is reached through a small ``ops`` object so that tests can stand
 in a CPU implementation for it.
 
 * :class:`VocabParallelHead` — fused lm-head + cross-entropy with the vocabulary
-  split over ranks; one MAX and one SUM all-reduce of per-row statistics in the
-  forward, a SUM all-reduce of ``d_hidden`` in the backward.
+  split over ranks; one all-gather of the per-row statistics and one merge
+  kernel in the forward, the sum of ``d_hidden`` over the shards in the
+  backward (copy-engine reduce-scatter under the weight-gradient GEMM, or
+  NCCL's all-reduce).
 * :class:`ExpertParallelMoe` — experts split over ranks, tokens split over
-  ranks; counts exchange, all-to-all dispatch, grouped expert GEMMs on the rows
-  received, all-to-all combine.
+  ranks; on GPUs the exchange is driven from the device (counts gathered by
+  the barrier kernel, rows dispatched into and fetched from peer memory by
+  this library's kernels, token slices as a pipeline); over ``gloo`` a counts
+  exchange and two all-to-alls.
 * :class:`TensorParallelMlp` — column-parallel up, row-parallel down,
-  reduce-scatter of the partial outputs, chunked so that the collective of one
-  chunk overlaps the GEMMs of the next.
+  reduce-scatter of the partial outputs, in row pieces so that the exchange of
+  one piece overlaps the GEMMs of the next.
+* :class:`PeerRowExchange`, :class:`PeerBarrier` — what the above share on
+  GPUs: row blocks moved by the copy engines between peer-mapped buffers, and
+  a one-block barrier kernel over peer memory.
+
+On GPUs the classes keep their large buffers between steps: what ``forward`` /
+``backward`` return is valid until the next call of the same method.
 """
 from __future__ import annotations
 
