@@ -891,6 +891,45 @@ def run_only(args):
                           "device_status": gemm.device_status()}), flush=True)
         gemm.close()
         return
+    if name == "moe" and kind.startswith("exchange"):
+        # The expert exchange's dispatch and combine kernels alone, two ranks' buffers in this one
+        # GPU's memory (every "peer" store and load is local: what is timed is the kernels' own
+        # throughput, not the links).  moe.exchange: stores / loads from two blocks per SM;
+        # moe.exchange_bulk: bulk asynchronous copies through shared memory from 48 blocks.
+        import ctypes as C
+        n_tok, d, experts, top_k, world = args.only_tokens, 1536, 64, 8, 2
+        ops = pkg.parallel.DeviceOps(gemm)
+        x = torch.randn((n_tok, d), device=dev).to(bf)
+        bias = 0.5 * torch.log(1.0 / torch.arange(1, experts + 1, device=dev, dtype=f32))
+        logits = (torch.randn((n_tok, experts), device=dev) + bias).contiguous()
+        r = ops.route(logits, top_k, True)
+        counts = torch.stack([r.accepted_counts.to(torch.int32), torch.zeros_like(r.accepted_counts, dtype=torch.int32)])
+        dst_base, _, _ = ops.ep_plan(counts.contiguous(), world, 0, experts)
+        cap = n_tok * top_k
+        inbox = [torch.zeros((cap, d), dtype=bf, device=dev) for _ in range(world)]
+        ptrs = (C.c_void_p * world)(*[t.data_ptr() for t in inbox])
+        out = torch.empty((n_tok, d), dtype=f32, device=dev)
+        gemm.set_exchange_ctas(48 if kind.endswith("bulk") else 0, kind.endswith("bulk"))
+
+        def fn():
+            ops.ep_push(x, r, dst_base, ptrs, cap, world, experts)
+            ops.ep_pull_combine(ptrs, r, dst_base, None, cap, world, experts, d, out)
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        s0, e0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            fn()
+        e0.record()
+        torch.cuda.synchronize()
+        ms = s0.elapsed_time(e0) / args.steps
+        moved = 2.0 * n_tok * top_k * d * 2 + n_tok * d * (2 + 4)       # rows written + read, x read, out written
+        print(json.dumps({"only": args.only, "tokens": n_tok, "ms": ms, "gb_per_s": moved / ms / 1e6,
+                          "bytes_per_step": moved, "device_status": gemm.device_status()}), flush=True)
+        gemm.set_exchange_ctas(0)
+        gemm.close()
+        return
     if name == "moe":
         n_tok, d, ff, experts, top_k = args.only_tokens, 1536, 768, 64, 8
         x = torch.randn((n_tok, d), device=dev).to(bf)
@@ -1141,6 +1180,7 @@ def main():
     ap.add_argument("--only", default=None,
                     help="profiling aid: run one piece, e.g. qkv.forward, mlp_up.weight_grad, lm_head.fused_forward, "
                          "lm_head.fused_backward, moe.forward, moe.gated_forward, moe.backward, moe.gated_backward, "
+                         "moe.exchange, moe.exchange_bulk, "
                          "mlp_gate_up.{swiglu,swiglu_no_panel,plain_gemm_only,unfused}")
     ap.add_argument("--only-tokens", type=int, default=M_TOKENS)
     ap.add_argument("--tile", default="auto", choices=["auto", "wide", "narrow"],
