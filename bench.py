@@ -442,7 +442,8 @@ def build_sharded(workload, torch, pkg, gemm, ops, dev, rank, world):
         # (the all-reduce takes about the same time whatever N is while the GEMM shrinks with N)
         if HEAD_EXCHANGE == "copy" or world == 1:
             # d_hidden's sum goes by copy-engine pushes into peer memory and a local sum: no SMs to
-            # set aside for a collective's kernels beyond the few its one-element barriers run on
+            # set aside for a collective's kernels; four stay free so that the sum kernel and the
+            # barrier kernel start at once
             reserve = 0 if world == 1 else 4
             # each rank keeps its own m / N rows of the summed d_hidden (a reduce-scatter): what a
             # row-parallel layer below the head consumes; `d_hidden="all"` would gather them again

@@ -513,13 +513,14 @@ class ExpertParallelMoe:
     def _forward_device(self, x, scores, scores_are_logits, residual, out_dtype):
         """Several GPUs, device-driven exchange: nothing is read back to the host.
 
-        Per slice of tokens: route; all-gather the per-expert counts; a plan kernel turns
-        them into inbox offsets; a push kernel writes every routed row straight into its
-        expert owner's inbox (peer stores); barrier; the two grouped GEMMs run on what
-        arrived; barrier; a combine kernel reads each result row from its owner's result
-        buffer (peer loads).  Slices alternate between two streams, so the NVLink traffic
-        of one slice runs beside the tensor-core work of the other; the whole step is
-        enqueued without a host round trip."""
+        Per slice of tokens: route; gather the per-expert counts (on the barrier kernel's
+        way, or NCCL's all-gather); a plan kernel turns them into inbox offsets; a dispatch
+        kernel puts every routed row straight into its expert owner's inbox (peer memory);
+        barrier; the two grouped GEMMs run on what arrived; barrier; a combine kernel
+        fetches each result row from its owner's result buffer.  The slices form a pipeline
+        (see ``_forward_device_body``), so the NVLink traffic of one slice runs beside the
+        tensor-core work of its neighbours; the whole step is enqueued without a host
+        round trip."""
         import ctypes as C
         n, d = x.shape
         ff, d_out = self.w_up.shape[2], self.w_down.shape[2]
@@ -570,8 +571,8 @@ class ExpertParallelMoe:
         out = dv.get(("out", out_dtype))
         if out is None:
             out = dv[("out", out_dtype)] = torch.empty((n, d_out), dtype=out_dtype, device=x.device)
-        # The expert GEMMs leave a few SMs to the one-element all-reduces used as barriers
-        # and to the other slice's small kernels.
+        # The expert GEMMs leave `reserve_sms` SMs to the neighbouring slices' dispatch and
+        # combine kernels (and to NCCL's barriers, where those are used).
         with _ReservedSms(self.ops, self.reserve_sms):
             return self._forward_device_body(x, scores, scores_are_logits, residual, out, dv, slices, caps, first)
 
@@ -986,7 +987,7 @@ class PeerRowExchange:
     the link rate, while the GEMMs it ran beside slowed down too).  Here every rank instead
     *copies* the row block each peer owns straight into that peer's inbox (``cudaMemcpyAsync``
     between peer-mapped buffers: the copy engines move the bytes over NVLink, no SM is
-    involved), a one-element all-reduce orders the ranks, and a small kernel of this library
+    involved), a barrier orders the ranks, and a small kernel of this library
     adds the ``world`` parts that arrived (fp32 adds, rank order).  The all-gather is the same
     without the sum.  Buffers are ``torch.distributed`` symmetric memory; the row data moves by
     copy engine only, and the ranks wait for one another in a one-block barrier kernel
