@@ -563,7 +563,10 @@ B200GEMM_API int b200gemm_moe_combine(b200gemm_handle_t h, void* stream, const v
  *                 (peer loads), ranks added in order in fp32; a row at or beyond
  *                 `result_rows` is skipped and device status 105 recorded.
  * The caller orders the phases between ranks (a barrier after every rank's push and
- * after every rank's expert GEMMs); the kernels themselves never wait on a peer.
+ * after every rank's expert GEMMs, e.g. b200gemm_peer_barrier, which can also gather
+ * all_counts); the kernels themselves never wait on a peer.  After
+ * b200gemm_set_exchange_ctas(h, n, 1) push and pull_combine move their rows by bulk
+ * asynchronous copies through shared memory from n blocks (bit-identical results).
  * world <= 8, experts a multiple of world and <= 192, top_k <= 16, d % 8 == 0; every row buffer
  * (x, the peers' inboxes and result buffers, residual, out) 16-byte aligned.
  */
